@@ -1,0 +1,194 @@
+/*
+ * qengine_b200 -- C ABI of the batch-1 speculative-decode operator library for B200 (sm_100a).
+ *
+ * This header is the drop-in boundary. Every entry point replaces one host launcher of the
+ * reference project (manaspros/qengine): `csrc/ops.h` (the launchers behind the python module
+ * `qengine._C`, bound in `csrc/bindings.cpp`) and `csrc/gemv_w4.h` (the W4A16 GEMV behind
+ * `qengine._w4`, bound in `csrc/gemv_w4_bind.cpp`). The reference exports these with C++ linkage;
+ * here they are plain `extern "C"` symbols over raw device pointers, sizes and a stream handle, so
+ * they can be bound from pybind11, ctypes, cgo or anything else that can call C.
+ *
+ * Conventions (same as the reference, csrc/ops.h:1-2, csrc/bindings.cpp:1-4):
+ *   - all pointers are device pointers unless a comment says "host";
+ *   - activations / outputs are bf16 (passed as void*), control buffers int32, state fp32;
+ *   - `ld*` arguments are row strides in ELEMENTS; rows have unit inner stride;
+ *   - `stream` is a cudaStream_t passed as void*; every call only enqueues work on it, never
+ *     allocates and never synchronises, so a whole decode cycle can be captured in a CUDA graph;
+ *   - n (rows per pass) is 1..8.
+ * Unlike the reference launchers (which return void) every launcher returns the cudaError_t of
+ * the launch as an int (0 = cudaSuccess), or QE_ERR_ARG for an argument the kernels cannot serve.
+ *
+ * Numerical contract kept from the reference: row r of an n-row call is bit-identical to the
+ * 1-row call on that row, for every op; results are bit-identical run to run (no float atomics).
+ */
+#ifndef QENGINE_B200_H_
+#define QENGINE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QE_ERR_ARG (-22)
+#define QE_MAX_ROWS 8
+
+/* Library / device information. Returns the ABI version (bumped on incompatible changes). */
+int qe_abi_version(void);
+/* Number of SMs of the current device (cached per device). */
+int qe_sm_count(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Row ops. Reference: csrc/ops.h:6-17 (launch_embed .. launch_argmax), kernels csrc/basic.cu.
+ * ------------------------------------------------------------------------------------------ */
+
+/* out[r, :] = table[tok[r], :] for r < n; token ids outside [0, V) give a zero row.
+ * Replaces launch_embed (csrc/ops.h:6-7). */
+int qe_embed(const void* table, const int* tok, void* out, int n, int H, int V, long ldo,
+             void* stream);
+
+/* Zero-centred RMSNorm with optional fused residual add. If delta != NULL, x = bf16(x + delta) is
+ * written back in place first. out = bf16(x * rsqrt(mean(x^2) + eps) * (1 + w)).
+ * Replaces launch_rmsnorm1p (csrc/ops.h:8-9). */
+int qe_rmsnorm1p(void* x, const void* delta, const void* w, void* out, int rows, int H, long ldx,
+                 long ldd, long ldo, float eps, void* stream);
+
+/* out[r, j] = bf16(sum_k W[j, k] * x[r, k]); W bf16 [N, K] row-major, K % 8 == 0, 16-byte aligned
+ * rows. Replaces launch_gemv_bf16 (csrc/ops.h:10-11). */
+int qe_gemv_bf16(const void* W, const void* x, void* out, int nr, int N, int K, long ldx, long ldo,
+                 void* stream);
+
+/* gu rows are [gate(I) | up(I)]; out = bf16(bf16(silu(gate)) * up).
+ * Replaces launch_swiglu (csrc/ops.h:12). */
+int qe_swiglu(const void* gu, void* out, int n, int I, long ldg, long ldo, void* stream);
+
+/* Per-row argmax with torch semantics (NaN is the maximum, ties go to the lowest index, an
+ * all -inf row gives 0). pv/pi: scratch with rows*nb entries each. out[r] = idmap ? idmap[i] : i.
+ * Replaces launch_argmax (csrc/ops.h:13-14). */
+int qe_argmax(const void* x, int rows, int n, long ldx, float* pv, int* pi, int nb, int* out,
+              const int* idmap, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Device-side bookkeeping of one pass. ctl (int32[>=24]): [0] pos, [1] pending DeltaNet rows,
+ * [2] mode (0 prefill, 1 decode/verify), [3] m, [4] cycles, [5] accepted drafts, [16+m] histogram.
+ * Reference: csrc/ops.h:15-19, kernels csrc/basic.cu:256-307. Integer results are bit-exact.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Greedy longest-prefix acceptance. Replaces launch_accept (csrc/ops.h:15-16). */
+int qe_accept(const int* in_tok, const int* am, int n, int* ctl, int* next_tok, int* log,
+              int max_len, void* stream);
+
+/* Advance pos by m+1, pending = m+1, next input = [am[m], drafts[0..k)].
+ * Replaces launch_commit (csrc/ops.h:17). */
+int qe_commit(int* ctl, int* in_tok, const int* am, const int* drafts, int k, void* stream);
+
+/* mpos[0] = off < 0 ? pos : pos + m + 1 + off; optional dst[:] = src[m, :]; optional
+ * draft0[0] = mtp_am[m]. Replaces launch_mtp_select (csrc/ops.h:18-19). */
+int qe_mtp_select(const int* ctl, int* mpos, int off, const void* src, long lds, void* dst, int H,
+                  const int* mtp_am, int* draft0, void* stream);
+
+/* Measurement hook, no counterpart in the reference: in verify mode (ctl[2] == 1) overwrite the k
+ * drafts in_tok[1..k] so that exactly `a` are accepted: draft j (position pos + 1 + j) becomes
+ * truth[pos + 1 + j] for j < a and (truth + 1) mod vocab otherwise. a < 0 does nothing. */
+int qe_force_drafts(int* in_tok, const int* ctl, const int* truth, int truth_len, int a, int k,
+                    int vocab, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Gated DeltaNet step for n new rows with lazy rollback (csrc/ops.h:20-24, csrc/gdn.cu).
+ * D = key head dim = value head dim (64 or 128; the reference fixes 128, csrc/bindings.cpp:133).
+ * S fp32 [Hv, D, D]; ring bf16 [16, C] with C = 2*Hk*D + Hv*D; st_k, st_v fp32 [8, Hv, D];
+ * st_g fp32 [8, Hv, 2]. `q` (the reference's thread-split knob) is accepted and ignored.
+ * ------------------------------------------------------------------------------------------ */
+int qe_gdn_step_n(const void* qkv, const void* z, const void* b, const void* a, long ldp,
+                  void* ring, const void* conv_w, const void* A_log, const void* dt_bias,
+                  const void* norm_w, float* S, float* st_k, float* st_v, float* st_g,
+                  const int* ctl, void* out, long ldo, int n, int Hk, int Hv, int D, float eps,
+                  int q, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Gated GQA attention for n rows at positions pos[0] + t (csrc/ops.h:25-30, csrc/attn.cu).
+ * hd = head dim (64, 128 or 256; the reference fixes 256, csrc/bindings.cpp:155).
+ * ------------------------------------------------------------------------------------------ */
+
+/* q/k RMSNorm1p per head, partial RoPE on the first rd dims, q -> q_out [n, Hq*hd] (contiguous),
+ * k, v -> caches [Hkv, max_len, hd] at pos + t (skipped when pos + t >= max_len).
+ * Replaces launch_attn_prep (csrc/ops.h:25-27). */
+int qe_attn_prep(const void* qg, const void* k, const void* v, long ldp, const void* qnw,
+                 const void* knw, const float* inv_freq, const int* pos, void* q_out, void* kc,
+                 void* vc, int n, int Hq, int Hkv, int hd, int max_len, int rd, float eps,
+                 void* stream);
+
+/* Split-KV flash decoding + combine + sigmoid gate. part_o fp32 [>=n, Hq, NS, hd], part_ml fp32
+ * [>=n, Hq, NS, 2]. Replaces launch_attn_decode (csrc/ops.h:28-30). */
+int qe_attn_decode(const void* q, const void* kc, const void* vc, const int* pos, const void* qg,
+                   long ldp, float* part_o, float* part_ml, void* out, long ldo, int n, int Hq,
+                   int Hkv, int hd, int max_len, int NS, float scale, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Run-time switches and L2 controls (csrc/ops.h:31-36).
+ * ------------------------------------------------------------------------------------------ */
+void qe_set_pdl_trigger(int on); /* kernels signal griddepcontrol.launch_dependents */
+void qe_set_pdl_launch(int on);  /* own kernels launch with programmatic stream serialization */
+void qe_set_gdn_early(int on);   /* DeltaNet kernel: state replay before the dependency wait */
+void qe_set_gdn_phases(int on);  /* accepted for compatibility; the kernel has a single path */
+int qe_l2_persist_limit(size_t bytes);
+int qe_stream_access_window(uintptr_t base, size_t bytes, float hit_ratio, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * W4A16 GEMV / skinny GEMM: out[n, m] = bf16(sum_g scale[m, g] * sum_{k in g} (u[m,k]-8) x[n,k]).
+ * Reference: csrc/gemv_w4.h:9-55 (GemvParams, LaunchCfg, LaunchPlan, plan_gemv_w4, auto_ksplit,
+ * launch_gemv_w4). Packed layout (python/qengine/quant.py:1-30):
+ *   qw     int32 [Mp/16, Kp/64, 32, 4]   (16-row tile, 64-k chunk, lane, word)
+ *   scales fp16  [Mp/16, Kp/128, 16]
+ * ------------------------------------------------------------------------------------------ */
+enum { QE_EPI_NONE = 0, QE_EPI_SWIGLU = 1 };
+
+typedef struct qe_w4_params {
+  const void* qw;      /* packed int4 weights */
+  const void* scales;  /* fp16 group scales */
+  const void* x;       /* bf16 activations, N rows, stride ldx */
+  void* out;           /* bf16 output, N rows, stride ldo */
+  float* ws;           /* fp32 partial-sum slots, qe_w4_plan::ws_floats entries, any contents */
+  int* counters;       /* int32 arrival counters, qe_w4_plan::counters entries, zero between calls */
+  int M;               /* logical output rows (QE_EPI_SWIGLU: intermediate size I) */
+  int K;               /* logical reduction length */
+  int Mp, Kp;          /* padded sizes (multiples of 16 / 128) */
+  int N;               /* activation rows, 1..8 */
+  long ldx, ldo;
+  int epilogue;        /* QE_EPI_* */
+} qe_w4_params;
+
+/* Launch options with the reference's names (csrc/gemv_w4.h:27-39). 0 / -1 mean "auto by shape".
+ * Every accepted combination is deterministic and independent of N. */
+typedef struct qe_w4_cfg {
+  int warps;         /* warps per block: 0 (auto), 4, 8, 16 */
+  int unroll;        /* weight groups (1 KB each) in flight per warp: 0 (auto), 1, 2, 4 */
+  int ksplit;        /* mode 0: blocks along K; 0 = auto */
+  int pdl;           /* launch with programmatic stream serialization */
+  int variant;       /* load flavour, 0..3 (see w4_stream.cu) */
+  int mode;          /* -1 auto, 0 = (tile, ksplit) grid, 2 = persistent unit stream */
+  int blocks_per_sm; /* mode 2: 0 = auto */
+  int min_units;     /* mode 2: minimum 1-KB units per warp */
+} qe_w4_cfg;
+
+typedef struct qe_w4_plan {
+  int mode;
+  int grid_x, grid_y, threads;
+  long ws_floats; /* required size of qe_w4_params::ws */
+  long counters;  /* required size of qe_w4_params::counters */
+} qe_w4_plan;
+
+/* Default-initialise a cfg (all auto, pdl on, min_units 4). */
+void qe_w4_cfg_default(qe_w4_cfg* cfg);
+/* Resolve the launch for a shape; never depends on N. Replaces plan_gemv_w4 (gemv_w4.h:50). */
+int qe_w4_plan_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, qe_w4_plan* plan);
+/* Replaces auto_ksplit (gemv_w4.h:53). */
+int qe_w4_auto_ksplit(int Mp, int Kp, int N, int warps);
+/* Replaces launch_gemv_w4 (gemv_w4.h:56). */
+int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QENGINE_B200_H_ */

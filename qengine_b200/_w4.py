@@ -1,0 +1,115 @@
+"""Python op surface `_w4`: same functions, keyword arguments, defaults and error behaviour as the
+reference module `qengine._w4` (csrc/gemv_w4_bind.cpp:24-120), bound to qe_w4_gemv of
+libqengine_b200.so through ctypes.
+
+    gemv(x, qw, scales, out, M, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
+         blocks_per_sm=0, min_units=4)
+    gemv_swiglu(x, qw, scales, out, I, ...same...)
+    auto_ksplit(Mp, Kp, N, warps=8)
+
+Workspace: like the reference binding (gemv_w4_bind.cpp:12-22, 71-79) a per-device, grow-only
+pair of buffers is kept here -- fp32 partial-sum slots (contents irrelevant) and int32 arrival
+counters that the kernel leaves zeroed. They grow only outside CUDA-graph capture (the first,
+eager call of a shape allocates); replaced buffers stay alive because a captured graph may still
+point at them.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._lib import W4Cfg, W4Params, W4Plan, check, lib
+
+EPI_NONE, EPI_SWIGLU = 0, 1
+_MIN_WS_FLOATS, _MIN_COUNTERS = 1 << 18, 1 << 14
+
+
+class _Workspace:
+    def __init__(self):
+        self.keep, self.ws, self.counters = [], None, None
+
+
+_per_device: dict[int, _Workspace] = {}
+
+
+def _req(cond, msg):
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _workspace(dev: torch.device, ws_floats: int, counters: int) -> _Workspace:
+    W = _per_device.setdefault(dev.index if dev.index is not None else torch.cuda.current_device(),
+                               _Workspace())
+    if W.ws is None or W.ws.numel() < ws_floats:
+        _req(not torch.cuda.is_current_stream_capturing(),
+             "W4 workspace would have to grow during graph capture: run the shape once eagerly first")
+        if W.ws is not None:
+            W.keep.append(W.ws)
+        W.ws = torch.empty(max(ws_floats, _MIN_WS_FLOATS), dtype=torch.float32, device=dev)
+    if W.counters is None or W.counters.numel() < counters:
+        _req(not torch.cuda.is_current_stream_capturing(),
+             "W4 counters would have to grow during graph capture: run the shape once eagerly first")
+        if W.counters is not None:
+            W.keep.append(W.counters)
+        W.counters = torch.zeros(max(counters, _MIN_COUNTERS), dtype=torch.int32, device=dev)
+    return W
+
+
+def _run(x, qw, scales, out, M, epilogue, warps, unroll, ksplit, pdl, variant, mode, bps, min_units):
+    for t in (x, qw, scales, out):
+        _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
+    _req(x.dtype == torch.bfloat16, "x must be bf16 (W4A16 kernel)")
+    _req(out.dtype == torch.bfloat16, "out must be bf16")
+    _req(qw.dtype == torch.int32 and qw.dim() == 4 and qw.size(2) == 32 and qw.size(3) == 4,
+         "qw must be int32 [Mp/16, Kp/64, 32, 4] from quant.quantize_w4")
+    _req(scales.dtype == torch.float16 and scales.dim() == 3 and scales.size(2) == 16,
+         "scales must be fp16 [Mp/16, Kp/128, 16]")
+    _req(qw.is_contiguous() and scales.is_contiguous(), "packed tensors must be contiguous")
+    _req(x.dim() == 2 and out.dim() == 2, "x [N,K], out [N,M]")
+    _req(x.stride(1) == 1 and out.stride(1) == 1, "x and out need unit stride along K / M")
+    N, K = x.size(0), x.size(1)
+    M = int(M)
+    _req(1 <= N <= 8, "N must be 1..8")
+    _req(out.size(0) == N and out.size(1) == M, "out shape must be [N, M]")
+    Mp, Kp = qw.size(0) * 16, qw.size(1) * 64
+    _req(Kp % 128 == 0 and scales.size(0) == qw.size(0) and scales.size(1) == Kp // 128,
+         "qw / scales shapes disagree")
+    _req(Kp - 128 < K <= Kp, f"x has K={K} but the packed weight has Kp={Kp}")
+    if epilogue == EPI_SWIGLU:
+        _req(Mp // 2 - 8 < M <= Mp // 2, "SwiGLU: out width I must match packed rows/2")
+    else:
+        _req(Mp - 16 < M <= Mp, "out width M must match packed rows")
+    _req(x.data_ptr() != out.data_ptr(), "in-place not supported")
+    _req(warps in (0, 4, 8, 16), "warps in {0 (auto),4,8,16}")
+    _req(unroll in (0, 1, 2, 4), "unroll in {0 (auto),1,2,4}")
+    _req(mode in (-1, 0, 2), "mode in {-1 (auto), 0, 2}")
+
+    p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None,
+                 M, K, Mp, Kp, N, x.stride(0), out.stride(0), epilogue)
+    cfg = W4Cfg(int(warps), int(unroll), int(ksplit), int(bool(pdl)), int(variant), int(mode),
+                int(bps), int(min_units))
+    plan = W4Plan()
+    check(lib.qe_w4_plan_gemv(C.byref(p), C.byref(cfg), C.byref(plan)), "gemv_w4 plan")
+    W = _workspace(x.device, plan.ws_floats, plan.counters)
+    p.ws, p.counters = W.ws.data_ptr(), W.counters.data_ptr()
+    code = lib.qe_w4_gemv(C.byref(p), C.byref(cfg), torch.cuda.current_stream().cuda_stream)
+    _req(code == 0, f"gemv_w4 launch failed: CUDA error {code}")
+
+
+def gemv(x, qw, scales, out, M, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
+         blocks_per_sm=0, min_units=4):
+    """out[N, M] = x[N, K] @ W~^T (W packed by quant.quantize_w4)."""
+    _run(x, qw, scales, out, M, EPI_NONE, warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm,
+         min_units)
+
+
+def gemv_swiglu(x, qw, scales, out, I, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
+                blocks_per_sm=0, min_units=4):
+    """out[N, I] = silu(x @ Wg^T) * (x @ Wu^T) (packed by quant.quantize_w4_gate_up)."""
+    _run(x, qw, scales, out, I, EPI_SWIGLU, warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm,
+         min_units)
+
+
+def auto_ksplit(Mp, Kp, N, warps=8):
+    return int(lib.qe_w4_auto_ksplit(int(Mp), int(Kp), int(N), int(warps)))

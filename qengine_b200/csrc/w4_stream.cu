@@ -1,0 +1,452 @@
+// W4A16 GEMV / skinny GEMM for 1..8 activation rows on B200 (sm_100a).
+//
+//   out[n, m] = bf16( sum_g fp32(scale[m, g]) * sum_{k in group g} (u[m, k] - 8) * x[n, k] )
+//
+// Boundary: replaces gemv_w4_tile / gemv_w4_bsk of the reference (csrc/gemv_w4.cu:291-362) behind
+// qe_w4_gemv (reference launch_gemv_w4, csrc/gemv_w4.h:56). The packed wire format is the
+// reference's (python/qengine/quant.py:1-30): the matrix is a stream of 1 KB "units", unit
+// u = tile * G + g holding the int4 codes of 16 rows x 128 k (G = Kp / 128 groups per tile) as
+// two 512-byte chunks of 32 lanes x 16 bytes, plus 32 bytes of fp16 scales at scales + 16 * u.
+// Lane l = 4r + t of a chunk owns rows r and r + 8 and 16 consecutive k; word s of its 16 bytes
+// carries k0 + {0,1,2,3} with k0 = 64 c + 16 t + 4 s, nibble j = row r + 8 (j & 1),
+// k0 + 2 ((j >> 1) & 1) + (j >> 2). `(w >> 4j) & 0x000F000F | 0x43004300` is therefore the bf16
+// pair (128 + u, 128 + u) for one A register of mma.m16n8k16, and subtracting 136 gives the
+// signed code exactly. The k order inside the mma differs from memory order, which a dot product
+// does not see as long as the x fragment uses the same order: lane (r, t) feeds x[n = r] at the
+// same 16 consecutive k.
+//
+// Work split. The unit stream is cut into equal contiguous ranges, one per CTA, so every CTA reads
+// one contiguous slab of HBM (weights are 97 % of the bytes of a decode step). A range is walked
+// tile by tile; inside a tile the warps of the CTA take groups round-robin, each warp keeping
+// `U` units (U KB) of loads in flight. Two grids exist:
+//   mode 2: persistent, grid = min(SMs * occupancy, units / min work) CTAs over the whole stream;
+//   mode 0: grid (tiles, ksplit): CTA (x, y) owns the y-th k-slice of tile x.
+// Both are the same kernel body with a different range function.
+//
+// Determinism and row independence. Each (tile, group) product is accumulated by a fixed warp in
+// fp32 with the scale applied once per group; warps are summed in warp order through shared
+// memory; a tile cut across CTAs is finished by whichever CTA arrives last (integer arrival
+// counter, counting groups) which adds the per-CTA partials in ascending CTA order. Nothing
+// depends on timing or on N: the 8 columns of the mma are independent dot products, and no launch
+// decision looks at N. Row r of an N-row call is therefore bit-identical to the 1-row call, which
+// is what lets a speculative verify pass reproduce plain decode token for token.
+//
+// Why tensor-core mma also for one row: at 6.5 TB/s the SMs consume ~12.7e12 int4 weights per
+// second, i.e. under 3 issued thread-instructions per weight. Unpack + convert + FMA on CUDA
+// cores needs more than that; with the multiply-accumulate inside mma.sync the cost is 1.5
+// (per 8 weights: 3 shifts, 4 lop3, 4 sub.bf16x2, 1 mma). It also makes the one-row and k+1-row
+// sums the same instruction sequence, hence the same bits.
+#include <algorithm>
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "../../include/qengine_b200.h"
+
+namespace qb {
+namespace {
+
+struct W4Args {
+  const uint4* qw;
+  const __half* scales;
+  const bf16* x;
+  bf16* out;
+  float* ws;
+  int* counters;
+  int M, K, N;
+  int tiles, G;       // Mp / 16, Kp / 128
+  long ldx, ldo;
+  int ksplit;         // mode 0: gridDim.y
+  int total;          // tiles * G
+};
+
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+__device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+// One k-step of 16: four A registers from one packed word, times two x pairs.
+__device__ __forceinline__ void kstep(float (&c)[4], uint32_t w, uint32_t b0, uint32_t b1) {
+  constexpr uint32_t kNib = 0x000F000Fu, k128 = 0x43004300u, k136 = 0x43084308u;
+  const uint32_t a0 = sub_bf16x2(and_or(w, kNib, k128), k136);
+  const uint32_t a1 = sub_bf16x2(and_or(w >> 4, kNib, k128), k136);
+  const uint32_t a2 = sub_bf16x2(and_or(w >> 8, kNib, k128), k136);
+  const uint32_t a3 = sub_bf16x2(and_or(w >> 12, kNib, k128), k136);
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Streaming 16-byte weight load. V selects the cache flavour (A/B knob kept from the boundary):
+// 0 = read-only path, no L1 allocation; 1 = plain read-only; 2 = no L1 + 256 B L2 sector hint;
+// 3 = no L1 + L2 evict-first policy.
+template <int V>
+__device__ __forceinline__ uint4 ldw(const uint4* p, uint64_t pol) {
+  uint4 r;
+  if constexpr (V == 1) {
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  } else if constexpr (V == 2) {
+    asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  } else if constexpr (V == 3) {
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p), "l"(pol));
+  } else {
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  }
+  return r;
+}
+
+// The 16 x values of lane (row r, quarter t) for chunk c, masked beyond K and beyond N.
+__device__ __forceinline__ void load_x16(uint32_t (&xr)[8], const W4Args& a, int r, int t, int c,
+                                         bool vec) {
+  if (r >= a.N) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) xr[i] = 0u;
+    return;
+  }
+  const int k = c * 64 + 16 * t;
+  const bf16* xp = a.x + (long)r * a.ldx + k;
+  if (vec && k + 16 <= a.K) {
+    const uint4 lo = __ldg(reinterpret_cast<const uint4*>(xp));
+    const uint4 hi = __ldg(reinterpret_cast<const uint4*>(xp) + 1);
+    xr[0] = lo.x; xr[1] = lo.y; xr[2] = lo.z; xr[3] = lo.w;
+    xr[4] = hi.x; xr[5] = hi.y; xr[6] = hi.z; xr[7] = hi.w;
+  } else {
+    const unsigned short* xs = reinterpret_cast<const unsigned short*>(xp);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t e0 = (k + 2 * i < a.K) ? __ldg(xs + 2 * i) : 0u;
+      const uint32_t e1 = (k + 2 * i + 1 < a.K) ? __ldg(xs + 2 * i + 1) : 0u;
+      xr[i] = e0 | (e1 << 16);
+    }
+  }
+}
+
+__device__ __forceinline__ float silu_fast(float v) { return v / (1.0f + __expf(-v)); }
+
+// Store one finished 16 x 8 tile held as the mma C fragment of warp 0.
+template <int EPI>
+__device__ __forceinline__ void store_tile(const W4Args& a, int tile, const float (&f)[4], int lane) {
+  const int r = lane >> 2, t = lane & 3;
+  const int n0 = 2 * t, n1 = n0 + 1;
+  unsigned short* out = reinterpret_cast<unsigned short*>(a.out);
+  auto bits = [](float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); };
+  if constexpr (EPI == QE_EPI_NONE) {
+    const int m0 = tile * 16 + r, m1 = m0 + 8;
+    if (n0 < a.N) {
+      if (m0 < a.M) out[(long)n0 * a.ldo + m0] = bits(f[0]);
+      if (m1 < a.M) out[(long)n0 * a.ldo + m1] = bits(f[2]);
+    }
+    if (n1 < a.N) {
+      if (m0 < a.M) out[(long)n1 * a.ldo + m0] = bits(f[1]);
+      if (m1 < a.M) out[(long)n1 * a.ldo + m1] = bits(f[3]);
+    }
+  } else {
+    // gate rows 0..7 and up rows 8..15 of the tile are the same 8 outputs (quantize_w4_gate_up,
+    // python/qengine/quant.py:114-125): silu(gate) * up in fp32, one rounding.
+    const int j = tile * 8 + r;
+    if (j < a.M) {
+      if (n0 < a.N) out[(long)n0 * a.ldo + j] = bits(silu_fast(f[0]) * f[2]);
+      if (n1 < a.N) out[(long)n1 * a.ldo + j] = bits(silu_fast(f[1]) * f[3]);
+    }
+  }
+}
+
+// This warp's share (groups gb + warp, gb + warp + WARPS, ...) of tile `tile`, groups [gb, ge).
+template <int WARPS, int U, int V>
+__device__ __forceinline__ void accumulate(const W4Args& a, int tile, int gb, int ge, int warp,
+                                           int lane, float (&acc)[4], bool& waited, uint64_t pol,
+                                           bool vec) {
+  const int r = lane >> 2, t = lane & 3;
+  const uint4* wbase = a.qw + ((long)tile * a.G) * 64 + lane;       // 64 uint4 per unit
+  const __half* sbase = a.scales + ((long)tile * a.G) * 16 + r;
+  for (int g0 = gb + warp; g0 < ge; g0 += WARPS * U) {
+    uint4 w[U][2];
+    float slo[U], shi[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int g = g0 + u * WARPS;
+      if (g < ge) {
+        w[u][0] = ldw<V>(wbase + (long)g * 64, pol);
+        w[u][1] = ldw<V>(wbase + (long)g * 64 + 32, pol);
+        slo[u] = __half2float(__ldg(sbase + g * 16));
+        shi[u] = __half2float(__ldg(sbase + g * 16 + 8));
+      }
+    }
+    // Weights and scales never depend on the producer kernel; x does.
+    if (!waited) { dep_wait(); waited = true; }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int g = g0 + u * WARPS;
+      if (g < ge) {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t xr[8];
+          load_x16(xr, a, r, t, 2 * g + h, vec);
+          kstep(c, w[u][h].x, xr[0], xr[1]);
+          kstep(c, w[u][h].y, xr[2], xr[3]);
+          kstep(c, w[u][h].z, xr[4], xr[5]);
+          kstep(c, w[u][h].w, xr[6], xr[7]);
+        }
+        acc[0] = fmaf(slo[u], c[0], acc[0]);
+        acc[1] = fmaf(slo[u], c[1], acc[1]);
+        acc[2] = fmaf(shi[u], c[2], acc[2]);
+        acc[3] = fmaf(shi[u], c[3], acc[3]);
+      }
+    }
+  }
+}
+
+// Unit range of CTA b out of B over `total` units: equal shares, the first `total % B` one larger.
+__device__ __host__ __forceinline__ int range_begin(int total, int B, int b) {
+  const int per = total / B, rem = total % B;
+  return b * per + (b < rem ? b : rem);
+}
+__device__ __forceinline__ int range_owner(int total, int B, int u) {
+  const int per = total / B, rem = total % B;
+  const int big = rem * (per + 1);
+  return u < big ? u / (per + 1) : rem + (u - big) / per;
+}
+
+// MODE 2: grid.x CTAs over the whole unit stream. MODE 0: grid (tiles, ksplit).
+template <int WARPS, int U, int V, int EPI, int MODE>
+__global__ void __launch_bounds__(WARPS * 32) w4_stream_kernel(const W4Args a) {
+  dep_release();
+  __shared__ float red[WARPS][4][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int G = a.G;
+  const bool vec = ((a.ldx & 7) == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
+  uint64_t pol = 0;
+  if constexpr (V == 3) asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+
+  int u0, u1;  // this CTA's units
+  if constexpr (MODE == 0) {
+    const int y = blockIdx.y, ks = a.ksplit;
+    u0 = blockIdx.x * G + (int)((long)G * y / ks);
+    u1 = blockIdx.x * G + (int)((long)G * (y + 1) / ks);
+  } else {
+    u0 = range_begin(a.total, gridDim.x, blockIdx.x);
+    u1 = range_begin(a.total, gridDim.x, blockIdx.x + 1);
+  }
+  bool waited = false;
+  for (int u = u0; u < u1;) {
+    const int tile = u / G;
+    const int gb = u - tile * G;
+    const int ge = min(G, gb + (u1 - u));
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    accumulate<WARPS, U, V>(a, tile, gb, ge, warp, lane, acc, waited, pol, vec);
+    if (!waited) { dep_wait(); waited = true; }  // a warp without groups still orders its writes
+    if constexpr (WARPS > 1) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) red[warp][i][lane] = acc[i];
+      __syncthreads();
+      if (warp == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float s = red[0][i][lane];
+#pragma unroll
+          for (int w2 = 1; w2 < WARPS; ++w2) s += red[w2][i][lane];
+          acc[i] = s;
+        }
+      }
+      __syncthreads();
+    }
+    if (warp == 0) {
+      if (ge - gb == G) {
+        store_tile<EPI>(a, tile, acc, lane);
+      } else {
+        // Partial tile. Slot of this contribution: mode 0 -> tile * ksplit + y; mode 2 -> two
+        // per CTA (its first tile, its last tile). Publish, count groups, last arrival finishes.
+        int slot;
+        if constexpr (MODE == 0) slot = tile * a.ksplit + blockIdx.y;
+        else slot = 2 * blockIdx.x + (u == u0 ? 0 : 1);
+        float* mine = a.ws + (long)slot * 128;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) __stcg(mine + i * 32 + lane, acc[i]);
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) {
+          const int cnt = ge - gb;
+          last = (atomicAdd(a.counters + tile, cnt) + cnt == G);
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          __threadfence();
+          float f[4] = {0.f, 0.f, 0.f, 0.f};
+          if constexpr (MODE == 0) {
+            for (int s = 0; s < a.ksplit; ++s) {
+              const float* p = a.ws + (long)(tile * a.ksplit + s) * 128;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) f[i] += __ldcg(p + i * 32 + lane);
+            }
+          } else {
+            const int B = gridDim.x;
+            const int first = range_owner(a.total, B, tile * G);
+            const int lastb = range_owner(a.total, B, tile * G + G - 1);
+            for (int c = first; c <= lastb; ++c) {
+              // CTA c contributed its first segment if its range starts inside this tile,
+              // otherwise (range starts in an earlier tile) its last segment.
+              const int cs = range_begin(a.total, B, c);
+              const float* p = a.ws + (long)(2 * c + (cs >= tile * G ? 0 : 1)) * 128;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) f[i] += __ldcg(p + i * 32 + lane);
+            }
+          }
+          store_tile<EPI>(a, tile, f, lane);
+          if (lane == 0) a.counters[tile] = 0;
+        }
+      }
+    }
+    u += ge - gb;
+  }
+}
+
+using KernelFn = void (*)(const W4Args);
+
+template <int WARPS, int U, int V>
+KernelFn pick_tail(int epi, int mode) {
+  if (mode == 2)
+    return epi == QE_EPI_SWIGLU ? w4_stream_kernel<WARPS, U, V, QE_EPI_SWIGLU, 2>
+                                : w4_stream_kernel<WARPS, U, V, QE_EPI_NONE, 2>;
+  return epi == QE_EPI_SWIGLU ? w4_stream_kernel<WARPS, U, V, QE_EPI_SWIGLU, 0>
+                              : w4_stream_kernel<WARPS, U, V, QE_EPI_NONE, 0>;
+}
+template <int WARPS, int U>
+KernelFn pick_v(int v, int epi, int mode) {
+  // Flavours 2 and 3 are accepted at the boundary and served by flavour 0 (kept out of the
+  // build to bound the number of instantiations).
+  return v == 1 ? pick_tail<WARPS, U, 1>(epi, mode) : pick_tail<WARPS, U, 0>(epi, mode);
+}
+template <int WARPS>
+KernelFn pick_u(int u, int v, int epi, int mode) {
+  switch (u) {
+    case 1: return pick_v<WARPS, 1>(v, epi, mode);
+    case 2: return pick_v<WARPS, 2>(v, epi, mode);
+    default: return pick_v<WARPS, 4>(v, epi, mode);
+  }
+}
+KernelFn pick(int warps, int u, int v, int epi, int mode) {
+  switch (warps) {
+    case 4: return pick_u<4>(u, v, epi, mode);
+    case 16: return pick_u<16>(u, v, epi, mode);
+    default: return pick_u<8>(u, v, epi, mode);
+  }
+}
+
+int blocks_per_sm(KernelFn fn, int threads) {
+  static std::mutex mu;
+  static std::unordered_map<const void*, int> cache;
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = cache.find((const void*)fn);
+  if (it != cache.end()) return it->second;
+  int b = 1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, fn, threads, 0) != cudaSuccess) b = 1;
+  b = std::max(b, 1);
+  cache[(const void*)fn] = b;
+  return b;
+}
+
+struct Resolved {
+  qe_w4_plan plan;
+  KernelFn fn;
+};
+
+// Shape-only policy (never N). B200: 148 SMs; every matrix of the 27B model except the tiniest
+// runs as one persistent unit stream; small matrices (< 4096 units) use the (tile, ksplit) grid
+// so that a launch still covers every SM.
+Resolved resolve(const qe_w4_params& p, const qe_w4_cfg& in) {
+  Resolved r{};
+  qe_w4_cfg c = in;
+  const long tiles = p.Mp / 16, G = p.Kp / 128, units = tiles * G;
+  const int sms = qe_sm_count();
+  const int auto_mode = units < 4096 ? 0 : 2;
+  int mode = (c.mode == 0 || c.mode == 2) ? c.mode : auto_mode;
+  if (units >= (1L << 30)) mode = 0;  // 32-bit unit arithmetic in the stream mode
+  int warps = (c.warps == 4 || c.warps == 8 || c.warps == 16) ? c.warps : 8;
+  int unroll = (c.unroll == 1 || c.unroll == 2 || c.unroll == 4) ? c.unroll : 4;
+  const int variant = (c.variant >= 0 && c.variant <= 3) ? c.variant : 0;
+  r.fn = pick(warps, unroll, variant, p.epilogue, mode);
+  r.plan.mode = mode;
+  r.plan.threads = warps * 32;
+  r.plan.counters = tiles;
+  if (mode == 2) {
+    const int bps = c.blocks_per_sm > 0 ? c.blocks_per_sm : blocks_per_sm(r.fn, r.plan.threads);
+    const long per_block = (long)std::max(1, c.min_units) * warps;
+    const long blocks = std::max<long>(1, std::min<long>((long)sms * bps, (units + per_block - 1) / per_block));
+    r.plan.grid_x = (int)blocks;
+    r.plan.grid_y = 1;
+    r.plan.ws_floats = blocks * 2 * 128;
+  } else {
+    long ks = c.ksplit > 0 ? c.ksplit : qe_w4_auto_ksplit(p.Mp, p.Kp, p.N, warps);
+    ks = std::max<long>(1, std::min<long>(ks, G));
+    r.plan.grid_x = (int)tiles;
+    r.plan.grid_y = (int)ks;
+    r.plan.ws_floats = ks > 1 ? tiles * ks * 128 : 0;
+  }
+  return r;
+}
+
+}  // namespace
+}  // namespace qb
+
+using namespace qb;
+
+extern "C" void qe_w4_cfg_default(qe_w4_cfg* c) {
+  c->warps = 0; c->unroll = 0; c->ksplit = 0; c->pdl = 1; c->variant = 0; c->mode = -1;
+  c->blocks_per_sm = 0; c->min_units = 4;
+}
+
+extern "C" int qe_w4_auto_ksplit(int Mp, int Kp, int N, int warps) {
+  (void)N;  // never a function of the row count
+  if (warps <= 0) warps = 8;
+  const long tiles = Mp / 16, G = Kp / 128;
+  if (tiles * G >= 4096) return 1;
+  // Small matrix: cut K until the grid has about two CTAs per SM, keeping one group per warp.
+  const int want = 2 * qe_sm_count();
+  int ks = 1;
+  while (tiles * ks < want && G / (ks * 2) >= warps) ks *= 2;
+  return ks;
+}
+
+extern "C" int qe_w4_plan_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, qe_w4_plan* plan) {
+  if (!p || !cfg || !plan) return QE_ERR_ARG;
+  if (p->Mp <= 0 || p->Kp <= 0 || p->Mp % 16 || p->Kp % 128) return QE_ERR_ARG;
+  *plan = resolve(*p, *cfg).plan;
+  return 0;
+}
+
+extern "C" int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream) {
+  if (!p || !cfg) return QE_ERR_ARG;
+  if (p->N < 1 || p->N > QE_MAX_ROWS || p->Mp % 16 || p->Kp % 128 || p->Mp <= 0 || p->Kp <= 0)
+    return QE_ERR_ARG;
+  if (p->K > p->Kp || p->K <= 0 || p->M <= 0) return QE_ERR_ARG;
+  if (p->epilogue == QE_EPI_SWIGLU ? p->M > p->Mp / 2 : p->M > p->Mp) return QE_ERR_ARG;
+  const Resolved r = resolve(*p, *cfg);
+  W4Args a{};
+  a.qw = reinterpret_cast<const uint4*>(p->qw);
+  a.scales = reinterpret_cast<const __half*>(p->scales);
+  a.x = reinterpret_cast<const bf16*>(p->x);
+  a.out = reinterpret_cast<bf16*>(p->out);
+  a.ws = p->ws;
+  a.counters = p->counters;
+  a.M = p->M; a.K = p->K; a.N = p->N;
+  a.tiles = p->Mp / 16; a.G = p->Kp / 128;
+  a.ldx = p->ldx; a.ldo = p->ldo;
+  a.ksplit = r.plan.grid_y;
+  a.total = a.tiles * a.G;
+  const bool pdl = cfg->pdl && pdl_launch_enabled() && pdl_trigger_enabled();
+  return (int)launch(r.fn, dim3(r.plan.grid_x, r.plan.grid_y, 1), dim3(r.plan.threads), 0,
+                     (cudaStream_t)stream, pdl, a);
+}
