@@ -1,0 +1,398 @@
+"""Benchmark of the batch-1 decode path on B200: 27B-shape W4A16 model, random-init weights,
+128-token seeded prompt, 1,024 greedy tokens per step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One JSON line on stdout (rank 0). `value` = decode tokens per second (plain greedy, inputs
+resident on the device, CUDA-event time of the decode replays); `e2e` = the same through
+Engine.generate() with the prompt coming from host memory and the tokens read back to the host,
+prefill included; `roofline` = the W4 GEMV kernel timed alone on this model's own matrices in
+token order (every matrix distinct, 13 GB, far larger than L2) against the measured HBM copy
+bandwidth; `mtp_k4` = speculative decoding with k = 4 at forced acceptance lengths 0..4 and natural
+acceptance; `cpu_baseline` = the CPU oracle (port of the reference torch path) timed on a bounded
+sample on the host cores.
+
+--impl reference times that CPU port as an arm of its own (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PROMPT_LEN, N_NEW = 128, 1024
+FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of w4_stream_kernel, from the ncu
+# capture summarised in profiles/ (None until a capture exists for the current kernel).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peak():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons during the timed region (read-only query)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.idx)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in Path(self.path).read_text().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            # under load = the upper half of the samples (idle gaps between steps clock down)
+            sm.sort()
+            out["sm_mhz"] = statistics.median(sm[len(sm) // 2:])
+            out["sm_max_mhz"] = max(mx)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the oracle (port of the reference torch path) on a bounded sample of the workload
+# ----------------------------------------------------------------------------------------------
+def cpu_reference_sample(steps: int, warmup: int, head_frac: int = 8):
+    """One step = one token through one DeltaNet layer, one attention layer and 1/head_frac of the
+    lm_head of the 27B shape, on dense fp32 dequantised weights; per-token time of the whole model
+    = 48 t_gdn + 16 t_attn + head_frac t_head. Returns (tok_s, cores, description)."""
+    import torch
+    sys.path.insert(0, str(ROOT / "tests"))
+    from oracle import model as OM
+    from qengine_b200 import synth
+    from util import dequant_oracle, oracle_config
+
+    cfg = synth.qwen27b_config(layers=4)  # layers 0..2 DeltaNet, 3 attention: one of each is used
+    ocfg = oracle_config(cfg)
+    S = synth._Seeds(0, "cpu")
+
+    def dense(L):
+        D = {k: v for k, v in L.items() if not hasattr(v, "qw")}
+        for k in ("in_proj", "out", "down"):
+            D[k] = dequant_oracle(L[k])
+        D["gate"], D["up"] = dequant_oracle(L["gate_up"])
+        return D
+
+    Lg = dense(synth._layer(cfg, "linear_attention", S, 0.01))
+    La = dense(synth._layer(cfg, "full_attention", S, 0.01))
+    head = dequant_oracle(synth.random_w4(cfg.vocab // head_frac, cfg.hidden, S.gen(), "cpu", 0.01))
+    st = OM.State(ocfg, 256, with_mtp=False)
+    g = torch.Generator().manual_seed(3)
+    h = torch.randn(cfg.hidden, generator=g).to(torch.bfloat16)
+    tg, ta, th = [], [], []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        OM.decoder_layer(h, Lg, st, 0, i, ocfg)
+        t1 = time.perf_counter()
+        OM.decoder_layer(h, La, st, 3, i, ocfg)
+        t2 = time.perf_counter()
+        OM.lin(h, head)
+        t3 = time.perf_counter()
+        if i >= warmup:
+            tg.append(t1 - t0); ta.append(t2 - t1); th.append(t3 - t2)
+    per_tok = 48 * statistics.mean(tg) + 16 * statistics.mean(ta) + head_frac * statistics.mean(th)
+    desc = (f"{steps} tokens through 1 DeltaNet layer + 1 attention layer + 1/{head_frac} of the lm_head at the "
+            f"27B shape (dense fp32 dequantised weights), scaled to 48 + 16 layers + full head")
+    return 1.0 / per_tok, torch.get_num_threads(), desc, per_tok
+
+
+def run_reference_arm(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tok_s, cores, desc, per_tok = cpu_reference_sample(max(1, a.steps), max(1, a.warmup))
+    line = {
+        "impl": "reference", "metric": "batch-1 decode tok/s (plain)", "value": tok_s, "unit": "tok/s",
+        "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": per_tok * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "27B-shape W4A16 plain greedy decode, 128-token prompt, 1,024 tokens",
+                   "timing": "host wall clock, CPU only"},
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def w4_sequence_timing(eng, n_rows, reps=10):
+    """Every W4 GEMV of one token (all layers in order, then the lm_head) as one CUDA graph on the
+    model's own weights: the dominant kernel timed alone, in situ shapes, nothing reused in L2.
+    Returns (ms per token, launches, algorithmic bytes)."""
+    import torch
+    cfg = eng.cfg
+    lin = eng.linear
+    H = cfg.hidden
+    xs = {k: torch.randn(n_rows, k, device=eng.dev).to(torch.bfloat16) for k in
+          {H, cfg.value_dim, cfg.hq * cfg.head_dim, cfg.inter}}
+    outs, plan, nbytes = {}, [], 0
+    for L in eng.layers:
+        for key in ("in_proj", "out", "gate_up", "down"):
+            p = L[key]
+            outs.setdefault(p.M, torch.empty(n_rows, p.M, device=eng.dev, dtype=torch.bfloat16))
+            plan.append(p)
+            nbytes += p.nbytes + n_rows * (p.K + p.M) * 2
+    p = eng.lm_head
+    outs.setdefault(p.M, torch.empty(n_rows, p.M, device=eng.dev, dtype=torch.bfloat16))
+    plan.append(p)
+    nbytes += p.nbytes + n_rows * (p.K + p.M) * 2
+
+    def body():
+        for p in plan:
+            (lin.gate_up if p.gate_up else lin)(xs[p.K], p, outs[p.M])
+
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        body()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        body()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    ms = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    return statistics.median(ms), len(plan), nbytes
+
+
+def mlp_pair_timing(eng, n_rows, reps=20):
+    """W4 microbench: fused gate/up (5120 -> 2 x 17408, SwiGLU) then down (17408 -> 5120), rotating
+    over the layers' distinct weights so L2 cannot hold them. Returns (us per pair, GB/s)."""
+    import torch
+    cfg, lin = eng.cfg, eng.linear
+    x = torch.randn(n_rows, cfg.hidden, device=eng.dev).to(torch.bfloat16)
+    act = torch.empty(n_rows, cfg.inter, device=eng.dev, dtype=torch.bfloat16)
+    out = torch.empty(n_rows, cfg.hidden, device=eng.dev, dtype=torch.bfloat16)
+    Ls = eng.layers
+    nbytes = Ls[0]["gate_up"].nbytes + Ls[0]["down"].nbytes + n_rows * (cfg.hidden * 2 + cfg.inter * 2) * 2
+
+    def body():
+        for L in Ls:
+            lin.gate_up(x, L["gate_up"], act)
+            lin(act, L["down"], out)
+
+    body()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        body()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    ms = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    us = statistics.median(ms) * 1e3 / len(Ls)
+    return us, nbytes / (us * 1e-6) / 1e9
+
+
+def bytes_per_token(eng, mean_ctx):
+    """Algorithmic HBM bytes of one plain decode step at context length mean_ctx."""
+    from qengine_b200 import synth
+    cfg = eng.cfg
+    pb = synth.packed_bytes({"layers": eng.layers, "lm_head": eng.lm_head, "mtp": eng.mtp})
+    n_gdn = sum(t == "linear_attention" for t in cfg.layer_types)
+    n_att = cfg.layers - n_gdn
+    state = n_gdn * 2 * cfg.hv * cfg.dk * cfg.dv * 4
+    staged = n_gdn * 2 * (cfg.hv * (cfg.dk + cfg.dv + 2)) * 4
+    norms = (2 * cfg.layers + 1) * cfg.hidden * 2
+    kv_row = n_att * 2 * cfg.hkv * cfg.head_dim * 2
+    total = pb["decoder"] + pb["lm_head"] + state + staged + norms + cfg.hidden * 2 + kv_row * mean_ctx + kv_row
+    return total, pb
+
+
+def run_ours(a):
+    import torch
+    import torch.distributed as dist
+    from qengine_b200 import synth
+    from qengine_b200.engine import Engine
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    cfg = synth.qwen27b_config(layers=a.layers)
+    n_new, P = a.tokens, PROMPT_LEN
+    W = synth.build_model(cfg, seed=1, device=dev, scale_std=0.01)
+    eng = Engine(cfg, W, max_len=P + n_new + 32, device=dev)
+    prompt = synth.prompt_ids(P, cfg.vocab, seed=1234 + (rank if world > 1 else 0))
+
+    # ---- warm-up (captures the graphs) and timed plain decode ------------------------------
+    for _ in range(max(1, a.warmup)):
+        eng.generate(prompt, n_new)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    dec_s, e2e_s = [], []
+    for _ in range(a.steps):
+        t0 = time.perf_counter()
+        gen, _, d = eng.generate(prompt, n_new, timing=True)   # host prompt in, host tokens out
+        e2e_s.append(time.perf_counter() - t0)
+        dec_s.append(d)
+    barrier()
+    clocks = sampler.stop()
+    t_dec = torch.tensor([sum(dec_s), sum(e2e_s)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_dec, op=dist.ReduceOp.MAX)
+    dec_total, e2e_total = t_dec.tolist()
+    tokens_all = world * a.steps * (n_new - 1)
+    value = tokens_all / dec_total
+    e2e = world * a.steps * n_new / e2e_total
+    kernels_per_token = eng.graph_kernels[(1, False, 0, False)]
+    launches = a.steps * ((n_new - 1) * kernels_per_token +
+                          sum(eng.graph_kernels[k] for k in eng._prefill_keys(P, False, 0)) * (P // 8))
+
+    line = {}
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        B_tok, pb = bytes_per_token(eng, P + n_new / 2)
+        ms_tok = dec_total / (a.steps * (n_new - 1)) * 1e3
+        # dominant kernel alone, in situ
+        seq_ms, seq_launches, seq_bytes = w4_sequence_timing(eng, 1)
+        seq5_ms, _, _ = w4_sequence_timing(eng, 5)
+        pair1_us, pair1_gbs = mlp_pair_timing(eng, 1)
+        pair5_us, pair5_gbs = mlp_pair_timing(eng, 5)
+        achieved = seq_bytes / (seq_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                    "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": f"of {peak_kind}",
+                    "kernel": "w4_stream_kernel",
+                    "how": f"{seq_launches} launches (every W4 matrix of one token, in order) as one graph, "
+                           f"median of 10 CUDA-event timings; bytes = packed weights + scales + x + out"}
+        # ---- MTP k = 4 ---------------------------------------------------------------------
+        mtp = {}
+        if not a.no_mtp:
+            truth = prompt + gen + [0] * 64
+            for label, fa in [("natural", None)] + [(f"a{i}", i) for i in range(5)]:
+                kw = dict(force_accept=fa, truth=truth) if fa is not None else {}
+                eng.generate_spec(prompt, n_new, 4, **kw)  # capture + warm
+                out, _, d, st = eng.generate_spec(prompt, n_new, 4, timing=True, **kw)
+                mtp[label] = {"tok_s": (n_new - 1) / d, "tokens_per_cycle": st["tokens_per_cycle"],
+                              "ms_per_cycle": d * 1e3 / max(1, st["cycles"]), "identical_to_plain": out == gen}
+            mtp["verify_cost_vs_plain_step"] = None
+        cpu = None
+        if world == 1 and not a.no_cpu:
+            tok_s, cores, desc, _ = cpu_reference_sample(3, 1)
+            cpu = {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": desc}
+        line = {
+            "metric": "batch-1 decode tok/s (plain)", "value": value, "unit": "tok/s", "n_gpus": world,
+            "steps": a.steps, "warmup": a.warmup, "ms_per_step": dec_total / a.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"27B-shape W4A16 plain greedy decode ({cfg.layers} layers, hidden 5120, vocab "
+                                   f"248320), {P}-token seeded prompt, {n_new} tokens per step",
+                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                       "l2": "inputs larger than L2 (13 GB of weights streamed per token)",
+                       "timing": "CUDA events around the decode graph replays, max over ranks"},
+            "ms_per_token": ms_tok,
+            "hbm_roofline": {"bytes_per_token": B_tok, "tok_s_at_measured_peak": peak * 1e9 / B_tok,
+                             "frac_of_measured": value / world / (peak * 1e9 / B_tok),
+                             "tok_s_at_8TBs": 8e12 / B_tok, "frac_of_8TBs": value / world / (8e12 / B_tok)},
+            "roofline": roofline,
+            "w4_sequence": {"ms_n1": seq_ms, "ms_n5": seq5_ms, "bytes": seq_bytes, "launches": seq_launches},
+            "w4_mlp_pair": {"us_m1": pair1_us, "gbs_m1": pair1_gbs, "us_m5": pair5_us, "gbs_m5": pair5_gbs},
+            "mtp_k4": mtp,
+            "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": (P // 8) * 36 + 8,
+                    "d2h_bytes_per_step": n_new * 4},
+            "gpu_launches": launches,
+            "kernels_per_token": kernels_per_token,
+            "clocks": clocks,
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=64, help="model depth (64 = the 27B shape)")
+    ap.add_argument("--tokens", type=int, default=N_NEW, help="generated tokens per step")
+    ap.add_argument("--no-mtp", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        run_reference_arm(a)
+    else:
+        run_ours(a)
+
+
+if __name__ == "__main__":
+    main()

@@ -105,7 +105,7 @@ def argmax(x, ws_v, ws_i, out, idmap=None):
         _req(idmap.numel() == xw, "idmap size")
         mp = idmap.data_ptr()
     check(lib.qe_argmax(x.data_ptr(), xn, xw, xld, ws_v.data_ptr(), ws_i.data_ptr(), nb,
-                        out.data_ptr(), mp, _stream()), "argmax")
+                        out.data_ptr(), mp, _stream()), "argmax", kernels=2)
 
 
 def accept(in_tok, am, n, ctl, next_tok, log):
@@ -230,7 +230,7 @@ def attn_decode(q, kc, vc, pos, qg, part_o, part_ml, out):
          "part_ml / out / qg shapes")
     check(lib.qe_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), qg.data_ptr(),
                              gld, part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(), old, n, Hq,
-                             Hkv, hd, max_len, NS, float(hd) ** -0.5, _stream()), "attn_decode")
+                             Hkv, hd, max_len, NS, float(hd) ** -0.5, _stream()), "attn_decode", kernels=2)
 
 
 def l2_persist_limit(nbytes):

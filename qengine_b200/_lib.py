@@ -84,9 +84,15 @@ def load() -> C.CDLL:
 lib = load()
 
 
-def check(code: int, what: str) -> None:
+# Number of kernels this process has enqueued through the wrappers (eagerly or into a graph being
+# captured). The engine reads it around a capture to know how many kernel nodes a graph holds.
+launches = [0]
+
+
+def check(code: int, what: str, kernels: int = 1) -> None:
     """Turn a launcher's return code into RuntimeError (the reference throws via TORCH_CHECK)."""
     if code == 0:
+        launches[0] += kernels
         return
     if code == -22:
         raise RuntimeError(f"{what}: argument not supported by the kernels")

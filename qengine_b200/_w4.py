@@ -19,7 +19,7 @@ import ctypes as C
 
 import torch
 
-from ._lib import W4Cfg, W4Params, W4Plan, check, lib
+from ._lib import W4Cfg, W4Params, W4Plan, check, launches, lib
 
 EPI_NONE, EPI_SWIGLU = 0, 1
 _MIN_WS_FLOATS, _MIN_COUNTERS = 1 << 18, 1 << 14
@@ -90,11 +90,12 @@ def _run(x, qw, scales, out, M, epilogue, warps, unroll, ksplit, pdl, variant, m
     cfg = W4Cfg(int(warps), int(unroll), int(ksplit), int(bool(pdl)), int(variant), int(mode),
                 int(bps), int(min_units))
     plan = W4Plan()
-    check(lib.qe_w4_plan_gemv(C.byref(p), C.byref(cfg), C.byref(plan)), "gemv_w4 plan")
+    check(lib.qe_w4_plan_gemv(C.byref(p), C.byref(cfg), C.byref(plan)), "gemv_w4 plan", kernels=0)
     W = _workspace(x.device, plan.ws_floats, plan.counters)
     p.ws, p.counters = W.ws.data_ptr(), W.counters.data_ptr()
     code = lib.qe_w4_gemv(C.byref(p), C.byref(cfg), torch.cuda.current_stream().cuda_stream)
     _req(code == 0, f"gemv_w4 launch failed: CUDA error {code}")
+    launches[0] += 1
 
 
 def gemv(x, qw, scales, out, M, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,

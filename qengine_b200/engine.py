@@ -25,6 +25,7 @@ from __future__ import annotations
 import torch
 
 from . import _C
+from ._lib import launches
 from .quant import W4Packed
 from .synth import Config
 
@@ -103,6 +104,7 @@ class Engine:
             self._build_draft_head(draft_vocab)
         self._alloc()
         self.graphs = {}
+        self.graph_kernels = {}  # kernels of this library per captured graph
         self.force_a = -1      # forced acceptance length for verify passes (< 0: off)
         self.truth = torch.zeros(1, dtype=I32, device=self.dev)
         _C.set_gdn_early(True)  # safe here: passes start with a fully ordered kernel (see _main)
@@ -262,10 +264,12 @@ class Engine:
             torch.cuda.current_stream().wait_stream(s)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
+            before = launches[0]
             with torch.cuda.graph(g):
                 self._pass(n, mtp_rows, k, force)
             torch.cuda.synchronize()
             self.graphs[key] = g
+            self.graph_kernels[key] = launches[0] - before
         return self.graphs[key]
 
     # ------------------------------------------------------------------------------------------

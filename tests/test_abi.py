@@ -1,0 +1,53 @@
+"""The C ABI: the shared library loads and exports every symbol include/qengine_b200.h declares,
+and the ctypes signature table covers exactly those symbols. No compute calls (CPU only)."""
+from __future__ import annotations
+
+import ctypes
+import re
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _declared():
+    text = (ROOT / "include" / "qengine_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(qe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from qengine_b200 import _lib
+    names = _declared()
+    assert len(names) >= 24
+    lib = ctypes.CDLL(str(_lib.LIB_PATH))
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+    assert sorted(_lib.SIGNATURES) == names, "ctypes signature table and header disagree"
+
+
+def test_struct_layouts_match_header():
+    """Field order of the ctypes mirrors follows the header's struct definitions."""
+    from qengine_b200 import _lib
+    text = (ROOT / "include" / "qengine_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+
+    def fields(name):
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (name, name), text, flags=re.S).group(1)
+        out = []
+        for decl in body.split(";"):
+            decl = decl.strip()
+            if not decl:
+                continue
+            out += [re.sub(r"[\s\*]", "", v) for v in decl.split(",")][0:1] and \
+                   [re.sub(r"^.*[\s\*]", "", v.strip()) for v in decl.split(",")]
+        return out
+
+    assert fields("qe_w4_params") == [f[0] for f in _lib.W4Params._fields_]
+    assert fields("qe_w4_cfg") == [f[0] for f in _lib.W4Cfg._fields_]
+    assert fields("qe_w4_plan") == [f[0] for f in _lib.W4Plan._fields_]
+
+
+def test_abi_version_and_plan_without_gpu():
+    from qengine_b200 import _lib
+    assert _lib.lib.qe_abi_version() == 1
+    assert _lib.lib.qe_w4_auto_ksplit(5120, 17408, 1, 8) == 1

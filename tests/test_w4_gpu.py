@@ -1,0 +1,279 @@
+"""W4A16 GEMV (qe_w4_gemv through `_w4`) against fp32 x @ dequantised(W)^T.
+
+Per-element tolerance, with S = |x| @ |W~|^T in fp32 (the reference's own bound,
+tests/test_gemv_w4.py:1-18 of the reference):
+    |out - ref| <= 2^-8 |ref| + K 2^-24 S
+(one bf16 rounding of the output plus reordering of K exact fp32 products), and at least 90 % of
+the outputs must be bit-identical to bf16(fp32 reference). On top of the value checks: bitwise
+repeatability, and row r of an N-row call bit-identical to the 1-row call, in every launch
+configuration the boundary accepts.
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+H, I, V = 5120, 17408, 248320
+SHAPES_27B = {
+    "gdn.in_proj_qkv": (10240, H), "gdn.in_proj_z": (6144, H), "gdn.in_proj_a/b": (48, H),
+    "gdn.in_proj_fused": (16480, H), "gdn.out_proj": (H, 6144), "attn.q_proj": (12288, H),
+    "attn.k/v_proj": (1024, H), "attn.in_proj_fused": (14336, H), "attn.o_proj": (H, 6144),
+    "mlp.gate/up_proj": (I, H), "mlp.down_proj": (H, I), "lm_head": (V, H), "mtp.fc": (H, 2 * H),
+}
+ODD_SHAPES = [(1, 1), (1, 128), (7, 127), (16, 129), (127, 1000), (1000, 4097), (33, 32768), (4097, 7),
+              (17, 255), (100, 136)]
+CFGS = [dict(), dict(warps=4), dict(warps=16), dict(unroll=1), dict(unroll=4), dict(warps=16, unroll=1),
+        dict(mode=0), dict(mode=0, ksplit=2), dict(mode=0, ksplit=7), dict(mode=2), dict(mode=2, min_units=1),
+        dict(mode=2, warps=4, unroll=1), dict(variant=1), dict(pdl=False)]
+
+
+@pytest.fixture(scope="module")
+def api():
+    from qengine_b200 import _w4
+    from qengine_b200.quant import dequantize_w4, gemv, quantize_w4, quantize_w4_gate_up
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return dict(w4=_w4, deq=dequantize_w4, gemv=gemv, q=quantize_w4, qgu=quantize_w4_gate_up)
+
+
+def rand_w(M, K, scale=0.02, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(M, K, generator=g, device=DEV) * scale).to(torch.bfloat16)
+
+
+def rand_x(N, K, seed=1):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return torch.randn(N, K, generator=g, device=DEV).to(torch.bfloat16)
+
+
+def bound(x, Wd, ref):
+    return 2.0 ** -8 * ref.abs() + x.shape[1] * 2.0 ** -24 * (x.float().abs() @ Wd.abs().T)
+
+
+def check(out, ref, bnd, what):
+    o = out.float()
+    assert torch.equal(torch.isnan(o), torch.isnan(ref)), f"{what}: NaN pattern differs"
+    inf = torch.isinf(ref)
+    assert torch.equal(torch.isinf(o), inf), f"{what}: inf pattern differs"
+    assert torch.equal(o[inf], ref[inf]), f"{what}: inf sign differs"
+    fin = ~(torch.isnan(ref) | inf)
+    err = (o - ref).abs()[fin]
+    bad = err > bnd[fin]
+    assert not bad.any(), f"{what}: {int(bad.sum())} elements over bound, worst {err.max().item():.3e}"
+    if fin.sum() >= 8:
+        exact = (o[fin] == ref[fin].to(torch.bfloat16).float()).float().mean().item()
+        assert exact >= 0.9, f"{what}: only {exact:.3f} of outputs equal bf16(reference)"
+
+
+def bits(t):
+    return t.view(torch.int16).clone()
+
+
+def test_product_dequantiser_matches_oracle_dequantiser(api):
+    from util import dequant_oracle
+    p = api["q"](rand_w(100, 300, seed=2))
+    assert torch.equal(api["deq"](p).cpu(), dequant_oracle(p))
+    pg = api["qgu"](rand_w(21, 200, seed=3), rand_w(21, 200, seed=4))
+    g, u = api["deq"](pg)
+    og, ou = dequant_oracle(pg)
+    assert torch.equal(g.cpu(), og) and torch.equal(u.cpu(), ou)
+
+
+@pytest.mark.parametrize("name", list(SHAPES_27B))
+def test_27b_shapes_all_row_counts(api, name):
+    M, K = SHAPES_27B[name]
+    p = api["q"](rand_w(M, K, seed=5))
+    Wd = api["deq"](p)
+    x = rand_x(8, K, seed=6)
+    ref = x.float() @ Wd.T
+    bnd = bound(x, Wd, ref)
+    for N in range(1, 9):
+        check(api["gemv"](x[:N].contiguous(), p), ref[:N], bnd[:N], f"{name} N={N}")
+
+
+@pytest.mark.parametrize("M,K", ODD_SHAPES)
+def test_odd_shapes(api, M, K):
+    p = api["q"](rand_w(M, K, seed=7))
+    Wd = api["deq"](p)
+    x = rand_x(8, K, seed=8)
+    for N in range(1, 9):
+        ref = x[:N].float() @ Wd.T
+        check(api["gemv"](x[:N].contiguous(), p), ref, bound(x[:N], Wd, ref), f"{M}x{K} N={N}")
+
+
+@pytest.mark.parametrize("mode,ksplit,min_units", [(0, 1, 4), (0, 2, 4), (0, 3, 4), (0, 7, 4), (0, 40, 4),
+                                                  (2, 0, 1), (2, 0, 4), (-1, 0, 4)])
+@pytest.mark.parametrize("warps,unroll", [(4, 1), (8, 2), (8, 4), (16, 1)])
+def test_launch_configs(api, mode, ksplit, min_units, warps, unroll):
+    p = api["q"](rand_w(1000, 5120, seed=9))
+    Wd = api["deq"](p)
+    x = rand_x(5, 5120, seed=10)
+    ref = x.float() @ Wd.T
+    for variant in range(4):
+        for pdl in (False, True):
+            out = api["gemv"](x, p, ksplit=ksplit, warps=warps, unroll=unroll, variant=variant, pdl=pdl,
+                              mode=mode, min_units=min_units)
+            check(out, ref, bound(x, Wd, ref), f"mode={mode} ks={ksplit} w={warps} u={unroll} v={variant}")
+
+
+@pytest.mark.parametrize("kw", [dict(mode=0, ksplit=16), dict(mode=2, min_units=1)])
+def test_partial_sum_scratch_left_clean(api, kw):
+    """The arrival counters must be zero again after every call: repeated calls agree."""
+    p = api["q"](rand_w(64, 8192, seed=11))
+    Wd = api["deq"](p)
+    x = rand_x(3, 8192, seed=12)
+    ref = x.float() @ Wd.T
+    for _ in range(20):
+        check(api["gemv"](x, p, **kw), ref, bound(x, Wd, ref), f"repeat {kw}")
+
+
+def test_cuda_graph_replay(api):
+    p = api["q"](rand_w(1024, 5120, seed=13))
+    Wd = api["deq"](p)
+    x = rand_x(2, 5120, seed=14)
+    out = torch.empty(2, 1024, dtype=torch.bfloat16, device=DEV)
+    for kw in (dict(mode=0, ksplit=8), dict(mode=2, min_units=1), dict()):
+        api["gemv"](x, p, out, **kw)  # sizes the scratch outside capture
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        api["gemv"](x, p, out, mode=0, ksplit=8)
+        api["gemv"](x, p, out, mode=2, min_units=1)
+        api["gemv"](x, p, out)
+    for seed in range(3):
+        x.copy_(rand_x(2, 5120, seed=100 + seed))
+        out.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        ref = x.float() @ Wd.T
+        check(out, ref, bound(x, Wd, ref), f"graph replay {seed}")
+
+
+@pytest.mark.parametrize("Iw,K", [(I, H), (37, 200), (8, 128), (1000, 4097)])
+def test_swiglu_epilogue(api, Iw, K):
+    p = api["qgu"](rand_w(Iw, K, seed=15), rand_w(Iw, K, seed=16))
+    gd, ud = api["deq"](p)
+    x = rand_x(8, K, seed=17)
+    for N in range(1, 9):
+        xs = x[:N].contiguous()
+        g, u = xs.float() @ gd.T, xs.float() @ ud.T
+        ref = torch.nn.functional.silu(g) * u
+        kb = K * 2.0 ** -24
+        eg, eu = kb * (xs.float().abs() @ gd.abs().T), kb * (xs.float().abs() @ ud.abs().T)
+        bnd = 2.0 ** -8 * ref.abs() + 1.1 * u.abs() * eg + torch.nn.functional.silu(g).abs() * eu + 1e-30
+        out = api["gemv"](xs, p)
+        assert out.shape == (N, Iw)
+        check(out, ref, bnd, f"swiglu {Iw}x{K} N={N}")
+
+
+def test_nan_inf_rows(api):
+    p = api["q"](rand_w(300, 1000, seed=18))
+    Wd = api["deq"](p)
+    x = rand_x(4, 1000, seed=19)
+    x[1, 17] = float("nan")
+    x[2, 900] = float("inf")
+    x[3, 5], x[3, 6] = float("-inf"), float("inf")
+    ref = x.float() @ Wd.T
+    out = api["gemv"](x, p)
+    check(out, ref, bound(x, Wd, ref).nan_to_num(posinf=0.0), "nan/inf")
+    assert torch.isnan(out[1]).all() and not torch.isnan(out[0]).any()
+
+
+@pytest.mark.parametrize("mag", [1e-30, 1e-4, 1e4, 1e30])
+def test_extreme_magnitudes(api, mag):
+    p = api["q"](rand_w(256, 2048, seed=20))
+    Wd = api["deq"](p)
+    x = (rand_x(3, 2048, seed=21).float() * mag).to(torch.bfloat16)
+    ref = x.float() @ Wd.T
+    check(api["gemv"](x, p), ref, bound(x, Wd, ref), f"mag {mag}")
+
+
+def test_weight_extremes(api):
+    W = rand_w(64, 1024, seed=22).float()
+    W[0] *= 1e3
+    W[1] *= 1e-3
+    W[2, :128] = 0
+    W[3, 5] = 50.0
+    p = api["q"](W.to(torch.bfloat16))
+    Wd = api["deq"](p)
+    x = rand_x(2, 1024, seed=23)
+    ref = x.float() @ Wd.T
+    check(api["gemv"](x, p), ref, bound(x, Wd, ref), "weight extremes")
+
+
+@pytest.mark.parametrize("pad,offset", [(64, 0), (3, 0), (0, 1), (8, 3)])
+def test_strided_and_misaligned_views(api, pad, offset):
+    M, K = 500, 1024
+    p = api["q"](rand_w(M, K, seed=24))
+    Wd = api["deq"](p)
+    big = rand_x(4, K + pad + offset, seed=25)
+    x = big[:, offset:offset + K]
+    obig = torch.full((4, M + 40), 7.0, dtype=torch.bfloat16, device=DEV)
+    out = obig[:, 8:8 + M]
+    api["gemv"](x, p, out)
+    ref = x.float() @ Wd.T
+    check(out, ref, bound(x, Wd, ref), f"strided pad={pad} off={offset}")
+    assert (obig[:, :8] == 7).all() and (obig[:, 8 + M:] == 7).all(), "wrote outside the out view"
+
+
+def test_rejects_bad_inputs(api):
+    p = api["q"](rand_w(32, 256))
+    w4 = api["w4"]
+    o1 = torch.empty(1, 32, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError):
+        w4.gemv(rand_x(1, 256).half(), p.qw, p.scales, o1, 32)
+    with pytest.raises(RuntimeError):
+        w4.gemv(rand_x(9, 256), p.qw, p.scales, torch.empty(9, 32, dtype=torch.bfloat16, device=DEV), 32)
+    with pytest.raises(RuntimeError):
+        w4.gemv(rand_x(1, 384), p.qw, p.scales, o1, 32)
+    with pytest.raises(RuntimeError):
+        w4.gemv(rand_x(1, 256), p.qw, p.scales, o1, 32, warps=3)
+
+
+@pytest.mark.parametrize("M,K", [(5120, 17408), (1024, 5120), (1000, 4097), (16480, 5120)])
+def test_bitwise_repeatable(api, M, K):
+    p = api["q"](rand_w(M, K, seed=30))
+    x = rand_x(8, K, seed=31)
+    out = torch.empty(8, M, dtype=torch.bfloat16, device=DEV)
+    for kw in CFGS:
+        api["gemv"](x, p, out, **kw)
+        first = bits(out)
+        for _ in range(30):
+            out.fill_(0)
+            api["gemv"](x, p, out, **kw)
+            assert torch.equal(bits(out), first), f"{M}x{K} {kw}: run differs bitwise"
+
+
+@pytest.mark.parametrize("M,K", [(5120, 17408), (1024, 5120), (127, 1000), (16480, 5120)])
+def test_row_independent_of_row_count(api, M, K):
+    p = api["q"](rand_w(M, K, seed=32))
+    x = rand_x(8, K, seed=33)
+    for kw in CFGS:
+        single = [bits(api["gemv"](x[r:r + 1].contiguous(), p, **kw)) for r in range(8)]
+        for N in range(2, 9):
+            out = api["gemv"](x[:N].contiguous(), p, **kw)
+            for r in range(N):
+                assert torch.equal(bits(out[r:r + 1]), single[r]), f"{M}x{K} {kw} N={N} row {r}"
+
+
+def test_swiglu_bitwise_and_row_independent(api):
+    p = api["qgu"](rand_w(I, H, seed=34), rand_w(I, H, seed=35))
+    x = rand_x(8, H, seed=36)
+    for kw in CFGS:
+        full = bits(api["gemv"](x, p, **kw))
+        for _ in range(5):
+            assert torch.equal(bits(api["gemv"](x, p, **kw)), full), f"swiglu {kw} repeat"
+        for r in range(8):
+            assert torch.equal(bits(api["gemv"](x[r:r + 1].contiguous(), p, **kw)), full[r:r + 1]), \
+                f"swiglu {kw} row {r}"
+
+
+def test_linearity_at_full_size(api):
+    """Size-independent property on the full lm_head shape: the kernel is linear in x up to the
+    output rounding: gemv(2 x) == 2 gemv(x) bit for bit (scaling by 2 is exact in bf16/fp32)."""
+    p = api["q"](rand_w(V, H, seed=40))
+    x = rand_x(2, H, seed=41)
+    a = api["gemv"](x, p).float()
+    b = api["gemv"]((x.float() * 2).to(torch.bfloat16), p).float()
+    assert torch.equal(a * 2, b)
