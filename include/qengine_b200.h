@@ -167,7 +167,8 @@ typedef struct qe_w4_cfg {
   int ksplit;        /* mode 0: blocks along K; 0 = auto */
   int pdl;           /* launch with programmatic stream serialization */
   int variant;       /* load flavour, 0..3 (see w4_stream.cu) */
-  int mode;          /* -1 auto, 0 = (tile, ksplit) grid, 2 = persistent unit stream */
+  int mode;          /* -1 auto, 0 = (tile, ksplit) grid, 2 = persistent unit stream,
+                        3 = unit stream through a shared-memory ring fed by bulk copies */
   int blocks_per_sm; /* mode 2: 0 = auto */
   int min_units;     /* mode 2: minimum 1-KB units per warp */
 } qe_w4_cfg;
@@ -187,6 +188,10 @@ int qe_w4_plan_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, qe_w4_plan* pla
 int qe_w4_auto_ksplit(int Mp, int Kp, int N, int warps);
 /* Replaces launch_gemv_w4 (gemv_w4.h:56). */
 int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
+/* Mode 3 (shared-memory ring fed by bulk copies) bounds every barrier wait; this returns the
+ * sticky error word those waits set on expiry (0 = none). Synchronises with the device. No
+ * counterpart in the reference. */
+int qe_w4_ring_error(void);
 
 #ifdef __cplusplus
 }

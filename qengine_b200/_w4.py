@@ -83,7 +83,7 @@ def _run(x, qw, scales, out, M, epilogue, warps, unroll, ksplit, pdl, variant, m
     _req(x.data_ptr() != out.data_ptr(), "in-place not supported")
     _req(warps in (0, 4, 8, 16), "warps in {0 (auto),4,8,16}")
     _req(unroll in (0, 1, 2, 4), "unroll in {0 (auto),1,2,4}")
-    _req(mode in (-1, 0, 2), "mode in {-1 (auto), 0, 2}")
+    _req(mode in (-1, 0, 2, 3), "mode in {-1 (auto), 0, 2, 3}")
 
     p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None,
                  M, K, Mp, Kp, N, x.stride(0), out.stride(0), epilogue)
@@ -114,3 +114,8 @@ def gemv_swiglu(x, qw, scales, out, I, warps=0, unroll=0, ksplit=0, pdl=True, va
 
 def auto_ksplit(Mp, Kp, N, warps=8):
     return int(lib.qe_w4_auto_ksplit(int(Mp), int(Kp), int(N), int(warps)))
+
+
+def ring_error():
+    """Sticky error word of mode 3's bounded barrier waits (0 = none); synchronises."""
+    return int(lib.qe_w4_ring_error())

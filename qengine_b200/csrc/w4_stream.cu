@@ -219,6 +219,57 @@ __device__ __forceinline__ int range_owner(int total, int B, int u) {
   return u < big ? u / (per + 1) : rem + (u - big) / per;
 }
 
+// Warp 0 finishes a segment [gb, ge) of `tile` whose warp-reduced sums it holds: a whole tile is
+// stored; a partial one is published to this CTA's scratch slot and the contributor that completes
+// the tile (integer arrival count of groups) adds all slots in a fixed order and stores.
+// STREAM = true: CTAs own contiguous unit ranges (two slots per CTA: first / last tile of its
+// range); false: grid (tiles, ksplit), slot = tile * ksplit + y.
+template <int EPI, bool STREAM>
+__device__ __forceinline__ void finish_segment(const W4Args& a, int tile, int gb, int ge,
+                                               bool first_of_cta, const float (&acc)[4], int lane) {
+  const int G = a.G;
+  if (ge - gb == G) {
+    store_tile<EPI>(a, tile, acc, lane);
+    return;
+  }
+  const int slot = STREAM ? 2 * blockIdx.x + (first_of_cta ? 0 : 1) : tile * a.ksplit + blockIdx.y;
+  float* mine = a.ws + (long)slot * 128;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) __stcg(mine + i * 32 + lane, acc[i]);
+  __threadfence();
+  __syncwarp();
+  int last = 0;
+  if (lane == 0) {
+    const int cnt = ge - gb;
+    last = (atomicAdd(a.counters + tile, cnt) + cnt == G);
+  }
+  last = __shfl_sync(0xffffffffu, last, 0);
+  if (!last) return;
+  __threadfence();
+  float f[4] = {0.f, 0.f, 0.f, 0.f};
+  if constexpr (!STREAM) {
+    for (int s = 0; s < a.ksplit; ++s) {
+      const float* p = a.ws + (long)(tile * a.ksplit + s) * 128;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) f[i] += __ldcg(p + i * 32 + lane);
+    }
+  } else {
+    const int B = gridDim.x;
+    const int first = range_owner(a.total, B, tile * G);
+    const int lastb = range_owner(a.total, B, tile * G + G - 1);
+    for (int c = first; c <= lastb; ++c) {
+      // CTA c contributed its first segment if its range starts inside this tile, otherwise
+      // (its range starts in an earlier tile) its last segment.
+      const int cs = range_begin(a.total, B, c);
+      const float* p = a.ws + (long)(2 * c + (cs >= tile * G ? 0 : 1)) * 128;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) f[i] += __ldcg(p + i * 32 + lane);
+    }
+  }
+  store_tile<EPI>(a, tile, f, lane);
+  if (lane == 0) a.counters[tile] = 0;
+}
+
 // MODE 2: grid.x CTAs over the whole unit stream. MODE 0: grid (tiles, ksplit).
 template <int WARPS, int U, int V, int EPI, int MODE>
 __global__ void __launch_bounds__(WARPS * 32) w4_stream_kernel(const W4Args a) {
@@ -262,55 +313,181 @@ __global__ void __launch_bounds__(WARPS * 32) w4_stream_kernel(const W4Args a) {
       }
       __syncthreads();
     }
-    if (warp == 0) {
-      if (ge - gb == G) {
-        store_tile<EPI>(a, tile, acc, lane);
-      } else {
-        // Partial tile. Slot of this contribution: mode 0 -> tile * ksplit + y; mode 2 -> two
-        // per CTA (its first tile, its last tile). Publish, count groups, last arrival finishes.
-        int slot;
-        if constexpr (MODE == 0) slot = tile * a.ksplit + blockIdx.y;
-        else slot = 2 * blockIdx.x + (u == u0 ? 0 : 1);
-        float* mine = a.ws + (long)slot * 128;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) __stcg(mine + i * 32 + lane, acc[i]);
-        __threadfence();
-        __syncwarp();
-        int last = 0;
-        if (lane == 0) {
-          const int cnt = ge - gb;
-          last = (atomicAdd(a.counters + tile, cnt) + cnt == G);
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-          __threadfence();
-          float f[4] = {0.f, 0.f, 0.f, 0.f};
-          if constexpr (MODE == 0) {
-            for (int s = 0; s < a.ksplit; ++s) {
-              const float* p = a.ws + (long)(tile * a.ksplit + s) * 128;
-#pragma unroll
-              for (int i = 0; i < 4; ++i) f[i] += __ldcg(p + i * 32 + lane);
-            }
-          } else {
-            const int B = gridDim.x;
-            const int first = range_owner(a.total, B, tile * G);
-            const int lastb = range_owner(a.total, B, tile * G + G - 1);
-            for (int c = first; c <= lastb; ++c) {
-              // CTA c contributed its first segment if its range starts inside this tile,
-              // otherwise (range starts in an earlier tile) its last segment.
-              const int cs = range_begin(a.total, B, c);
-              const float* p = a.ws + (long)(2 * c + (cs >= tile * G ? 0 : 1)) * 128;
-#pragma unroll
-              for (int i = 0; i < 4; ++i) f[i] += __ldcg(p + i * 32 + lane);
-            }
-          }
-          store_tile<EPI>(a, tile, f, lane);
-          if (lane == 0) a.counters[tile] = 0;
-        }
-      }
-    }
+    if (warp == 0) finish_segment<EPI, MODE == 2>(a, tile, gb, ge, u == u0, acc, lane);
     u += ge - gb;
   }
+}
+
+// ---------------------------------------------------------------------------------------------
+// MODE 3: the same unit stream fed through shared memory by the TMA engine. One producer warp
+// issues bulk copies (cp.async.bulk global -> shared, completion on an mbarrier) of SU units
+// (SU KB of codes + SU * 32 B of scales) per stage into a ring of STAGES stages, WARPS consumer
+// warps read their units from the ring. The copies do not depend on the producer kernel of x, so
+// the ring is filled before the programmatic-dependency wait: the whole ring (STAGES * SU KB per
+// CTA) of weights is already on chip when x becomes available, and the stream never stops at tile
+// boundaries. Consumer warp w owns the units u0 + w, u0 + w + WARPS, ... of the CTA's range
+// (a function of the launch shape only), so results stay deterministic and independent of N.
+// Every barrier wait is bounded; on expiry the kernel records an error code and drains.
+// ---------------------------------------------------------------------------------------------
+__device__ int g_ring_error = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* b, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+// Bounded wait: false if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int limit = 1 << 20) {
+  const uint32_t addr = smem_u32(b);
+  for (int it = 0; it < limit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void consumer_sync(int threads) {
+  asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+}
+
+template <int WARPS, int SU, int STAGES, int EPI>
+__global__ void __launch_bounds__((WARPS + 1) * 32) w4_ring_kernel(const W4Args a) {
+  static_assert(SU % WARPS == 0, "every consumer warp owns SU / WARPS units of each stage");
+  constexpr int PER = SU / WARPS;
+  dep_release();
+  extern __shared__ __align__(128) unsigned char ring_raw[];
+  uint4* wring = reinterpret_cast<uint4*>(ring_raw);                                  // [STAGES][SU][64]
+  __half* sring = reinterpret_cast<__half*>(ring_raw + (size_t)STAGES * SU * 1024);   // [STAGES][SU][16]
+  __shared__ uint64_t full[STAGES], empty[STAGES];
+  __shared__ float red[2][WARPS][4][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int G = a.G;
+  const int u0 = range_begin(a.total, gridDim.x, blockIdx.x);
+  const int u1 = range_begin(a.total, gridDim.x, blockIdx.x + 1);
+  const int nstage = (u1 - u0 + SU - 1) / SU;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], WARPS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == WARPS) {
+    // ---- producer: one lane streams this CTA's slab, stage by stage ----
+    if (lane == 0) {
+      for (int st = 0; st < nstage; ++st) {
+        const int slot = st % STAGES;
+        if (st >= STAGES && !mbar_wait(&empty[slot], ((st / STAGES) - 1) & 1)) {
+          atomicExch(&g_ring_error, 1);
+          break;
+        }
+        const int ub = u0 + st * SU, cnt = min(SU, u1 - ub);
+        mbar_expect_tx(&full[slot], (uint32_t)cnt * (1024 + 32));
+        bulk_load(wring + (size_t)slot * SU * 64, a.qw + (size_t)ub * 64, (uint32_t)cnt * 1024, &full[slot]);
+        bulk_load(sring + (size_t)slot * SU * 16, a.scales + (size_t)ub * 16, (uint32_t)cnt * 32, &full[slot]);
+      }
+    }
+    dep_wait();
+    return;
+  }
+
+  // ---- consumers ----
+  const int r = lane >> 2, t = lane & 3;
+  dep_wait();  // x, out, scratch: after the producer kernel
+  // Lane (r, t) multiplies x row r. Rows >= N feed mma columns that are never stored, so those
+  // lanes simply read row N - 1 again: no zero fill, no branch. (Host guarantees K % 128 == 0,
+  // 16-byte aligned x and ldx % 8 == 0 for this mode.)
+  const uint4* xlane = reinterpret_cast<const uint4*>(a.x + (long)min(r, a.N - 1) * a.ldx + 16 * t);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  int tile = u0 / G;          // tile of the segment being accumulated
+  int seg_begin = u0;         // first unit of that segment
+  int phase = 0;              // red[] double buffer
+  bool ok = true;
+
+  // Sum the warps' partial tiles in warp order and let warp 0 store / publish the segment.
+  auto close_segment = [&](int seg_end) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) red[phase][warp][c][lane] = acc[c];
+    consumer_sync(WARPS * 32);
+    if (warp == 0) {
+      float f[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float s = red[phase][0][c][lane];
+#pragma unroll
+        for (int w2 = 1; w2 < WARPS; ++w2) s += red[phase][w2][c][lane];
+        f[c] = s;
+      }
+      finish_segment<EPI, true>(a, tile, seg_begin - tile * G, seg_end - tile * G, seg_begin == u0, f, lane);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[c] = 0.f;
+    phase ^= 1;
+    seg_begin = seg_end;
+    ++tile;
+  };
+
+  for (int st = 0; st < nstage; ++st) {
+    const int slot = st % STAGES;
+    if (!mbar_wait(&full[slot], (st / STAGES) & 1, ok ? (1 << 20) : 64)) {
+      ok = false;
+      atomicExch(&g_ring_error, 2);
+    }
+    const int ub = u0 + st * SU;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int idx = warp + i * WARPS;  // unit of this stage owned by this warp
+      const int u = ub + idx;
+      // Tile boundaries inside the range that lie at or before u: close them. Every consumer
+      // warp closes every such boundary exactly once (here, or in the catch-up loop after the
+      // last stage), so the k-th barrier of each warp always belongs to the k-th boundary.
+      while (u >= (tile + 1) * G && (tile + 1) * G < u1) close_segment((tile + 1) * G);
+      if (u < u1 && ok) {
+        const int g = u - tile * G;
+        const uint4* wp = wring + ((size_t)slot * SU + idx) * 64 + lane;
+        const uint4 w0 = wp[0], w1 = wp[32];
+        const __half* sp = sring + ((size_t)slot * SU + idx) * 16 + r;
+        const float slo = __half2float(sp[0]), shi = __half2float(sp[8]);
+        const uint4* xp = xlane + g * 16;  // 128 bf16 per group = 16 uint4
+        const uint4 x0 = __ldg(xp), x1 = __ldg(xp + 1), x2 = __ldg(xp + 8), x3 = __ldg(xp + 9);
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        kstep(c, w0.x, x0.x, x0.y);
+        kstep(c, w0.y, x0.z, x0.w);
+        kstep(c, w0.z, x1.x, x1.y);
+        kstep(c, w0.w, x1.z, x1.w);
+        kstep(c, w1.x, x2.x, x2.y);
+        kstep(c, w1.y, x2.z, x2.w);
+        kstep(c, w1.z, x3.x, x3.y);
+        kstep(c, w1.w, x3.z, x3.w);
+        acc[0] = fmaf(slo, c[0], acc[0]);
+        acc[1] = fmaf(slo, c[1], acc[1]);
+        acc[2] = fmaf(shi, c[2], acc[2]);
+        acc[3] = fmaf(shi, c[3], acc[3]);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[slot]);
+  }
+  while ((tile + 1) * G < u1) close_segment((tile + 1) * G);  // boundaries this warp never reached
+  close_segment(u1);                                          // the last segment of the range
 }
 
 using KernelFn = void (*)(const W4Args);
@@ -361,7 +538,25 @@ int blocks_per_sm(KernelFn fn, int threads) {
 struct Resolved {
   qe_w4_plan plan;
   KernelFn fn;
+  size_t smem = 0;
 };
+
+// Ring geometry of mode 3: 8 consumer warps, 16 units (16.5 KB) per stage, 6 stages = 99 KB of
+// weights in flight per CTA, two CTAs per SM.
+constexpr int kRingWarps = 8, kRingSU = 16, kRingStages = 6;
+constexpr size_t kRingSmem = (size_t)kRingStages * kRingSU * (1024 + 32);
+
+KernelFn ring_kernel(int epi) {
+  static bool configured = false;
+  KernelFn a = w4_ring_kernel<kRingWarps, kRingSU, kRingStages, QE_EPI_NONE>;
+  KernelFn b = w4_ring_kernel<kRingWarps, kRingSU, kRingStages, QE_EPI_SWIGLU>;
+  if (!configured) {
+    cudaFuncSetAttribute(a, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingSmem);
+    cudaFuncSetAttribute(b, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingSmem);
+    configured = true;
+  }
+  return epi == QE_EPI_SWIGLU ? b : a;
+}
 
 // Shape-only policy (never N). B200: 148 SMs; every matrix of the 27B model except the tiniest
 // runs as one persistent unit stream; small matrices (< 4096 units) use the (tile, ksplit) grid
@@ -372,8 +567,24 @@ Resolved resolve(const qe_w4_params& p, const qe_w4_cfg& in) {
   const long tiles = p.Mp / 16, G = p.Kp / 128, units = tiles * G;
   const int sms = qe_sm_count();
   const int auto_mode = units < 4096 ? 0 : 2;
-  int mode = (c.mode == 0 || c.mode == 2) ? c.mode : auto_mode;
-  if (units >= (1L << 30)) mode = 0;  // 32-bit unit arithmetic in the stream mode
+  int mode = (c.mode == 0 || c.mode == 2 || c.mode == 3) ? c.mode : auto_mode;
+  if (units >= (1L << 30)) mode = 0;  // 32-bit unit arithmetic in the stream modes
+  // The ring path serves the aligned fast case only (every matrix of the model qualifies).
+  if (mode == 3 && (p.K != p.Kp || (p.ldx & 7) || (reinterpret_cast<uintptr_t>(p.x) & 15))) mode = 2;
+  if (mode == 3) {
+    r.fn = ring_kernel(p.epilogue);
+    r.smem = kRingSmem;
+    r.plan.mode = 3;
+    r.plan.threads = (kRingWarps + 1) * 32;
+    r.plan.counters = tiles;
+    const int bps = c.blocks_per_sm > 0 ? c.blocks_per_sm : 2;
+    const long per_block = (long)std::max(1, c.min_units) * kRingWarps;
+    const long blocks = std::max<long>(1, std::min<long>((long)sms * bps, (units + per_block - 1) / per_block));
+    r.plan.grid_x = (int)blocks;
+    r.plan.grid_y = 1;
+    r.plan.ws_floats = blocks * 2 * 128;
+    return r;
+  }
   int warps = (c.warps == 4 || c.warps == 8 || c.warps == 16) ? c.warps : 8;
   int unroll = (c.unroll == 1 || c.unroll == 2 || c.unroll == 4) ? c.unroll : 4;
   const int variant = (c.variant >= 0 && c.variant <= 3) ? c.variant : 0;
@@ -427,6 +638,13 @@ extern "C" int qe_w4_plan_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, qe_w
   return 0;
 }
 
+// Error word of the ring kernel's bounded waits (0 = none). Host-visible for tests and the engine.
+extern "C" int qe_w4_ring_error(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_ring_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
 extern "C" int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream) {
   if (!p || !cfg) return QE_ERR_ARG;
   if (p->N < 1 || p->N > QE_MAX_ROWS || p->Mp % 16 || p->Kp % 128 || p->Mp <= 0 || p->Kp <= 0)
@@ -447,6 +665,6 @@ extern "C" int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* str
   a.ksplit = r.plan.grid_y;
   a.total = a.tiles * a.G;
   const bool pdl = cfg->pdl && pdl_launch_enabled() && pdl_trigger_enabled();
-  return (int)launch(r.fn, dim3(r.plan.grid_x, r.plan.grid_y, 1), dim3(r.plan.threads), 0,
+  return (int)launch(r.fn, dim3(r.plan.grid_x, r.plan.grid_y, 1), dim3(r.plan.threads), r.smem,
                      (cudaStream_t)stream, pdl, a);
 }

@@ -26,7 +26,8 @@ ODD_SHAPES = [(1, 1), (1, 128), (7, 127), (16, 129), (127, 1000), (1000, 4097), 
               (17, 255), (100, 136)]
 CFGS = [dict(), dict(warps=4), dict(warps=16), dict(unroll=1), dict(unroll=4), dict(warps=16, unroll=1),
         dict(mode=0), dict(mode=0, ksplit=2), dict(mode=0, ksplit=7), dict(mode=2), dict(mode=2, min_units=1),
-        dict(mode=2, warps=4, unroll=1), dict(variant=1), dict(pdl=False)]
+        dict(mode=2, warps=4, unroll=1), dict(variant=1), dict(pdl=False), dict(mode=3),
+        dict(mode=3, blocks_per_sm=1, min_units=1)]
 
 
 @pytest.fixture(scope="module")
@@ -103,7 +104,7 @@ def test_odd_shapes(api, M, K):
 
 
 @pytest.mark.parametrize("mode,ksplit,min_units", [(0, 1, 4), (0, 2, 4), (0, 3, 4), (0, 7, 4), (0, 40, 4),
-                                                  (2, 0, 1), (2, 0, 4), (-1, 0, 4)])
+                                                  (2, 0, 1), (2, 0, 4), (-1, 0, 4), (3, 0, 1), (3, 0, 4)])
 @pytest.mark.parametrize("warps,unroll", [(4, 1), (8, 2), (8, 4), (16, 1)])
 def test_launch_configs(api, mode, ksplit, min_units, warps, unroll):
     p = api["q"](rand_w(1000, 5120, seed=9))
@@ -267,6 +268,21 @@ def test_swiglu_bitwise_and_row_independent(api):
         for r in range(8):
             assert torch.equal(bits(api["gemv"](x[r:r + 1].contiguous(), p, **kw)), full[r:r + 1]), \
                 f"swiglu {kw} row {r}"
+
+
+@pytest.mark.parametrize("name", list(SHAPES_27B))
+def test_ring_mode_all_row_counts(api, name):
+    """Mode 3 (weights through the shared-memory ring) on every 27B shape; its bounded waits must
+    never expire."""
+    M, K = SHAPES_27B[name]
+    p = api["q"](rand_w(M, K, seed=50))
+    Wd = api["deq"](p)
+    x = rand_x(8, K, seed=51)
+    ref = x.float() @ Wd.T
+    bnd = bound(x, Wd, ref)
+    for N in (1, 2, 5, 8):
+        check(api["gemv"](x[:N].contiguous(), p, mode=3), ref[:N], bnd[:N], f"ring {name} N={N}")
+    assert api["w4"].ring_error() == 0
 
 
 def test_linearity_at_full_size(api):
