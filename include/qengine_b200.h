@@ -157,6 +157,10 @@ typedef struct qe_w4_params {
   int N;               /* activation rows, 1..8 */
   long ldx, ldo;
   int epilogue;        /* QE_EPI_* */
+  int x_f16;           /* 0: x is bf16 (the reference's contract). 1: x is fp16 -- same row layout;
+                          needs K == Kp, 16-byte aligned x and ldx % 8 == 0. No counterpart in the
+                          reference; used by the decode engine, whose GEMV inputs are bf16-rounded
+                          values that convert to fp16 exactly. */
 } qe_w4_params;
 
 /* Launch options with the reference's names (csrc/gemv_w4.h:27-39). 0 / -1 mean "auto by shape".

@@ -18,7 +18,7 @@ class W4Params(C.Structure):
     """struct qe_w4_params"""
     _fields_ = [("qw", P), ("scales", P), ("x", P), ("out", P), ("ws", P), ("counters", P),
                 ("M", c_int), ("K", c_int), ("Mp", c_int), ("Kp", c_int), ("N", c_int),
-                ("ldx", c_long), ("ldo", c_long), ("epilogue", c_int)]
+                ("ldx", c_long), ("ldo", c_long), ("epilogue", c_int), ("x_f16", c_int)]
 
 
 class W4Cfg(C.Structure):

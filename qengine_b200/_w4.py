@@ -56,10 +56,12 @@ def _workspace(dev: torch.device, ws_floats: int, counters: int) -> _Workspace:
     return W
 
 
-def _run(x, qw, scales, out, M, epilogue, warps, unroll, ksplit, pdl, variant, mode, bps, min_units):
+def _run(x, qw, scales, out, M, epilogue, warps, unroll, ksplit, pdl, variant, mode, bps, min_units,
+         allow_f16=False):
     for t in (x, qw, scales, out):
         _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
-    _req(x.dtype == torch.bfloat16, "x must be bf16 (W4A16 kernel)")
+    x_f16 = allow_f16 and x.dtype == torch.float16
+    _req(x.dtype == torch.bfloat16 or x_f16, "x must be bf16 (W4A16 kernel)")
     _req(out.dtype == torch.bfloat16, "out must be bf16")
     _req(qw.dtype == torch.int32 and qw.dim() == 4 and qw.size(2) == 32 and qw.size(3) == 4,
          "qw must be int32 [Mp/16, Kp/64, 32, 4] from quant.quantize_w4")
@@ -83,10 +85,13 @@ def _run(x, qw, scales, out, M, epilogue, warps, unroll, ksplit, pdl, variant, m
     _req(x.data_ptr() != out.data_ptr(), "in-place not supported")
     _req(warps in (0, 4, 8, 16), "warps in {0 (auto),4,8,16}")
     _req(unroll in (0, 1, 2, 4), "unroll in {0 (auto),1,2,4}")
-    _req(mode in (-1, 0, 2, 3), "mode in {-1 (auto), 0, 2, 3}")
+    _req(mode in (-1, 0, 2, 3, 4), "mode in {-1 (auto), 0, 2, 3, 4}")
 
     p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None,
-                 M, K, Mp, Kp, N, x.stride(0), out.stride(0), epilogue)
+                 M, K, Mp, Kp, N, x.stride(0), out.stride(0), epilogue, int(x_f16))
+    if x_f16:
+        _req(K == Kp and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0,
+             "fp16 activations need K % 128 == 0 and 16-byte aligned rows")
     cfg = W4Cfg(int(warps), int(unroll), int(ksplit), int(bool(pdl)), int(variant), int(mode),
                 int(bps), int(min_units))
     plan = W4Plan()
@@ -110,6 +115,16 @@ def gemv_swiglu(x, qw, scales, out, I, warps=0, unroll=0, ksplit=0, pdl=True, va
     """out[N, I] = silu(x @ Wg^T) * (x @ Wu^T) (packed by quant.quantize_w4_gate_up)."""
     _run(x, qw, scales, out, I, EPI_SWIGLU, warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm,
          min_units)
+
+
+def gemv_act16(x, qw, scales, out, M, swiglu=False, **kw):
+    """Engine-internal variant (not in the reference): x may be fp16. The decode engine keeps its
+    GEMV inputs as fp16 copies of bf16-rounded values (an exact conversion), because the fp16
+    unpack needs fewer integer-pipe instructions per weight than the bf16 one."""
+    cfg = dict(warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1, blocks_per_sm=0, min_units=4)
+    cfg.update(kw)
+    _run(x, qw, scales, out, M, EPI_SWIGLU if swiglu else EPI_NONE, cfg["warps"], cfg["unroll"], cfg["ksplit"],
+         cfg["pdl"], cfg["variant"], cfg["mode"], cfg["blocks_per_sm"], cfg["min_units"], allow_f16=True)
 
 
 def auto_ksplit(Mp, Kp, N, warps=8):

@@ -16,25 +16,36 @@
 //   conv  c = w0 x[p-3] + w1 x[p-2] + w2 x[p-1] + w3 x[p] (fp32), y = bf16(silu(bf16(c)))
 //   q = y_q * rsqrt(sum y_q^2 + 1e-6) / sqrt(D),  k = y_k * rsqrt(sum y_k^2 + 1e-6),  v = y_v
 //   beta = bf16(sigmoid(b)),  decay = exp(-exp(A_log) * softplus(a + dt_bias))
-//   S *= decay;  kv = S^T k;  delta = (v - kv) * beta;  S += k delta^T;  o = S^T q
+//   S' = decay S + k delta^T with delta = beta (v - decay S^T k);  o = S'^T q
 //   out = bf16( bf16(norm_w * bf16(o_b * rsqrt(mean o_b^2 + eps))) * silu(z) ),  o_b = bf16(o)
 // Conv history lives in a 16-slot ring keyed by absolute position (slot p & 15); with n <= 8 the
 // slots read (p-3..p-1 of the first row) and written (p..p+n-1) never alias.
 //
-// Layout: one CTA per value head, 4 D threads. Thread (d, h) owns column d of S and the rows
-// [h D/4, (h+1) D/4): S is read and written coalesced along d and stays in registers for the
-// whole pass. Dot products over the D rows are finished through shared memory in a fixed order.
+// B200 layout. The columns of S are independent in the recurrence (column d only needs k, q,
+// v[d]), so a head is split over a thread-block cluster of D / 32 CTAs, 32 columns each: 192 CTAs
+// for the 48 heads of the 27B shape instead of 48. A CTA is 8 warps; warp w owns rows
+// [w D/8, (w+1) D/8) of its 32 columns in registers (lane = column, S read and written coalesced).
+// One pass over the register state per row gives both S^T k and S^T q of the pre-update state:
+//   kv = decay (S^T k),  delta = beta (v - kv),  o = decay (S^T q) + delta (k . q)
+// so a row costs one block barrier (partials are double-buffered) instead of several. The gated
+// RMSNorm needs the sum of o_b^2 over all D columns of the head: every CTA publishes its partial
+// sum in shared memory and reads the others' through distributed shared memory in rank order.
 //
-// Dependency handling: the state load, the staged checkpoints and the per-head constants do not
-// depend on the producer of this pass's projections (they were written by this kernel one pass
-// ago), so they are fetched before the programmatic-dependency wait and overlap the in_proj GEMV.
+// Dependency handling: the state load and the per-head constants do not depend on the producer
+// of this pass's projections, so with `early` they are fetched before the programmatic-dependency
+// wait and overlap the in_proj GEMV. Everything the previous pass wrote recently (ctl, ring,
+// checkpoints) is read after the wait.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "../../include/qengine_b200.h"
+
+namespace cg = cooperative_groups;
 
 namespace qb {
 namespace {
 
-constexpr int kRing = 16, kMaxRows = QE_MAX_ROWS, kRowGroups = 4;
+constexpr int kRing = 16, kMaxRows = QE_MAX_ROWS, kCols = 32, kWarps = 8;
 
 struct GdnArgs {
   const bf16 *qkv, *z, *b, *a;
@@ -50,91 +61,105 @@ struct GdnArgs {
   int early;
 };
 
-// S <- decay S + k (beta (v - (decay S)^T k))^T on this thread's rows of column d.
 template <int D>
-__device__ __forceinline__ void delta_update(float (&s)[D / kRowGroups], const float* k,
-                                             const float* v, float decay, float beta,
-                                             float (*part)[D], int d, int h) {
-  constexpr int RP = D / kRowGroups;
-  float acc = 0.f;
-#pragma unroll
-  for (int i = 0; i < RP; ++i) {
-    s[i] *= decay;
-    acc = fmaf(s[i], k[h * RP + i], acc);
-  }
-  part[h][d] = acc;
-  __syncthreads();
-  float kv = part[0][d];
-#pragma unroll
-  for (int g = 1; g < kRowGroups; ++g) kv += part[g][d];
-  const float delta = (v[d] - kv) * beta;
-  __syncthreads();
-#pragma unroll
-  for (int i = 0; i < RP; ++i) s[i] = fmaf(k[h * RP + i], delta, s[i]);
-}
-
-template <int D>
-__global__ void __launch_bounds__(kRowGroups * D) gdn_rows_kernel(const GdnArgs a) {
-  constexpr int RP = D / kRowGroups, NT = kRowGroups * D;
-  static_assert(NT >= 3 * D + kMaxRows, "one thread per conv channel plus one per row gate");
+__global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs a) {
+  constexpr int RP = D / kWarps;        // state rows per warp
+  constexpr int NT = kWarps * 32;
+  constexpr int NCTA = D / kCols;       // CTAs per head = cluster size
   dep_release();
   if (!a.early) dep_wait();
+  cg::cluster_group cluster = cg::this_cluster();
 
-  __shared__ float q_s[kMaxRows][D], k_s[kMaxRows][D], v_s[kMaxRows][D];
-  __shared__ float gate_s[kMaxRows][2];  // (decay, beta)
-  __shared__ float part[kRowGroups][D];
-  __shared__ float scratch[32];
+  __shared__ float q_s[kMaxRows][D], k_s[kMaxRows][D];
+  __shared__ float v_s[kMaxRows][kCols], o_s[kMaxRows][kCols];
+  __shared__ float gate_s[kMaxRows][2];      // (decay, beta)
+  __shared__ float kq_s[kMaxRows];           // k . q per row
+  __shared__ float part[2][2][kWarps][kCols];  // [buffer][k or q][warp][column]
+  __shared__ float ss_s[kMaxRows];           // this CTA's sum of o_b^2 per row
 
-  const int j = blockIdx.x;
+  const int j = blockIdx.y;                  // value head
+  const int cs = blockIdx.x;                 // column slice = rank in the cluster
+  const int c0 = cs * kCols;
   const int rep = a.Hv / a.Hk, i_qk = j / rep;
   const int C = 2 * a.Hk * D + a.Hv * D;
-  const int tid = threadIdx.x, d = tid % D, h = tid / D;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n = a.n;
-  float* Sj = a.S + (size_t)j * D * D;
+  float* Sj = a.S + (size_t)j * D * D + c0 + lane;
 
-  // ---- independent of this pass's producer: state, per-head constants ----
+  // ---- independent of this pass's producer: state slice, per-head constants ----
   float s[RP];
 #pragma unroll
-  for (int i = 0; i < RP; ++i) s[i] = Sj[(h * RP + i) * D + d];
-  int ch = 0;
-  float cw[4] = {0.f, 0.f, 0.f, 0.f};
-  if (tid < 3 * D) {
-    const int part_id = tid / D, c = tid % D;
-    ch = part_id == 0 ? i_qk * D + c : part_id == 1 ? a.Hk * D + i_qk * D + c : 2 * a.Hk * D + j * D + c;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) cw[w] = tofloat(a.conv_w[ch * 4 + w]);
-  }
+  for (int i = 0; i < RP; ++i) s[i] = Sj[(size_t)(warp * RP + i) * D];
   const float A_log = tofloat(a.A_log[j]), dt_bias = tofloat(a.dt_bias[j]);
-  const float nw = tid < D ? tofloat(a.norm_w[tid]) : 0.f;
+  const float nw = tofloat(a.norm_w[c0 + lane]);
   if (a.early) dep_wait();
 
   const int P = a.ctl[0], pend = min(max(a.ctl[1], 0), kMaxRows);
 
+  // S <- decay S + k (beta (v - decay S^T k))^T on this thread's rows of its column; with Q also
+  // returns o = S'^T q for the column. Identical arithmetic for replayed and new rows.
+  auto row_update = [&](const float* kk, const float* qq, float v, float decay, float beta, float kq,
+                        int buf, bool want_o) -> float {
+    float pk = 0.f, pq = 0.f;
+#pragma unroll
+    for (int i = 0; i < RP; ++i) {
+      pk = fmaf(s[i], kk[warp * RP + i], pk);
+      if (want_o) pq = fmaf(s[i], qq[warp * RP + i], pq);
+    }
+    part[buf][0][warp][lane] = pk;
+    if (want_o) part[buf][1][warp][lane] = pq;
+    __syncthreads();
+    float kv = part[buf][0][0][lane];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) kv += part[buf][0][w][lane];
+    const float delta = (v - decay * kv) * beta;
+#pragma unroll
+    for (int i = 0; i < RP; ++i) s[i] = fmaf(kk[warp * RP + i], delta, decay * s[i]);
+    if (!want_o) return 0.f;
+    float qs = part[buf][1][0][lane];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) qs += part[buf][1][w][lane];
+    return fmaf(delta, kq, decay * qs);
+  };
+
   // ---- 1. replay the kept rows of the previous pass, write the committed state once ----
+  int buf = 0;
   for (int t = 0; t < pend; ++t) {
-    if (tid < D) k_s[0][tid] = a.st_k[((size_t)t * a.Hv + j) * D + tid];
-    else if (tid < 2 * D) v_s[0][tid - D] = a.st_v[((size_t)t * a.Hv + j) * D + tid - D];
-    __syncthreads();
-    delta_update<D>(s, k_s[0], v_s[0], a.st_g[(t * a.Hv + j) * 2], a.st_g[(t * a.Hv + j) * 2 + 1],
-                    part, d, h);
-    __syncthreads();
+    // checkpoints into shared memory (k for all D rows, v for this CTA's columns)
+    for (int i = tid; i < D; i += NT) k_s[t][i] = a.st_k[((size_t)t * a.Hv + j) * D + i];
+    if (tid < kCols) v_s[t][tid] = a.st_v[((size_t)t * a.Hv + j) * D + c0 + tid];
+  }
+  __syncthreads();
+  for (int t = 0; t < pend; ++t) {
+    row_update(k_s[t], nullptr, v_s[t][lane], a.st_g[(t * a.Hv + j) * 2], a.st_g[(t * a.Hv + j) * 2 + 1],
+               0.f, buf, false);
+    buf ^= 1;
   }
   if (pend > 0) {
 #pragma unroll
-    for (int i = 0; i < RP; ++i) Sj[(h * RP + i) * D + d] = s[i];
+    for (int i = 0; i < RP; ++i) Sj[(size_t)(warp * RP + i) * D] = s[i];
   }
+  __syncthreads();  // k_s / v_s are about to be overwritten by the new rows
 
-  // ---- 2a. causal conv + SiLU of every new row; conv ring update; gates ----
-  if (tid < 3 * D) {
-    const int part_id = tid / D, c = tid % D;
-    float hist[3];
+  // ---- 2a. causal conv + SiLU of every new row (q, k: all D channels; v: own columns) ----
+  for (int idx = tid; idx < 2 * D + kCols; idx += NT) {
+    const int part_id = idx < D ? 0 : idx < 2 * D ? 1 : 2;
+    const int c = part_id == 0 ? idx : part_id == 1 ? idx - D : idx - 2 * D;
+    const int ch = part_id == 0 ? i_qk * D + c
+                 : part_id == 1 ? a.Hk * D + i_qk * D + c
+                                : 2 * a.Hk * D + j * D + c0 + c;
+    float cw[4];
 #pragma unroll
-    for (int w = 0; w < 3; ++w) {
-      const int p = P - 3 + w;
-      hist[w] = p >= 0 ? tofloat(a.ring[(size_t)(p & (kRing - 1)) * C + ch]) : 0.f;
+    for (int w = 0; w < 4; ++w) cw[w] = tofloat(a.conv_w[ch * 4 + w]);
+    float x0, x1, x2;
+    {
+      const int p0 = P - 3, p1 = P - 2, p2 = P - 1;
+      x0 = p0 >= 0 ? tofloat(a.ring[(size_t)(p0 & (kRing - 1)) * C + ch]) : 0.f;
+      x1 = p1 >= 0 ? tofloat(a.ring[(size_t)(p1 & (kRing - 1)) * C + ch]) : 0.f;
+      x2 = p2 >= 0 ? tofloat(a.ring[(size_t)(p2 & (kRing - 1)) * C + ch]) : 0.f;
     }
-    const bool owner = part_id == 2 || (j % rep) == 0;  // q/k channels are shared by `rep` heads
-    float x0 = hist[0], x1 = hist[1], x2 = hist[2];
+    // q/k channels are shared by `rep` heads and by the CTAs of a head: one CTA writes them
+    const bool owner = part_id == 2 || ((j % rep) == 0 && cs == 0);
     for (int t = 0; t < n; ++t) {
       const bf16 xb = a.qkv[(long)t * a.ldp + ch];
       const float x3 = tofloat(xb);
@@ -149,79 +174,102 @@ __global__ void __launch_bounds__(kRowGroups * D) gdn_rows_kernel(const GdnArgs 
       if (owner) a.ring[(size_t)((P + t) & (kRing - 1)) * C + ch] = xb;
       x0 = x1; x1 = x2; x2 = x3;
     }
-  } else if (tid < 3 * D + n) {
-    const int t = tid - 3 * D;
+  }
+  if (tid < n) {
+    const int t = tid;
     const float bt = rnd(sigmoid_acc(tofloat(a.b[(long)t * a.ldp + j])));
     const float x = tofloat(a.a[(long)t * a.ldp + j]) + dt_bias;
     const float sp = x > 20.f ? x : log1pf(expf(x));
     gate_s[t][0] = expf(-expf(A_log) * sp);
     gate_s[t][1] = bt;
   }
-  float zr[kMaxRows];
-  if (tid < D) {
-#pragma unroll
-    for (int t = 0; t < kMaxRows; ++t)
-      if (t < n) zr[t] = tofloat(a.z[(long)t * a.ldp + j * D + tid]);
-  }
   __syncthreads();
 
-  // ---- 2b. l2norm of q and k of every row: one warp per vector, fixed summation order ----
-  {
-    const int lane = tid & 31, warp = tid >> 5, nwarps = NT / 32;
-    for (int vec = warp; vec < 2 * n; vec += nwarps) {
-      float* p = (vec & 1) ? k_s[vec >> 1] : q_s[vec >> 1];
-      float e[D / 32], ss = 0.f;
+  // ---- 2b. l2norm of q and k of every row and k . q: warp t handles row t ----
+  for (int t = warp; t < n; t += kWarps) {
+    float eq[D / 32], ek[D / 32], sq = 0.f, sk = 0.f;
 #pragma unroll
-      for (int u = 0; u < D / 32; ++u) {
-        e[u] = p[lane + 32 * u];
-        ss += warp_allsum(e[u] * e[u]);
-      }
-      const float inv = rsqrtf(ss + 1e-6f);
-#pragma unroll
-      for (int u = 0; u < D / 32; ++u)
-        p[lane + 32 * u] = (vec & 1) ? e[u] * inv : (e[u] * inv) / sqrtf((float)D);
+    for (int u = 0; u < D / 32; ++u) {
+      eq[u] = q_s[t][lane + 32 * u];
+      ek[u] = k_s[t][lane + 32 * u];
+      sq += warp_allsum(eq[u] * eq[u]);
+      sk += warp_allsum(ek[u] * ek[u]);
     }
+    const float iq = rsqrtf(sq + 1e-6f), ik = rsqrtf(sk + 1e-6f);
+    float dot = 0.f;
+#pragma unroll
+    for (int u = 0; u < D / 32; ++u) {
+      const float qn = (eq[u] * iq) / sqrtf((float)D), kn = ek[u] * ik;
+      q_s[t][lane + 32 * u] = qn;
+      k_s[t][lane + 32 * u] = kn;
+      dot += warp_allsum(qn * kn);
+    }
+    if (lane == 0) kq_s[t] = dot;
   }
   __syncthreads();
 
-  // ---- 2c. checkpoint every row for the next pass ----
+  // ---- 2c. checkpoint every row for the next pass (k, gates: one CTA per head; v: own slice) ----
   for (int t = 0; t < n; ++t) {
-    if (tid < D) a.st_k[((size_t)t * a.Hv + j) * D + tid] = k_s[t][tid];
-    else if (tid < 2 * D) a.st_v[((size_t)t * a.Hv + j) * D + tid - D] = v_s[t][tid - D];
-    else if (tid == 2 * D) {
-      a.st_g[(t * a.Hv + j) * 2] = gate_s[t][0];
-      a.st_g[(t * a.Hv + j) * 2 + 1] = gate_s[t][1];
+    if (cs == 0) {
+      for (int i = tid; i < D; i += NT) a.st_k[((size_t)t * a.Hv + j) * D + i] = k_s[t][i];
+      if (tid == 0) {
+        a.st_g[(t * a.Hv + j) * 2] = gate_s[t][0];
+        a.st_g[(t * a.Hv + j) * 2 + 1] = gate_s[t][1];
+      }
     }
+    if (tid < kCols) a.st_v[((size_t)t * a.Hv + j) * D + c0 + tid] = v_s[t][tid];
   }
 
   // ---- 2d. the recurrence, row by row, on the register copy of S ----
   for (int t = 0; t < n; ++t) {
-    delta_update<D>(s, k_s[t], v_s[t], gate_s[t][0], gate_s[t][1], part, d, h);
-    float acc = 0.f;
-#pragma unroll
-    for (int i = 0; i < RP; ++i) acc = fmaf(s[i], q_s[t][h * RP + i], acc);
-    part[h][d] = acc;
-    __syncthreads();
-    float o = 0.f;
-    if (tid < D) {
-      o = part[0][tid];
-#pragma unroll
-      for (int g = 1; g < kRowGroups; ++g) o += part[g][tid];
-      o = rnd(o);
-    }
-    const float ss = block_allsum(tid < D ? o * o : 0.f, scratch);
-    if (tid < D) {
-      const float nn = rnd(o * rsqrtf(ss / (float)D + a.eps));
-      const float y = rnd(nw * nn);
-      a.out[(long)t * a.ldo + j * D + tid] = tobf16(y * silu_acc(zr[t]));
-    }
-    __syncthreads();
+    const float o = row_update(k_s[t], q_s[t], v_s[t][lane], gate_s[t][0], gate_s[t][1], kq_s[t], buf, true);
+    buf ^= 1;
+    if (warp == 0) o_s[t][lane] = rnd(o);  // the mixer output is a bf16 tensor in the model
   }
+  __syncthreads();
+
+  // ---- 2e. gated RMSNorm over the head's D outputs: cluster-wide sum of squares ----
+  for (int t = warp; t < n; t += kWarps) {
+    const float ob = o_s[t][lane];
+    const float ssum = warp_allsum(ob * ob);
+    if (lane == 0) ss_s[t] = ssum;
+  }
+  cluster.sync();
+  for (int t = warp; t < n; t += kWarps) {
+    float total = 0.f;
+#pragma unroll
+    for (int rk = 0; rk < NCTA; ++rk) total += *cluster.map_shared_rank(&ss_s[t], rk);
+    const float ob = o_s[t][lane];
+    const float nn = rnd(ob * rsqrtf(total / (float)D + a.eps));
+    const float y = rnd(nw * nn);
+    const float zz = tofloat(a.z[(long)t * a.ldp + j * D + c0 + lane]);
+    a.out[(long)t * a.ldo + j * D + c0 + lane] = tobf16(y * silu_acc(zz));
+  }
+  cluster.sync();  // nobody leaves while a peer may still read its shared memory
 }
 
 // Off by default: the early state load assumes that no launch on the same state is still in
 // flight, which a caller that keeps other kernels between two steps of a layer guarantees.
 bool g_gdn_early = false;
+
+template <int D>
+cudaError_t launch_gdn(const GdnArgs& g, int Hv, cudaStream_t s, bool pdl) {
+  cudaLaunchConfig_t c = {};
+  c.gridDim = dim3(D / kCols, Hv, 1);
+  c.blockDim = dim3(kWarps * 32, 1, 1);
+  c.dynamicSmemBytes = 0;
+  c.stream = s;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = D / kCols;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  c.attrs = at;
+  c.numAttrs = pdl ? 2 : 1;
+  return cudaLaunchKernelEx(&c, gdn_cluster_kernel<D>, g);
+}
 
 }  // namespace
 }  // namespace qb
@@ -246,7 +294,7 @@ extern "C" int qe_gdn_step_n(const void* qkv, const void* z, const void* b, cons
   g.n = n; g.Hk = Hk; g.Hv = Hv; g.eps = eps; g.early = g_gdn_early ? 1 : 0;
   const bool pdl = pdl_launch_enabled() && pdl_trigger_enabled();
   cudaStream_t s = (cudaStream_t)stream;
-  if (D == 128) return (int)launch(gdn_rows_kernel<128>, dim3(Hv), dim3(512), 0, s, pdl, g);
-  if (D == 64) return (int)launch(gdn_rows_kernel<64>, dim3(Hv), dim3(256), 0, s, pdl, g);
+  if (D == 128) return (int)launch_gdn<128>(g, Hv, s, pdl);
+  if (D == 64) return (int)launch_gdn<64>(g, Hv, s, pdl);
   return QE_ERR_ARG;
 }

@@ -23,10 +23,10 @@ constexpr int kSplitWarps = 8, kStep = 4;
 
 template <int HD>
 __global__ void __launch_bounds__(HD)
-attn_prep_kernel(const bf16* __restrict__ qg, const bf16* __restrict__ k, const bf16* __restrict__ v,
-                 long ldp, const bf16* __restrict__ qnw, const bf16* __restrict__ knw,
-                 const float* __restrict__ inv_freq, const int* __restrict__ pos_ptr,
-                 bf16* __restrict__ q_out, bf16* __restrict__ kc, bf16* __restrict__ vc, int Hq,
+attn_prep_kernel(const bf16* qg, const bf16* k, const bf16* v,
+                 long ldp, const bf16* qnw, const bf16* knw,
+                 const float* inv_freq, const int* pos_ptr,
+                 bf16* q_out, bf16* kc, bf16* vc, int Hq,
                  int max_len, int rd, float eps) {
   dep_release();
   dep_wait();
@@ -62,22 +62,22 @@ attn_prep_kernel(const bf16* __restrict__ qg, const bf16* __restrict__ k, const 
 template <int HD>
 __device__ __forceinline__ void load_lane(const bf16* row, int lane, float (&f)[HD / 32]) {
   if constexpr (HD == 256) {
-    widen8(__ldg(reinterpret_cast<const uint4*>(row) + lane), f);
+    widen8(reinterpret_cast<const uint4*>(row)[lane], f);
   } else if constexpr (HD == 128) {
-    const uint2 p = __ldg(reinterpret_cast<const uint2*>(row) + lane);
+    const uint2 p = reinterpret_cast<const uint2*>(row)[lane];
     f[0] = __uint_as_float(p.x << 16); f[1] = __uint_as_float(p.x & 0xffff0000u);
     f[2] = __uint_as_float(p.y << 16); f[3] = __uint_as_float(p.y & 0xffff0000u);
   } else {
-    const uint32_t p = __ldg(reinterpret_cast<const uint32_t*>(row) + lane);
+    const uint32_t p = reinterpret_cast<const uint32_t*>(row)[lane];
     f[0] = __uint_as_float(p << 16); f[1] = __uint_as_float(p & 0xffff0000u);
   }
 }
 
 template <int HD>
 __global__ void __launch_bounds__(kSplitWarps * 32)
-attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
-                  const bf16* __restrict__ vc, const int* __restrict__ pos_ptr,
-                  float* __restrict__ part_o, float* __restrict__ part_ml, int Hq, int Hkv,
+attn_split_kernel(const bf16* q, const bf16* kc,
+                  const bf16* vc, const int* pos_ptr,
+                  float* part_o, float* part_ml, int Hq, int Hkv,
                   int max_len, float scale) {
   constexpr int E = HD / 32;
   dep_release();
@@ -175,8 +175,8 @@ attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
 
 template <int HD>
 __global__ void __launch_bounds__(HD)
-attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                  const bf16* __restrict__ qg, long ldp, bf16* __restrict__ out, long ldo, int Hq,
+attn_merge_kernel(const float* part_o, const float* part_ml,
+                  const bf16* qg, long ldp, bf16* out, long ldo, int Hq,
                   int NS) {
   dep_release();
   dep_wait();

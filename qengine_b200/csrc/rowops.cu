@@ -15,8 +15,8 @@ namespace {
 // Embedding gather. Semantics of embed_kernel (reference csrc/basic.cu:16-26): out[r] =
 // table[tok[r]], ids outside [0, V) give zeros. 16-byte copies when the rows allow it.
 // ---------------------------------------------------------------------------------------------
-__global__ void embed_rows_kernel(const bf16* __restrict__ table, const int* __restrict__ tok,
-                                  bf16* __restrict__ out, int H, int V, long ldo, int vec) {
+__global__ void embed_rows_kernel(const bf16* table, const int* tok,
+                                  bf16* out, int H, int V, long ldo, int vec) {
   dep_release();
   dep_wait();
   const int r = blockIdx.y;
@@ -44,8 +44,8 @@ __global__ void embed_rows_kernel(const bf16* __restrict__ table, const int* __r
 // ---------------------------------------------------------------------------------------------
 template <int PKT>
 __global__ void __launch_bounds__(256)
-rmsnorm1p_vec_kernel(bf16* __restrict__ x, const bf16* __restrict__ delta,
-                     const bf16* __restrict__ w, bf16* __restrict__ out, int H, long ldx, long ldd,
+rmsnorm1p_vec_kernel(bf16* x, const bf16* delta,
+                     const bf16* w, bf16* out, int H, long ldx, long ldd,
                      long ldo, float eps) {
   dep_release();
   dep_wait();
@@ -88,8 +88,8 @@ rmsnorm1p_vec_kernel(bf16* __restrict__ x, const bf16* __restrict__ delta,
 
 // Any H, any alignment: two passes over the row, same arithmetic per element.
 __global__ void __launch_bounds__(256)
-rmsnorm1p_any_kernel(bf16* __restrict__ x, const bf16* __restrict__ delta,
-                     const bf16* __restrict__ w, bf16* __restrict__ out, int H, long ldx, long ldd,
+rmsnorm1p_any_kernel(bf16* x, const bf16* delta,
+                     const bf16* w, bf16* out, int H, long ldx, long ldd,
                      long ldo, float eps) {
   dep_release();
   dep_wait();
@@ -119,8 +119,8 @@ constexpr int kGemvWarps = 8;
 
 template <int NR>
 __global__ void __launch_bounds__(kGemvWarps * 32)
-gemv_bf16_rows_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x,
-                      bf16* __restrict__ out, int N, int K, long ldx, long ldo) {
+gemv_bf16_rows_kernel(const bf16* W, const bf16* x,
+                      bf16* out, int N, int K, long ldx, long ldo) {
   dep_release();
   const int lane = threadIdx.x & 31;
   const int j = blockIdx.x * kGemvWarps + (threadIdx.x >> 5);
@@ -145,7 +145,7 @@ gemv_bf16_rows_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x,
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
           float xf[8];
-          widen8(__ldg(reinterpret_cast<const uint4*>(x + (long)r * ldx) + p0 + 32 * u), xf);
+          widen8(reinterpret_cast<const uint4*>(x + (long)r * ldx)[p0 + 32 * u], xf);
 #pragma unroll
           for (int e = 0; e < 8; ++e) acc[r] = fmaf(wf[e], xf[e], acc[r]);
         }
@@ -163,7 +163,7 @@ gemv_bf16_rows_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x,
 // ---------------------------------------------------------------------------------------------
 // SwiGLU on unfused [gate | up] rows: bf16(bf16(silu(g)) * u) (reference csrc/basic.cu:157-170).
 // ---------------------------------------------------------------------------------------------
-__global__ void swiglu_rows_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I,
+__global__ void swiglu_rows_kernel(const bf16* gu, bf16* out, int I,
                                    long ldg, long ldo) {
   dep_release();
   dep_wait();
@@ -209,8 +209,8 @@ __device__ __forceinline__ void block_best(float& v, int& i, float* sv, int* si)
 }
 
 __global__ void __launch_bounds__(256)
-argmax_slab_kernel(const bf16* __restrict__ x, int n, long ldx, float* __restrict__ pv,
-                   int* __restrict__ pi) {
+argmax_slab_kernel(const bf16* x, int n, long ldx, float* pv,
+                   int* pi) {
   dep_release();
   dep_wait();
   __shared__ float sv[32];
@@ -228,7 +228,7 @@ argmax_slab_kernel(const bf16* __restrict__ x, int n, long ldx, float* __restric
     const int k0 = p * 8;
     if (vec && k0 + 8 <= n) {
       float f[8];
-      widen8(__ldg(reinterpret_cast<const uint4*>(xr) + p), f);
+      widen8(reinterpret_cast<const uint4*>(xr)[p], f);
 #pragma unroll
       for (int e = 0; e < 8; ++e) merge(v, i, f[e], k0 + e);
     } else {
@@ -240,8 +240,8 @@ argmax_slab_kernel(const bf16* __restrict__ x, int n, long ldx, float* __restric
 }
 
 __global__ void __launch_bounds__(256)
-argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int nb,
-                    int* __restrict__ out, const int* __restrict__ idmap) {
+argmax_final_kernel(const float* pv, const int* pi, int nb,
+                    int* out, const int* idmap) {
   dep_release();
   dep_wait();
   __shared__ float sv[32];

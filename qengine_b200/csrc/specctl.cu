@@ -13,9 +13,9 @@
 namespace qb {
 namespace {
 
-__global__ void accept_rows_kernel(const int* __restrict__ in_tok, const int* __restrict__ am, int n,
-                                   int* __restrict__ ctl, int* __restrict__ next_tok,
-                                   int* __restrict__ log, int max_len) {
+__global__ void accept_rows_kernel(const int* in_tok, const int* am, int n,
+                                   int* ctl, int* next_tok,
+                                   int* log, int max_len) {
   dep_release();
   dep_wait();
   if (threadIdx.x != 0) return;
@@ -42,8 +42,8 @@ __global__ void accept_rows_kernel(const int* __restrict__ in_tok, const int* __
   ctl[3] = m;
 }
 
-__global__ void commit_rows_kernel(int* __restrict__ ctl, int* __restrict__ in_tok,
-                                   const int* __restrict__ am, const int* __restrict__ drafts, int k) {
+__global__ void commit_rows_kernel(int* ctl, int* in_tok,
+                                   const int* am, const int* drafts, int k) {
   dep_release();
   dep_wait();
   if (threadIdx.x != 0) return;
@@ -54,10 +54,10 @@ __global__ void commit_rows_kernel(int* __restrict__ ctl, int* __restrict__ in_t
   for (int j = 0; j < k; ++j) in_tok[1 + j] = drafts[j];
 }
 
-__global__ void mtp_select_rows_kernel(const int* __restrict__ ctl, int* __restrict__ mpos, int off,
-                                       const bf16* __restrict__ src, long lds,
-                                       bf16* __restrict__ dst, int H, const int* __restrict__ mtp_am,
-                                       int* __restrict__ draft0) {
+__global__ void mtp_select_rows_kernel(const int* ctl, int* mpos, int off,
+                                       const bf16* src, long lds,
+                                       bf16* dst, int H, const int* mtp_am,
+                                       int* draft0) {
   dep_release();
   dep_wait();
   const int m = ctl[3];
@@ -76,8 +76,8 @@ __global__ void mtp_select_rows_kernel(const int* __restrict__ ctl, int* __restr
 // drafts so that exactly `a` of them will be accepted. truth[p] is the known greedy token at
 // position p; draft j sits at position pos + 1 + j and becomes truth[p] for j < a and
 // (truth[p] + 1) mod vocab otherwise. a < 0 leaves the drafts alone. Only acts in verify mode.
-__global__ void force_drafts_kernel(int* __restrict__ in_tok, const int* __restrict__ ctl,
-                                    const int* __restrict__ truth, int truth_len, int a, int k,
+__global__ void force_drafts_kernel(int* in_tok, const int* ctl,
+                                    const int* truth, int truth_len, int a, int k,
                                     int vocab) {
   dep_release();
   dep_wait();

@@ -70,6 +70,12 @@ __device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
   asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
+template <int S>
+__device__ __forceinline__ uint32_t shr_fma(uint32_t w) {
+  uint32_t r;
+  asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(w), "r"(1u << (32 - S)));
+  return r;
+}
 // One k-step of 16: four A registers from one packed word, times two x pairs.
 __device__ __forceinline__ void kstep(float (&c)[4], uint32_t w, uint32_t b0, uint32_t b1) {
   constexpr uint32_t kNib = 0x000F000Fu, k128 = 0x43004300u, k136 = 0x43084308u;
@@ -77,8 +83,40 @@ __device__ __forceinline__ void kstep(float (&c)[4], uint32_t w, uint32_t b0, ui
   const uint32_t a1 = sub_bf16x2(and_or(w >> 4, kNib, k128), k136);
   const uint32_t a2 = sub_bf16x2(and_or(w >> 8, kNib, k128), k136);
   const uint32_t a3 = sub_bf16x2(and_or(w >> 12, kNib, k128), k136);
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The same k-step for fp16 activations. fp16 has a 10-bit mantissa, so the magic number 1024
+// (0x6400) takes a nibble either at bits 0..3 (value 1024 + u) or at bits 4..7 (1024 + 16 u) of a
+// half-word: one shift by 8 serves all four A registers instead of three shifts, which matters
+// because shifts and lop3 share the half-rate ALU pipe. 1024 + u - 1032 and
+// (1024 + 16 u) / 16 - 72 are both exactly u - 8 in fp16.
+__device__ __forceinline__ uint32_t fma_f16x2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+__device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ void kstep_f16(float (&c)[4], uint32_t w, uint32_t b0, uint32_t b1) {
+  constexpr uint32_t kLo = 0x000F000Fu, kHi = 0x00F000F0u, k1024 = 0x64006400u;
+  constexpr uint32_t k1032 = 0x64086408u;   // fp16x2 (1032, 1032)
+  constexpr uint32_t kSixteenth = 0x2C002C00u;  // fp16x2 (1/16, 1/16)
+  constexpr uint32_t kNeg72 = 0xD480D480u;      // fp16x2 (-72, -72)
+  const uint32_t w8 = w >> 8;
+  const uint32_t a0 = sub_f16x2(and_or(w, kLo, k1024), k1032);
+  const uint32_t a1 = fma_f16x2(and_or(w, kHi, k1024), kSixteenth, kNeg72);
+  const uint32_t a2 = sub_f16x2(and_or(w8, kLo, k1024), k1032);
+  const uint32_t a3 = fma_f16x2(and_or(w8, kHi, k1024), kSixteenth, kNeg72);
+  asm(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
       "{%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -117,16 +155,17 @@ __device__ __forceinline__ void load_x16(uint32_t (&xr)[8], const W4Args& a, int
   const int k = c * 64 + 16 * t;
   const bf16* xp = a.x + (long)r * a.ldx + k;
   if (vec && k + 16 <= a.K) {
-    const uint4 lo = __ldg(reinterpret_cast<const uint4*>(xp));
-    const uint4 hi = __ldg(reinterpret_cast<const uint4*>(xp) + 1);
+    // plain (coherent) loads: x was written by a preceding kernel that may have overlapped this one
+    const uint4 lo = reinterpret_cast<const uint4*>(xp)[0];
+    const uint4 hi = reinterpret_cast<const uint4*>(xp)[1];
     xr[0] = lo.x; xr[1] = lo.y; xr[2] = lo.z; xr[3] = lo.w;
     xr[4] = hi.x; xr[5] = hi.y; xr[6] = hi.z; xr[7] = hi.w;
   } else {
     const unsigned short* xs = reinterpret_cast<const unsigned short*>(xp);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const uint32_t e0 = (k + 2 * i < a.K) ? __ldg(xs + 2 * i) : 0u;
-      const uint32_t e1 = (k + 2 * i + 1 < a.K) ? __ldg(xs + 2 * i + 1) : 0u;
+      const uint32_t e0 = (k + 2 * i < a.K) ? xs[2 * i] : 0u;
+      const uint32_t e1 = (k + 2 * i + 1 < a.K) ? xs[2 * i + 1] : 0u;
       xr[i] = e0 | (e1 << 16);
     }
   }
@@ -226,13 +265,15 @@ __device__ __forceinline__ int range_owner(int total, int B, int u) {
 // range); false: grid (tiles, ksplit), slot = tile * ksplit + y.
 template <int EPI, bool STREAM>
 __device__ __forceinline__ void finish_segment(const W4Args& a, int tile, int gb, int ge,
-                                               bool first_of_cta, const float (&acc)[4], int lane) {
+                                               bool first_of_cta, const float (&acc)[4], int lane,
+                                               int B, int b) {
+  // B workers (CTAs, or warps in mode 4) own the contiguous unit ranges; b = this worker.
   const int G = a.G;
   if (ge - gb == G) {
     store_tile<EPI>(a, tile, acc, lane);
     return;
   }
-  const int slot = STREAM ? 2 * blockIdx.x + (first_of_cta ? 0 : 1) : tile * a.ksplit + blockIdx.y;
+  const int slot = STREAM ? 2 * b + (first_of_cta ? 0 : 1) : tile * a.ksplit + blockIdx.y;
   float* mine = a.ws + (long)slot * 128;
 #pragma unroll
   for (int i = 0; i < 4; ++i) __stcg(mine + i * 32 + lane, acc[i]);
@@ -254,7 +295,6 @@ __device__ __forceinline__ void finish_segment(const W4Args& a, int tile, int gb
       for (int i = 0; i < 4; ++i) f[i] += __ldcg(p + i * 32 + lane);
     }
   } else {
-    const int B = gridDim.x;
     const int first = range_owner(a.total, B, tile * G);
     const int lastb = range_owner(a.total, B, tile * G + G - 1);
     for (int c = first; c <= lastb; ++c) {
@@ -313,7 +353,7 @@ __global__ void __launch_bounds__(WARPS * 32) w4_stream_kernel(const W4Args a) {
       }
       __syncthreads();
     }
-    if (warp == 0) finish_segment<EPI, MODE == 2>(a, tile, gb, ge, u == u0, acc, lane);
+    if (warp == 0) finish_segment<EPI, MODE == 2>(a, tile, gb, ge, u == u0, acc, lane, gridDim.x, blockIdx.x);
     u += ge - gb;
   }
 }
@@ -415,7 +455,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) w4_ring_kernel(const W4Args 
   // Lane (r, t) multiplies x row r. Rows >= N feed mma columns that are never stored, so those
   // lanes simply read row N - 1 again: no zero fill, no branch. (Host guarantees K % 128 == 0,
   // 16-byte aligned x and ldx % 8 == 0 for this mode.)
-  const uint4* xlane = reinterpret_cast<const uint4*>(a.x + (long)min(r, a.N - 1) * a.ldx + 16 * t);
+  const uint4* xlane = reinterpret_cast<const uint4*>(a.x + (long)min(r, a.N - 1) * a.ldx + 16 * t);  // coherent loads
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   int tile = u0 / G;          // tile of the segment being accumulated
   int seg_begin = u0;         // first unit of that segment
@@ -436,13 +476,38 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) w4_ring_kernel(const W4Args 
         for (int w2 = 1; w2 < WARPS; ++w2) s += red[phase][w2][c][lane];
         f[c] = s;
       }
-      finish_segment<EPI, true>(a, tile, seg_begin - tile * G, seg_end - tile * G, seg_begin == u0, f, lane);
+      finish_segment<EPI, true>(a, tile, seg_begin - tile * G, seg_end - tile * G, seg_begin == u0, f, lane,
+                                gridDim.x, blockIdx.x);
     }
 #pragma unroll
     for (int c = 0; c < 4; ++c) acc[c] = 0.f;
     phase ^= 1;
     seg_begin = seg_end;
     ++tile;
+  };
+
+  // One unit: 16 rows x 128 k from the ring times this lane's 32 x values.
+  auto unit = [&](int slot, int idx, int g) {
+    const uint4* wp = wring + ((size_t)slot * SU + idx) * 64 + lane;
+    const uint4 w0 = wp[0], w1 = wp[32];
+    const __half* sp = sring + ((size_t)slot * SU + idx) * 16 + r;
+    const float slo = __half2float(sp[0]), shi = __half2float(sp[8]);
+    const uint4* xp = xlane + g * 16;  // 128 bf16 per group = 16 uint4
+    const uint4 x0 = xp[0], x1 = xp[1], x2 = xp[8], x3 = xp[9];
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    auto ks = [&](uint32_t w, uint32_t b0, uint32_t b1) { kstep(c, w, b0, b1); };
+    ks(w0.x, x0.x, x0.y);
+    ks(w0.y, x0.z, x0.w);
+    ks(w0.z, x1.x, x1.y);
+    ks(w0.w, x1.z, x1.w);
+    ks(w1.x, x2.x, x2.y);
+    ks(w1.y, x2.z, x2.w);
+    ks(w1.z, x3.x, x3.y);
+    ks(w1.w, x3.z, x3.w);
+    acc[0] = fmaf(slo, c[0], acc[0]);
+    acc[1] = fmaf(slo, c[1], acc[1]);
+    acc[2] = fmaf(shi, c[2], acc[2]);
+    acc[3] = fmaf(shi, c[3], acc[3]);
   };
 
   for (int st = 0; st < nstage; ++st) {
@@ -452,35 +517,61 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) w4_ring_kernel(const W4Args 
       atomicExch(&g_ring_error, 2);
     }
     const int ub = u0 + st * SU;
+    if (ok && ub + SU <= u1 && ub + SU <= (tile + 1) * G) {
+      // Whole stage inside the current tile: no per-unit checks. Units are taken in pairs whose
+      // operands are all fetched before the first mma, so two independent mma chains overlap.
+      const int gb = ub - tile * G + warp;
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      const int idx = warp + i * WARPS;  // unit of this stage owned by this warp
-      const int u = ub + idx;
-      // Tile boundaries inside the range that lie at or before u: close them. Every consumer
-      // warp closes every such boundary exactly once (here, or in the catch-up loop after the
-      // last stage), so the k-th barrier of each warp always belongs to the k-th boundary.
-      while (u >= (tile + 1) * G && (tile + 1) * G < u1) close_segment((tile + 1) * G);
-      if (u < u1 && ok) {
-        const int g = u - tile * G;
-        const uint4* wp = wring + ((size_t)slot * SU + idx) * 64 + lane;
-        const uint4 w0 = wp[0], w1 = wp[32];
-        const __half* sp = sring + ((size_t)slot * SU + idx) * 16 + r;
-        const float slo = __half2float(sp[0]), shi = __half2float(sp[8]);
-        const uint4* xp = xlane + g * 16;  // 128 bf16 per group = 16 uint4
-        const uint4 x0 = __ldg(xp), x1 = __ldg(xp + 1), x2 = __ldg(xp + 8), x3 = __ldg(xp + 9);
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
-        kstep(c, w0.x, x0.x, x0.y);
-        kstep(c, w0.y, x0.z, x0.w);
-        kstep(c, w0.z, x1.x, x1.y);
-        kstep(c, w0.w, x1.z, x1.w);
-        kstep(c, w1.x, x2.x, x2.y);
-        kstep(c, w1.y, x2.z, x2.w);
-        kstep(c, w1.z, x3.x, x3.y);
-        kstep(c, w1.w, x3.z, x3.w);
-        acc[0] = fmaf(slo, c[0], acc[0]);
-        acc[1] = fmaf(slo, c[1], acc[1]);
-        acc[2] = fmaf(shi, c[2], acc[2]);
-        acc[3] = fmaf(shi, c[3], acc[3]);
+      for (int i0 = 0; i0 < PER; i0 += 2) {
+        constexpr int P2 = PER >= 2 ? 2 : 1;
+        uint4 wq[P2][2], xq[P2][4];
+        float slo[P2], shi[P2];
+#pragma unroll
+        for (int j = 0; j < P2; ++j) {
+          const int idx = warp + (i0 + j) * WARPS;
+          const uint4* wp = wring + ((size_t)slot * SU + idx) * 64 + lane;
+          wq[j][0] = wp[0];
+          wq[j][1] = wp[32];
+          const __half* sp = sring + ((size_t)slot * SU + idx) * 16 + r;
+          slo[j] = __half2float(sp[0]);
+          shi[j] = __half2float(sp[8]);
+          const uint4* xp = xlane + (gb + (i0 + j) * WARPS) * 16;
+          xq[j][0] = xp[0]; xq[j][1] = xp[1]; xq[j][2] = xp[8]; xq[j][3] = xp[9];
+        }
+        float c[P2][4];
+#pragma unroll
+        for (int j = 0; j < P2; ++j) { c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.f; }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int j = 0; j < P2; ++j) {
+            kstep(c[j], wq[j][h].x, xq[j][2 * h].x, xq[j][2 * h].y);
+            kstep(c[j], wq[j][h].y, xq[j][2 * h].z, xq[j][2 * h].w);
+          }
+#pragma unroll
+          for (int j = 0; j < P2; ++j) {
+            kstep(c[j], wq[j][h].z, xq[j][2 * h + 1].x, xq[j][2 * h + 1].y);
+            kstep(c[j], wq[j][h].w, xq[j][2 * h + 1].z, xq[j][2 * h + 1].w);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < P2; ++j) {
+          acc[0] = fmaf(slo[j], c[j][0], acc[0]);
+          acc[1] = fmaf(slo[j], c[j][1], acc[1]);
+          acc[2] = fmaf(shi[j], c[j][2], acc[2]);
+          acc[3] = fmaf(shi[j], c[j][3], acc[3]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int idx = warp + i * WARPS;  // unit of this stage owned by this warp
+        const int u = ub + idx;
+        // Tile boundaries inside the range that lie at or before u: close them. Every consumer
+        // warp closes every such boundary exactly once (here, or in the catch-up loop after the
+        // last stage), so the k-th barrier of each warp always belongs to the k-th boundary.
+        while (u >= (tile + 1) * G && (tile + 1) * G < u1) close_segment((tile + 1) * G);
+        if (u < u1 && ok) unit(slot, idx, u - tile * G);
       }
     }
     __syncwarp();
@@ -488,6 +579,117 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) w4_ring_kernel(const W4Args 
   }
   while ((tile + 1) * G < u1) close_segment((tile + 1) * G);  // boundaries this warp never reached
   close_segment(u1);                                          // the last segment of the range
+}
+
+// ---------------------------------------------------------------------------------------------
+// MODE 4: warp-private rings. The unit stream is cut into one contiguous range per WARP (all
+// warps of all CTAs); each warp is a pipeline of its own: its lane 0 issues the bulk copies
+// (cp.async.bulk global -> shared, completion on an mbarrier) that keep STAGES stages of PERW
+// units of ITS range in flight, all lanes consume. No CTA barrier, no cross-warp reduction, no
+// producer warp: a warp walks the groups of a tile in order, stores a tile it owned entirely and
+// publishes a partial one to its scratch slot (at most the first and the last tile of its range),
+// where the last contributor adds the partials in ascending warp order. Inner loop per unit:
+// 2 LDS.128 + 2 LDS.16 (weights, scales), 4 coherent LDG.128 (x), 8 mma, no branch but the
+// tile-end test. Ranges depend on the launch shape only: deterministic and independent of N.
+// ---------------------------------------------------------------------------------------------
+template <int PERW, int STAGES, int EPI, bool XF16>
+__global__ void __launch_bounds__(256) w4_warp_ring_kernel(const W4Args a, int nworkers) {
+  constexpr int WARPS = 8;
+  constexpr uint32_t kStageW = PERW * 1024, kStageS = PERW * 32;
+  dep_release();
+  extern __shared__ __align__(128) unsigned char ring_raw[];
+  __shared__ uint64_t full[WARPS][STAGES];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int worker = blockIdx.x * WARPS + warp;
+  unsigned char* wbase = ring_raw + (size_t)warp * STAGES * (kStageW + kStageS);
+  unsigned char* sbase = wbase + (size_t)STAGES * kStageW;
+  const int G = a.G;
+  int u0 = 0, u1 = 0;
+  if (worker < nworkers) {
+    u0 = range_begin(a.total, nworkers, worker);
+    u1 = range_begin(a.total, nworkers, worker + 1);
+  }
+  const int nstage = (u1 - u0 + PERW - 1) / PERW;
+
+  if (lane == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&full[warp][s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  auto refill = [&](int st) {  // lane 0 only
+    const int slot = st % STAGES;
+    const int ub = u0 + st * PERW, cnt = min(PERW, u1 - ub);
+    mbar_expect_tx(&full[warp][slot], (uint32_t)cnt * (1024 + 32));
+    bulk_load(wbase + (size_t)slot * kStageW, a.qw + (size_t)ub * 64, (uint32_t)cnt * 1024, &full[warp][slot]);
+    bulk_load(sbase + (size_t)slot * kStageS, a.scales + (size_t)ub * 16, (uint32_t)cnt * 32, &full[warp][slot]);
+  };
+  if (lane == 0)
+    for (int st = 0; st < min(STAGES, nstage); ++st) refill(st);  // weights never depend on x
+  dep_wait();
+  if (nstage == 0) return;
+
+  const int r = lane >> 2, t = lane & 3;
+  const uint4* xlane = reinterpret_cast<const uint4*>(a.x + (long)min(r, a.N - 1) * a.ldx + 16 * t);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  int tile = u0 / G;
+  int g = u0 - tile * G;       // group of the next unit inside its tile
+  int seg_gb = g;              // first group of the segment being accumulated
+  bool first_seg = true;
+  bool ok = true;
+
+  auto one_unit = [&](const uint4* wp, const __half* sp) {
+    const uint4 w0 = wp[0], w1 = wp[32];
+    const float slo = __half2float(sp[0]), shi = __half2float(sp[8]);
+    const uint4* xp = xlane + g * 16;
+    const uint4 x0 = xp[0], x1 = xp[1], x2 = xp[8], x3 = xp[9];
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    auto ks = [&](uint32_t w, uint32_t b0, uint32_t b1) {
+      if constexpr (XF16) kstep_f16(c, w, b0, b1); else kstep(c, w, b0, b1);
+    };
+    ks(w0.x, x0.x, x0.y);
+    ks(w0.y, x0.z, x0.w);
+    ks(w0.z, x1.x, x1.y);
+    ks(w0.w, x1.z, x1.w);
+    ks(w1.x, x2.x, x2.y);
+    ks(w1.y, x2.z, x2.w);
+    ks(w1.z, x3.x, x3.y);
+    ks(w1.w, x3.z, x3.w);
+    acc[0] = fmaf(slo, c[0], acc[0]);
+    acc[1] = fmaf(slo, c[1], acc[1]);
+    acc[2] = fmaf(shi, c[2], acc[2]);
+    acc[3] = fmaf(shi, c[3], acc[3]);
+    if (++g == G) {  // tile finished
+      finish_segment<EPI, true>(a, tile, seg_gb, G, first_seg, acc, lane, nworkers, worker);
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      g = 0; seg_gb = 0; first_seg = false; ++tile;
+    }
+  };
+
+  for (int st = 0; st < nstage; ++st) {
+    const int slot = st % STAGES;
+    if (!mbar_wait(&full[warp][slot], (st / STAGES) & 1, ok ? (1 << 20) : 64)) {
+      ok = false;
+      atomicExch(&g_ring_error, 4);
+    }
+    const uint4* wp = reinterpret_cast<const uint4*>(wbase + (size_t)slot * kStageW) + lane;
+    const __half* sp = reinterpret_cast<const __half*>(sbase + (size_t)slot * kStageS) + r;
+    const int cnt = min(PERW, u1 - (u0 + st * PERW));
+    if (ok) {
+      if (cnt == PERW) {
+#pragma unroll
+        for (int i = 0; i < PERW; ++i) one_unit(wp + i * 64, sp + i * 16);
+      } else {
+        for (int i = 0; i < cnt; ++i) one_unit(wp + i * 64, sp + i * 16);
+      }
+    }
+    __syncwarp();
+    if (lane == 0 && st + STAGES < nstage) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      refill(st + STAGES);
+    }
+  }
+  if (g != seg_gb)  // the range ended inside a tile
+    finish_segment<EPI, true>(a, tile, seg_gb, g, first_seg, acc, lane, nworkers, worker);
 }
 
 using KernelFn = void (*)(const W4Args);
@@ -535,27 +737,58 @@ int blocks_per_sm(KernelFn fn, int threads) {
   return b;
 }
 
+using WarpKernelFn = void (*)(const W4Args, int);
+
 struct Resolved {
   qe_w4_plan plan;
   KernelFn fn;
   size_t smem = 0;
+  WarpKernelFn wfn = nullptr;  // mode 4
+  int nworkers = 0;            // mode 4: warps that own a range
 };
 
-// Ring geometry of mode 3: 8 consumer warps, 16 units (16.5 KB) per stage, 6 stages = 99 KB of
-// weights in flight per CTA, two CTAs per SM.
-constexpr int kRingWarps = 8, kRingSU = 16, kRingStages = 6;
-constexpr size_t kRingSmem = (size_t)kRingStages * kRingSU * (1024 + 32);
+// Geometries of mode 4 (8 warps per CTA, one private ring per warp), chosen by `unroll`:
+//   unroll 0/4: 4 units per stage x 3 stages = 12.4 KB per warp, 99 KB per CTA, 2 CTAs per SM
+//   unroll 2  : 2 units per stage x 6 stages = same bytes, finer refill
+//   unroll 1  : 4 units per stage x 2 stages = 66 KB per CTA, 3 CTAs per SM
+struct WarpGeom {
+  WarpKernelFn fn[4];  // [epilogue + 2 * x_is_fp16]
+  size_t smem;
+  int bps;
+};
+template <int PERW, int ST>
+WarpGeom warp_geom(int bps) {
+  WarpGeom g{{w4_warp_ring_kernel<PERW, ST, QE_EPI_NONE, false>, w4_warp_ring_kernel<PERW, ST, QE_EPI_SWIGLU, false>,
+              w4_warp_ring_kernel<PERW, ST, QE_EPI_NONE, true>, w4_warp_ring_kernel<PERW, ST, QE_EPI_SWIGLU, true>},
+             (size_t)8 * ST * PERW * (1024 + 32), bps};
+  for (WarpKernelFn f : g.fn) cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
+  return g;
+}
+const WarpGeom& warp_geom_for(int unroll) {
+  static const WarpGeom g4 = warp_geom<4, 3>(2), g2 = warp_geom<2, 6>(2), g1 = warp_geom<4, 2>(3);
+  return unroll == 2 ? g2 : unroll == 4 ? g4 : g1;  // default: 3 CTAs per SM
+}
 
-KernelFn ring_kernel(int epi) {
-  static bool configured = false;
-  KernelFn a = w4_ring_kernel<kRingWarps, kRingSU, kRingStages, QE_EPI_NONE>;
-  KernelFn b = w4_ring_kernel<kRingWarps, kRingSU, kRingStages, QE_EPI_SWIGLU>;
-  if (!configured) {
-    cudaFuncSetAttribute(a, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingSmem);
-    cudaFuncSetAttribute(b, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingSmem);
-    configured = true;
-  }
-  return epi == QE_EPI_SWIGLU ? b : a;
+// Ring geometries of mode 3 (8 consumer warps + 1 producer warp per CTA), chosen by `unroll`:
+//   unroll 0/2: 16 units (16.5 KB) per stage x 6 stages = 99 KB in flight per CTA, 2 CTAs per SM
+//   unroll 4  : 32 units (33 KB) per stage x 3 stages   = 99 KB, 4 independent units per warp
+//   unroll 1  : 16 units per stage x 4 stages           = 66 KB, 3 CTAs per SM
+constexpr int kRingWarps = 8;
+struct RingGeom {
+  KernelFn fn[2];
+  size_t smem;
+  int bps;
+};
+template <int SU, int ST>
+RingGeom ring_geom(int bps) {
+  RingGeom g{{w4_ring_kernel<kRingWarps, SU, ST, QE_EPI_NONE>, w4_ring_kernel<kRingWarps, SU, ST, QE_EPI_SWIGLU>},
+             (size_t)ST * SU * (1024 + 32), bps};
+  for (KernelFn f : g.fn) cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
+  return g;
+}
+const RingGeom& ring_for(int unroll) {
+  static const RingGeom g2 = ring_geom<16, 6>(2), g4 = ring_geom<32, 3>(2), g1 = ring_geom<16, 4>(3);
+  return unroll == 4 ? g4 : unroll == 1 ? g1 : g2;
 }
 
 // Shape-only policy (never N). B200: 148 SMs; every matrix of the 27B model except the tiniest
@@ -566,18 +799,36 @@ Resolved resolve(const qe_w4_params& p, const qe_w4_cfg& in) {
   qe_w4_cfg c = in;
   const long tiles = p.Mp / 16, G = p.Kp / 128, units = tiles * G;
   const int sms = qe_sm_count();
-  const int auto_mode = units < 4096 ? 0 : 2;
-  int mode = (c.mode == 0 || c.mode == 2 || c.mode == 3) ? c.mode : auto_mode;
+  const int auto_mode = units < 4096 ? 0 : 4;  // warp-private rings for every large matrix
+  int mode = (c.mode == 0 || c.mode == 2 || c.mode == 3 || c.mode == 4) ? c.mode : auto_mode;
   if (units >= (1L << 30)) mode = 0;  // 32-bit unit arithmetic in the stream modes
-  // The ring path serves the aligned fast case only (every matrix of the model qualifies).
-  if (mode == 3 && (p.K != p.Kp || (p.ldx & 7) || (reinterpret_cast<uintptr_t>(p.x) & 15))) mode = 2;
+  // The ring paths serve the aligned fast case only (every matrix of the model qualifies).
+  if (mode >= 3 && (p.K != p.Kp || (p.ldx & 7) || (reinterpret_cast<uintptr_t>(p.x) & 15))) mode = 2;
+  if (p.x_f16) mode = 4;  // fp16 activations are served by the warp-ring kernel only
+  if (mode == 4) {
+    const WarpGeom& wg = warp_geom_for(c.unroll);
+    r.wfn = wg.fn[(p.epilogue == QE_EPI_SWIGLU ? 1 : 0) + (p.x_f16 ? 2 : 0)];
+    r.smem = wg.smem;
+    r.plan.mode = 4;
+    r.plan.threads = 256;
+    r.plan.counters = tiles;
+    const int bps = c.blocks_per_sm > 0 ? c.blocks_per_sm : wg.bps;
+    const long want = (units + std::max(1, c.min_units) - 1) / std::max(1, c.min_units);
+    const long workers = std::max<long>(1, std::min<long>((long)sms * bps * 8, want));
+    r.nworkers = (int)workers;
+    r.plan.grid_x = (int)((workers + 7) / 8);
+    r.plan.grid_y = 1;
+    r.plan.ws_floats = workers * 2 * 128;
+    return r;
+  }
   if (mode == 3) {
-    r.fn = ring_kernel(p.epilogue);
-    r.smem = kRingSmem;
+    const RingGeom& rg = ring_for(c.unroll);
+    r.fn = rg.fn[p.epilogue == QE_EPI_SWIGLU ? 1 : 0];
+    r.smem = rg.smem;
     r.plan.mode = 3;
     r.plan.threads = (kRingWarps + 1) * 32;
     r.plan.counters = tiles;
-    const int bps = c.blocks_per_sm > 0 ? c.blocks_per_sm : 2;
+    const int bps = c.blocks_per_sm > 0 ? c.blocks_per_sm : rg.bps;
     const long per_block = (long)std::max(1, c.min_units) * kRingWarps;
     const long blocks = std::max<long>(1, std::min<long>((long)sms * bps, (units + per_block - 1) / per_block));
     r.plan.grid_x = (int)blocks;
@@ -665,6 +916,9 @@ extern "C" int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* str
   a.ksplit = r.plan.grid_y;
   a.total = a.tiles * a.G;
   const bool pdl = cfg->pdl && pdl_launch_enabled() && pdl_trigger_enabled();
+  if (r.plan.mode == 4)
+    return (int)launch(r.wfn, dim3(r.plan.grid_x, 1, 1), dim3(r.plan.threads), r.smem,
+                       (cudaStream_t)stream, pdl, a, r.nworkers);
   return (int)launch(r.fn, dim3(r.plan.grid_x, r.plan.grid_y, 1), dim3(r.plan.threads), r.smem,
                      (cudaStream_t)stream, pdl, a);
 }

@@ -27,7 +27,8 @@ ODD_SHAPES = [(1, 1), (1, 128), (7, 127), (16, 129), (127, 1000), (1000, 4097), 
 CFGS = [dict(), dict(warps=4), dict(warps=16), dict(unroll=1), dict(unroll=4), dict(warps=16, unroll=1),
         dict(mode=0), dict(mode=0, ksplit=2), dict(mode=0, ksplit=7), dict(mode=2), dict(mode=2, min_units=1),
         dict(mode=2, warps=4, unroll=1), dict(variant=1), dict(pdl=False), dict(mode=3),
-        dict(mode=3, blocks_per_sm=1, min_units=1)]
+        dict(mode=3, blocks_per_sm=1, min_units=1), dict(mode=4), dict(mode=4, unroll=2, min_units=1),
+        dict(mode=4, unroll=1, blocks_per_sm=1)]
 
 
 @pytest.fixture(scope="module")
@@ -104,7 +105,7 @@ def test_odd_shapes(api, M, K):
 
 
 @pytest.mark.parametrize("mode,ksplit,min_units", [(0, 1, 4), (0, 2, 4), (0, 3, 4), (0, 7, 4), (0, 40, 4),
-                                                  (2, 0, 1), (2, 0, 4), (-1, 0, 4), (3, 0, 1), (3, 0, 4)])
+                                                  (2, 0, 1), (2, 0, 4), (-1, 0, 4), (3, 0, 1), (3, 0, 4), (4, 0, 1), (4, 0, 4)])
 @pytest.mark.parametrize("warps,unroll", [(4, 1), (8, 2), (8, 4), (16, 1)])
 def test_launch_configs(api, mode, ksplit, min_units, warps, unroll):
     p = api["q"](rand_w(1000, 5120, seed=9))
@@ -281,7 +282,8 @@ def test_ring_mode_all_row_counts(api, name):
     ref = x.float() @ Wd.T
     bnd = bound(x, Wd, ref)
     for N in (1, 2, 5, 8):
-        check(api["gemv"](x[:N].contiguous(), p, mode=3), ref[:N], bnd[:N], f"ring {name} N={N}")
+        for mode in (3, 4):
+            check(api["gemv"](x[:N].contiguous(), p, mode=mode), ref[:N], bnd[:N], f"ring mode {mode} {name} N={N}")
     assert api["w4"].ring_error() == 0
 
 
