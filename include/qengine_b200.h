@@ -192,6 +192,20 @@ int qe_w4_plan_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, qe_w4_plan* pla
 int qe_w4_auto_ksplit(int Mp, int Kp, int N, int warps);
 /* Replaces launch_gemv_w4 (gemv_w4.h:56). */
 int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
+/* Has no counterpart in the reference. The same GEMV as qe_w4_gemv for callers that cannot
+ * allocate device memory (a plugin inside another runtime's callback, code running between the
+ * capture and the replay of a graph, an embedder that may not call its allocator): p->ws and
+ * p->counters are ignored and the scratch comes from a fixed array inside the library instead,
+ * QE_W4_STATIC_WS_FLOATS fp32 slots + QE_W4_STATIC_COUNTERS counters (about 4.1 MiB per GPU, held
+ * until exit). A shape / configuration whose plan needs more returns QE_ERR_SCRATCH. The first
+ * call on a device looks the array's device address up (make it before any stream capture);
+ * nothing is ever allocated or freed. All calls share the array: calls that overlap on the GPU
+ * race, so keep them on one stream. `cfg->pdl` is ignored (plain stream order). */
+#define QE_W4_STATIC_WS_FLOATS (1L << 20)
+#define QE_W4_STATIC_COUNTERS (1L << 14)
+#define QE_ERR_SCRATCH (-28)
+int qe_w4_gemv_static(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
+
 /* Mode 3 (shared-memory ring fed by bulk copies) bounds every barrier wait; this returns the
  * sticky error word those waits set on expiry (0 = none). Synchronises with the device. No
  * counterpart in the reference. */

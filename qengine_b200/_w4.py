@@ -134,3 +134,38 @@ def auto_ksplit(Mp, Kp, N, warps=8):
 def ring_error():
     """Sticky error word of mode 3's bounded barrier waits (0 = none); synchronises."""
     return int(lib.qe_w4_ring_error())
+
+
+def gemv_static(x, qw, scales, out, M, swiglu=False, warps=0, unroll=0, ksplit=0, variant=0, mode=-1,
+                blocks_per_sm=0, min_units=4):
+    """The W4 GEMV for callers that must not allocate (no counterpart in the reference).
+
+    `gemv` keeps its partial-sum scratch in torch tensors that may have to grow, i.e. it can reach
+    the CUDA allocator. A host that runs where allocation is off limits -- inside another runtime's
+    callback, between the capture and the replay of a graph, under a memory pool it does not own --
+    calls this instead: the scratch is a fixed array inside the library (about 4.1 MiB per GPU),
+    nothing is allocated, and a shape whose launch plan needs more than that array raises
+    RuntimeError. The first call on a device resolves the array's address and should come before
+    any stream capture. All calls share the array, so calls that overlap on the GPU race: keep
+    them on one stream. Same validation and results as `gemv` / `gemv_swiglu`."""
+    for t in (x, qw, scales, out):
+        _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
+    _req(x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "x and out must be bf16")
+    _req(qw.dtype == torch.int32 and qw.dim() == 4 and qw.size(2) == 32 and qw.size(3) == 4 and qw.is_contiguous(),
+         "qw must be contiguous int32 [Mp/16, Kp/64, 32, 4]")
+    _req(scales.dtype == torch.float16 and scales.dim() == 3 and scales.size(2) == 16 and scales.is_contiguous(),
+         "scales must be contiguous fp16 [Mp/16, Kp/128, 16]")
+    _req(x.dim() == 2 and out.dim() == 2 and x.stride(1) == 1 and out.stride(1) == 1, "x [N,K], out [N,M] rows")
+    N, K, M = x.size(0), x.size(1), int(M)
+    Mp, Kp = qw.size(0) * 16, qw.size(1) * 64
+    _req(1 <= N <= 8 and out.size(0) == N and out.size(1) == M, "N in 1..8 and out [N, M]")
+    _req(scales.size(0) == qw.size(0) and scales.size(1) * 128 == Kp and Kp - 128 < K <= Kp, "shapes disagree")
+    _req((Mp // 2 - 8 < M <= Mp // 2) if swiglu else (Mp - 16 < M <= Mp), "out width must match packed rows")
+    p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None, M, K, Mp, Kp, N,
+                 x.stride(0), out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, 0)
+    cfg = W4Cfg(int(warps), int(unroll), int(ksplit), 0, int(variant), int(mode), int(blocks_per_sm), int(min_units))
+    code = lib.qe_w4_gemv_static(C.byref(p), C.byref(cfg), torch.cuda.current_stream().cuda_stream)
+    _req(code != -28, "gemv_static: this shape needs more scratch than the library's fixed array "
+                      "(1 Mi partial-sum floats, 16 Ki tile counters); use gemv with caller scratch")
+    _req(code == 0, f"gemv_static failed: error {code}")
+    launches[0] += 1

@@ -922,3 +922,70 @@ extern "C" int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* str
   return (int)launch(r.fn, dim3(r.plan.grid_x, r.plan.grid_y, 1), dim3(r.plan.threads), r.smem,
                      (cudaStream_t)stream, pdl, a);
 }
+
+// ---------------------------------------------------------------------------------------------
+// qe_w4_gemv_static: the same GEMV for callers that cannot allocate device memory.
+//
+// qe_w4_gemv needs two scratch buffers from its caller (fp32 partial-tile slots and int32 arrival
+// counters). Some hosts have no way to provide them: a plugin that runs inside another runtime's
+// callback where cudaMalloc is forbidden, code that executes between the capture and the replay
+// of a CUDA graph and must not touch the allocator, or an embedder whose memory pool is owned by
+// a framework it may not call back into. For them the scratch lives in this library instead, in
+// a file-scope device array of fixed size that every GPU loading the library holds until exit:
+// QE_W4_STATIC_WS_FLOATS fp32 slots (4 MiB) + QE_W4_STATIC_COUNTERS counters (64 KiB).
+//
+// The array's name is only a host-side handle. Its device address is looked up with
+// cudaGetSymbolAddress once per device, on the first call made while that device is current
+// (so make that first call before any stream capture), and that pointer is what the kernel
+// receives. No cudaMalloc, cudaFree or allocating library routine is called here.
+// Every call uses the same array and finds in it whatever the previous call left; the counters,
+// which must start at zero, are cleared on the stream before each launch. Two calls that overlap
+// on the GPU (different streams) therefore race on the scratch: serialise them.
+// ---------------------------------------------------------------------------------------------
+namespace qb {
+namespace {
+static __device__ __align__(256) unsigned char
+    g_w4_static_scratch[(size_t)QE_W4_STATIC_COUNTERS * 4 + (size_t)QE_W4_STATIC_WS_FLOATS * 4];
+
+// Device address of the scratch array on the current device (looked up once per device).
+cudaError_t static_scratch(unsigned char** out) {
+  static unsigned char* per_dev[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!per_dev[dev]) {
+    unsigned char* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_w4_static_scratch);
+    if (e != cudaSuccess) return e;
+    per_dev[dev] = ptr;
+  }
+  *out = per_dev[dev];
+  return cudaSuccess;
+}
+}  // namespace
+}  // namespace qb
+
+extern "C" int qe_w4_gemv_static(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream) {
+  if (!p || !cfg) return QE_ERR_ARG;
+  if (p->N < 1 || p->N > QE_MAX_ROWS || p->Mp % 16 || p->Kp % 128 || p->Mp <= 0 || p->Kp <= 0)
+    return QE_ERR_ARG;
+  qe_w4_plan plan;
+  int rc = qe_w4_plan_gemv(p, cfg, &plan);
+  if (rc) return rc;
+  if (plan.ws_floats > QE_W4_STATIC_WS_FLOATS || plan.counters > QE_W4_STATIC_COUNTERS)
+    return QE_ERR_SCRATCH;  // this shape / launch configuration needs more than the fixed array
+  unsigned char* base = nullptr;
+  cudaError_t e = static_scratch(&base);
+  if (e != cudaSuccess) return (int)e;
+  int* counters = reinterpret_cast<int*>(base);
+  float* ws = reinterpret_cast<float*>(base + (size_t)QE_W4_STATIC_COUNTERS * 4);
+  e = cudaMemsetAsync(counters, 0, (size_t)plan.counters * 4, (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  qe_w4_params q = *p;
+  q.ws = ws;
+  q.counters = counters;
+  qe_w4_cfg c = *cfg;
+  c.pdl = 0;  // the launch follows a memset on the stream: plain stream order
+  return qe_w4_gemv(&q, &c, stream);
+}
