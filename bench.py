@@ -286,7 +286,7 @@ def run_ours(a):
         torch.cuda.synchronize()
 
     cfg = synth.qwen27b_config(layers=a.layers)
-    n_new, P = a.tokens, PROMPT_LEN
+    n_new, P = a.tokens, a.prompt
     W = synth.build_model(cfg, seed=1, device=dev, scale_std=0.01)
     eng = Engine(cfg, W, max_len=P + n_new + 32, device=dev)
     prompt = synth.prompt_ids(P, cfg.vocab, seed=1234 + (rank if world > 1 else 0))
@@ -385,6 +385,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=64, help="model depth (64 = the 27B shape)")
     ap.add_argument("--tokens", type=int, default=N_NEW, help="generated tokens per step")
+    ap.add_argument("--prompt", type=int, default=PROMPT_LEN, help="prompt length (profiling runs use a short one)")
     ap.add_argument("--no-mtp", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     a = ap.parse_args()

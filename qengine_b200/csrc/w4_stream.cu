@@ -258,16 +258,15 @@ __device__ __forceinline__ int range_owner(int total, int B, int u) {
   return u < big ? u / (per + 1) : rem + (u - big) / per;
 }
 
-// Warp 0 finishes a segment [gb, ge) of `tile` whose warp-reduced sums it holds: a whole tile is
-// stored; a partial one is published to this CTA's scratch slot and the contributor that completes
-// the tile (integer arrival count of groups) adds all slots in a fixed order and stores.
-// STREAM = true: CTAs own contiguous unit ranges (two slots per CTA: first / last tile of its
-// range); false: grid (tiles, ksplit), slot = tile * ksplit + y.
+// A warp finishes a segment [gb, ge) of `tile` whose sums it holds: a whole tile is stored; a
+// partial one is published to this worker's scratch slot and the contributor that completes the
+// tile (integer arrival count of groups) adds all slots in a fixed order and stores.
+// STREAM = true: workers (CTAs, or warps in mode 4) own contiguous unit ranges, two slots each
+// (first / last tile of the range); false: grid (tiles, ksplit), slot = tile * ksplit + y.
 template <int EPI, bool STREAM>
 __device__ __forceinline__ void finish_segment(const W4Args& a, int tile, int gb, int ge,
                                                bool first_of_cta, const float (&acc)[4], int lane,
                                                int B, int b) {
-  // B workers (CTAs, or warps in mode 4) own the contiguous unit ranges; b = this worker.
   const int G = a.G;
   if (ge - gb == G) {
     store_tile<EPI>(a, tile, acc, lane);
@@ -295,11 +294,12 @@ __device__ __forceinline__ void finish_segment(const W4Args& a, int tile, int gb
       for (int i = 0; i < 4; ++i) f[i] += __ldcg(p + i * 32 + lane);
     }
   } else {
+    // Worker c contributed its first segment (slot 2c) if its range starts inside this tile,
+    // otherwise (its range starts in an earlier tile) its last one (slot 2c + 1).
     const int first = range_owner(a.total, B, tile * G);
     const int lastb = range_owner(a.total, B, tile * G + G - 1);
+#pragma unroll 1
     for (int c = first; c <= lastb; ++c) {
-      // CTA c contributed its first segment if its range starts inside this tile, otherwise
-      // (its range starts in an earlier tile) its last segment.
       const int cs = range_begin(a.total, B, c);
       const float* p = a.ws + (long)(2 * c + (cs >= tile * G ? 0 : 1)) * 128;
 #pragma unroll
@@ -592,8 +592,8 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) w4_ring_kernel(const W4Args 
 // 2 LDS.128 + 2 LDS.16 (weights, scales), 4 coherent LDG.128 (x), 8 mma, no branch but the
 // tile-end test. Ranges depend on the launch shape only: deterministic and independent of N.
 // ---------------------------------------------------------------------------------------------
-template <int PERW, int STAGES, int EPI, bool XF16>
-__global__ void __launch_bounds__(256) w4_warp_ring_kernel(const W4Args a, int nworkers) {
+template <int PERW, int STAGES, int EPI, bool XF16, int MINB>
+__global__ void __launch_bounds__(256, MINB) w4_warp_ring_kernel(const W4Args a, int nworkers) {
   constexpr int WARPS = 8;
   constexpr uint32_t kStageW = PERW * 1024, kStageS = PERW * 32;
   dep_release();
@@ -756,16 +756,23 @@ struct WarpGeom {
   size_t smem;
   int bps;
 };
-template <int PERW, int ST>
+template <int PERW, int ST, int MINB>
 WarpGeom warp_geom(int bps) {
-  WarpGeom g{{w4_warp_ring_kernel<PERW, ST, QE_EPI_NONE, false>, w4_warp_ring_kernel<PERW, ST, QE_EPI_SWIGLU, false>,
-              w4_warp_ring_kernel<PERW, ST, QE_EPI_NONE, true>, w4_warp_ring_kernel<PERW, ST, QE_EPI_SWIGLU, true>},
+  WarpGeom g{{w4_warp_ring_kernel<PERW, ST, QE_EPI_NONE, false, MINB>,
+              w4_warp_ring_kernel<PERW, ST, QE_EPI_SWIGLU, false, MINB>,
+              w4_warp_ring_kernel<PERW, ST, QE_EPI_NONE, true, MINB>,
+              w4_warp_ring_kernel<PERW, ST, QE_EPI_SWIGLU, true, MINB>},
              (size_t)8 * ST * PERW * (1024 + 32), bps};
   for (WarpKernelFn f : g.fn) cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
   return g;
 }
-const WarpGeom& warp_geom_for(int unroll) {
-  static const WarpGeom g4 = warp_geom<4, 3>(2), g2 = warp_geom<2, 6>(2), g1 = warp_geom<4, 2>(3);
+// variant 1 selects the half-SM geometries: 2 CTAs x 50 KB and at most 64 registers per thread, so
+// that the CTAs of the next kernel of the stream fit beside the running ones and fill their rings
+// before their programmatic-dependency wait ends.
+const WarpGeom& warp_geom_for(int unroll, int variant) {
+  static const WarpGeom g4 = warp_geom<4, 3, 1>(2), g2 = warp_geom<2, 6, 1>(2), g1 = warp_geom<4, 2, 1>(3);
+  static const WarpGeom h2 = warp_geom<2, 3, 4>(2), h3 = warp_geom<3, 2, 4>(2);
+  if (variant == 1) return unroll == 4 ? h3 : h2;
   return unroll == 2 ? g2 : unroll == 4 ? g4 : g1;  // default: 3 CTAs per SM
 }
 
@@ -806,7 +813,7 @@ Resolved resolve(const qe_w4_params& p, const qe_w4_cfg& in) {
   if (mode >= 3 && (p.K != p.Kp || (p.ldx & 7) || (reinterpret_cast<uintptr_t>(p.x) & 15))) mode = 2;
   if (p.x_f16) mode = 4;  // fp16 activations are served by the warp-ring kernel only
   if (mode == 4) {
-    const WarpGeom& wg = warp_geom_for(c.unroll);
+    const WarpGeom& wg = warp_geom_for(c.unroll, c.variant);
     r.wfn = wg.fn[(p.epilogue == QE_EPI_SWIGLU ? 1 : 0) + (p.x_f16 ? 2 : 0)];
     r.smem = wg.smem;
     r.plan.mode = 4;
