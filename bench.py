@@ -32,9 +32,11 @@ sys.path.insert(0, str(ROOT))
 
 PROMPT_LEN, N_NEW = 128, 1024
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of w4_stream_kernel, from the ncu
-# capture summarised in profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of w4_warp_ring_kernel, from the
+# ncu capture summarised in profiles/w4_warp_ring_kernel_27b_shapes.md: 16.28 / 16.22, 95.87 / 91.95
+# and 46.07 / 45.99 MB on out_proj, gate_up and down (the excess on gate_up is partial-tile scratch
+# written back from L2). Scaled to an average launch of the 257-launch sequence below.
+NCU_TRAFFIC_RATIO = (16.28 + 95.87 + 46.07) / (16.22 + 91.95 + 45.99)
 
 
 def measured_peak():
@@ -153,7 +155,7 @@ def run_reference_arm(a):
     line = {
         "impl": "reference", "metric": "batch-1 decode tok/s (plain)", "value": tok_s, "unit": "tok/s",
         "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": per_tok * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "27B-shape W4A16 plain greedy decode, 128-token prompt, 1,024 tokens",
                    "timing": "host wall clock, CPU only"},
         "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": desc},
@@ -251,6 +253,36 @@ def mlp_pair_timing(eng, n_rows, reps=20):
     return us, nbytes / (us * 1e-6) / 1e9
 
 
+def exchange_timing(eng, reps=10, count=128):
+    """One tensor-parallel exchange (all-gather of a rank's fp32 partial row, then the residual
+    norm that sums the parts) timed as a graph of `count` of them. Every rank must call this."""
+    import torch
+    from qengine_b200 import _C
+    h, w = eng.h[:1], eng.final_norm
+
+    def body():
+        for _ in range(count):
+            eng.tp.all_gather(eng.parts[1], eng.part32[:1])
+            _C.rmsnorm1p_parts(h, eng.parts[1], w, eng.xn[:1], eng.cfg.eps)
+
+    eng.part32.zero_()
+    body()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, capture_error_mode="thread_local"):
+        body()
+    ms = []
+    for i in range(reps + 3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            ms.append(e0.elapsed_time(e1))
+    return statistics.median(ms) * 1e3 / count
+
+
 def bytes_per_token(eng, mean_ctx):
     """Algorithmic HBM bytes of one plain decode step at context length mean_ctx."""
     from qengine_b200 import synth
@@ -287,9 +319,14 @@ def run_ours(a):
 
     cfg = synth.qwen27b_config(layers=a.layers)
     n_new, P = a.tokens, a.prompt
-    W = synth.build_model(cfg, seed=1, device=dev, scale_std=0.01)
-    eng = Engine(cfg, W, max_len=P + n_new + 32, device=dev)
-    prompt = synth.prompt_ids(P, cfg.vocab, seed=1234 + (rank if world > 1 else 0))
+    if world == 1:
+        W = synth.build_model(cfg, seed=1, device=dev, scale_std=0.01)
+        eng = Engine(cfg, W, max_len=P + n_new + 32, device=dev)
+    else:  # tensor parallel: one sequence, every matrix sharded over the ranks
+        from qengine_b200 import tp
+        W = tp.build_sharded_model(cfg, world, rank, seed=1, device=dev, scale_std=0.01)
+        eng = Engine(cfg, W, max_len=P + n_new + 32, device=dev, tp=tp.TPGroup())
+    prompt = synth.prompt_ids(P, cfg.vocab, seed=1234)
 
     # ---- warm-up (captures the graphs) and timed plain decode ------------------------------
     for _ in range(max(1, a.warmup)):
@@ -309,12 +346,28 @@ def run_ours(a):
     if world > 1:
         dist.all_reduce(t_dec, op=dist.ReduceOp.MAX)
     dec_total, e2e_total = t_dec.tolist()
-    tokens_all = world * a.steps * (n_new - 1)
-    value = tokens_all / dec_total
-    e2e = world * a.steps * n_new / e2e_total
+    value = a.steps * (n_new - 1) / dec_total
+    e2e = a.steps * n_new / e2e_total
     kernels_per_token = eng.graph_kernels[(1, False, 0, False)]
     launches = a.steps * ((n_new - 1) * kernels_per_token +
                           sum(eng.graph_kernels[k] for k in eng._prefill_keys(P, False, 0)) * (P // 8))
+
+    # ---- MTP k = 4 (every rank takes part: the passes hold collectives) -----------------------
+    mtp = {}
+    if not a.no_mtp:
+        truth = prompt + gen + [0] * 64
+        for label, fa in [("natural", None)] + [(f"a{i}", i) for i in range(5)]:
+            kw = dict(force_accept=fa, truth=truth) if fa is not None else {}
+            eng.generate_spec(prompt, n_new, 4, **kw)  # capture + warm
+            barrier()
+            out, _, d, st = eng.generate_spec(prompt, n_new, 4, timing=True, **kw)
+            td = torch.tensor([d], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(td, op=dist.ReduceOp.MAX)
+            d = float(td.item())
+            mtp[label] = {"tok_s": (n_new - 1) / d, "tokens_per_cycle": st["tokens_per_cycle"],
+                          "ms_per_cycle": d * 1e3 / max(1, st["cycles"]), "identical_to_plain": out == gen}
+    exchange_us = exchange_timing(eng) if world > 1 else None
 
     line = {}
     if rank == 0:
@@ -328,21 +381,12 @@ def run_ours(a):
         pair5_us, pair5_gbs = mlp_pair_timing(eng, 5)
         achieved = seq_bytes / (seq_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": f"of {peak_kind}",
-                    "kernel": "w4_stream_kernel",
+                    "traffic": NCU_TRAFFIC_RATIO * seq_bytes / seq_launches, "peak_kind": f"of {peak_kind}",
+                    "per_launch": {"algorithmic_bytes": seq_bytes / seq_launches,
+                                   "avg_us": seq_ms * 1e3 / seq_launches},
+                    "kernel": "w4_warp_ring_kernel",
                     "how": f"{seq_launches} launches (every W4 matrix of one token, in order) as one graph, "
                            f"median of 10 CUDA-event timings; bytes = packed weights + scales + x + out"}
-        # ---- MTP k = 4 ---------------------------------------------------------------------
-        mtp = {}
-        if not a.no_mtp:
-            truth = prompt + gen + [0] * 64
-            for label, fa in [("natural", None)] + [(f"a{i}", i) for i in range(5)]:
-                kw = dict(force_accept=fa, truth=truth) if fa is not None else {}
-                eng.generate_spec(prompt, n_new, 4, **kw)  # capture + warm
-                out, _, d, st = eng.generate_spec(prompt, n_new, 4, timing=True, **kw)
-                mtp[label] = {"tok_s": (n_new - 1) / d, "tokens_per_cycle": st["tokens_per_cycle"],
-                              "ms_per_cycle": d * 1e3 / max(1, st["cycles"]), "identical_to_plain": out == gen}
-            mtp["verify_cost_vs_plain_step"] = None
         cpu = None
         if world == 1 and not a.no_cpu:
             tok_s, cores, desc, _ = cpu_reference_sample(3, 1)
@@ -350,16 +394,18 @@ def run_ours(a):
         line = {
             "metric": "batch-1 decode tok/s (plain)", "value": value, "unit": "tok/s", "n_gpus": world,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": dec_total / a.steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"27B-shape W4A16 plain greedy decode ({cfg.layers} layers, hidden 5120, vocab "
                                    f"248320), {P}-token seeded prompt, {n_new} tokens per step",
-                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                       "parallelism": "single GPU" if world == 1 else f"tp{world} (one sequence, NCCL all-gather of "
+                                                                         f"fp32 partial rows, {2 * cfg.layers + 2} exchanges per token)",
                        "l2": "inputs larger than L2 (13 GB of weights streamed per token)",
                        "timing": "CUDA events around the decode graph replays, max over ranks"},
             "ms_per_token": ms_tok,
             "hbm_roofline": {"bytes_per_token": B_tok, "tok_s_at_measured_peak": peak * 1e9 / B_tok,
-                             "frac_of_measured": value / world / (peak * 1e9 / B_tok),
-                             "tok_s_at_8TBs": 8e12 / B_tok, "frac_of_8TBs": value / world / (8e12 / B_tok)},
+                             "frac_of_measured": value / (peak * 1e9 / B_tok),
+                             "tok_s_at_8TBs": 8e12 / B_tok, "frac_of_8TBs": value / (8e12 / B_tok),
+                             "note": "bytes one rank streams per token"},
             "roofline": roofline,
             "w4_sequence": {"ms_n1": seq_ms, "ms_n5": seq5_ms, "bytes": seq_bytes, "launches": seq_launches},
             "w4_mlp_pair": {"us_m1": pair1_us, "gbs_m1": pair1_gbs, "us_m5": pair5_us, "gbs_m5": pair5_gbs},
@@ -371,6 +417,9 @@ def run_ours(a):
             "clocks": clocks,
             "cpu_baseline": cpu,
         }
+        if exchange_us is not None:
+            line["tp_exchange"] = {"us_per_exchange": exchange_us, "per_token": 2 * cfg.layers + 2,
+                                   "what": "all-gather of one fp32 row [hidden] + the residual norm over the parts"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -69,6 +69,19 @@ int qe_swiglu(const void* gu, void* out, int n, int I, long ldg, long ldo, void*
 int qe_argmax(const void* x, int rows, int n, long ldx, float* pv, int* pi, int nb, int* out,
               const int* idmap, void* stream);
 
+/* Tensor-parallel helpers, no counterpart in the reference (it is single-GPU).
+ * qe_rmsnorm1p_parts: like qe_rmsnorm1p with delta = bf16(sum over p < nparts of parts[p]), parts
+ * fp32 [nparts, rows, H] contiguous (the all-gathered partial sums of a K-split GEMV), added in
+ * ascending p so that the result does not depend on the collective's algorithm.
+ * qe_argmax_v: qe_argmax that also stores the winning value and adds `base` to the index (a rank's
+ * slice of the vocabulary). qe_argmax_merge: best of nparts candidates per row, vals / idx
+ * [nparts, rows], same ordering rule (NaN first, larger value, lower index). */
+int qe_rmsnorm1p_parts(void* x, const float* parts, int nparts, const void* w, void* out, int rows,
+                       int H, long ldx, long ldo, float eps, void* stream);
+int qe_argmax_v(const void* x, int rows, int n, long ldx, float* pv, int* pi, int nb, int* out,
+                float* out_v, const int* idmap, int base, void* stream);
+int qe_argmax_merge(const float* vals, const int* idx, int nparts, int rows, int* out, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Device-side bookkeeping of one pass. ctl (int32[>=24]): [0] pos, [1] pending DeltaNet rows,
  * [2] mode (0 prefill, 1 decode/verify), [3] m, [4] cycles, [5] accepted drafts, [16+m] histogram.
@@ -161,6 +174,9 @@ typedef struct qe_w4_params {
                           needs K == Kp, 16-byte aligned x and ldx % 8 == 0. No counterpart in the
                           reference; used by the decode engine, whose GEMV inputs are bf16-rounded
                           values that convert to fp16 exactly. */
+  int out_f32;         /* 0: out is bf16 (the reference's contract). 1 (plain epilogue only): out is
+                          fp32, ldo in floats, sums stored unrounded -- the partial sums of a matrix
+                          split along K over tensor-parallel ranks. No counterpart in the reference. */
 } qe_w4_params;
 
 /* Launch options with the reference's names (csrc/gemv_w4.h:27-39). 0 / -1 mean "auto by shape".

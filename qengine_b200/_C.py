@@ -108,6 +108,37 @@ def argmax(x, ws_v, ws_i, out, idmap=None):
                         out.data_ptr(), mp, _stream()), "argmax", kernels=2)
 
 
+def rmsnorm1p_parts(x, parts, w, out, eps):
+    """Tensor-parallel residual + norm (not in the reference): parts fp32 [nparts, rows, H] are the
+    all-gathered partial sums of a K-split GEMV; x += bf16(sum of parts, ascending), out = norm(x)."""
+    _chk(w, BF, "w"); _chk(parts, F32, "parts")
+    xn, xw, xld = _rows(x, BF, "x")
+    on, ow, old = _rows(out, BF, "out")
+    _req(parts.dim() == 3 and parts.size(1) == xn and parts.size(2) == xw, "parts must be [nparts, rows, H]")
+    _req(xw == w.numel() and ow == xw and on == xn, "rmsnorm1p_parts: shape mismatch")
+    check(lib.qe_rmsnorm1p_parts(x.data_ptr(), parts.data_ptr(), parts.size(0), w.data_ptr(), out.data_ptr(),
+                                 xn, xw, xld, old, float(eps), _stream()), "rmsnorm1p_parts")
+
+
+def argmax_v(x, ws_v, ws_i, out, out_v, base=0, idmap=None):
+    """argmax that also stores the winning value and adds `base` to the index (vocabulary shard)."""
+    xn, xw, xld = _rows(x, BF, "x")
+    _chk(ws_v, F32, "ws_v"); _chk(ws_i, I32, "ws_i"); _chk(out, I32, "out"); _chk(out_v, F32, "out_v")
+    nb = ws_v.numel() // xn
+    _req(ws_v.numel() == ws_i.numel() and nb >= 1 and out.numel() >= xn and out_v.numel() >= xn, "argmax_v sizes")
+    check(lib.qe_argmax_v(x.data_ptr(), xn, xw, xld, ws_v.data_ptr(), ws_i.data_ptr(), nb, out.data_ptr(),
+                          out_v.data_ptr(), idmap.data_ptr() if idmap is not None else None, int(base),
+                          _stream()), "argmax_v", kernels=2)
+
+
+def argmax_merge(vals, idx, out):
+    """Best of nparts candidates per row: vals fp32 / idx int32 [nparts, rows] -> out int32 [rows]."""
+    _chk(vals, F32, "vals"); _chk(idx, I32, "idx"); _chk(out, I32, "out")
+    _req(vals.dim() == 2 and vals.shape == idx.shape and out.numel() >= vals.size(1), "argmax_merge sizes")
+    check(lib.qe_argmax_merge(vals.data_ptr(), idx.data_ptr(), vals.size(0), vals.size(1), out.data_ptr(),
+                              _stream()), "argmax_merge")
+
+
 def accept(in_tok, am, n, ctl, next_tok, log):
     for t in (in_tok, am, ctl, next_tok, log):
         _chk(t, I32, "int buffer")

@@ -18,7 +18,7 @@ class W4Params(C.Structure):
     """struct qe_w4_params"""
     _fields_ = [("qw", P), ("scales", P), ("x", P), ("out", P), ("ws", P), ("counters", P),
                 ("M", c_int), ("K", c_int), ("Mp", c_int), ("Kp", c_int), ("N", c_int),
-                ("ldx", c_long), ("ldo", c_long), ("epilogue", c_int), ("x_f16", c_int)]
+                ("ldx", c_long), ("ldo", c_long), ("epilogue", c_int), ("x_f16", c_int), ("out_f32", c_int)]
 
 
 class W4Cfg(C.Structure):
@@ -42,6 +42,9 @@ SIGNATURES = {
     "qe_gemv_bf16": (c_int, [P, P, P, c_int, c_int, c_int, c_long, c_long, P]),
     "qe_swiglu": (c_int, [P, P, c_int, c_int, c_long, c_long, P]),
     "qe_argmax": (c_int, [P, c_int, c_int, c_long, P, P, c_int, P, P, P]),
+    "qe_rmsnorm1p_parts": (c_int, [P, P, c_int, P, P, c_int, c_int, c_long, c_long, c_float, P]),
+    "qe_argmax_v": (c_int, [P, c_int, c_int, c_long, P, P, c_int, P, P, P, c_int, P]),
+    "qe_argmax_merge": (c_int, [P, P, c_int, c_int, P, P]),
     "qe_accept": (c_int, [P, P, c_int, P, P, P, c_int, P]),
     "qe_commit": (c_int, [P, P, P, P, c_int, P]),
     "qe_mtp_select": (c_int, [P, P, c_int, P, c_long, P, c_int, P, P, P]),

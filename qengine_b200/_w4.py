@@ -61,8 +61,9 @@ def _run(x, qw, scales, out, M, epilogue, warps, unroll, ksplit, pdl, variant, m
     for t in (x, qw, scales, out):
         _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
     x_f16 = allow_f16 and x.dtype == torch.float16
+    out_f32 = allow_f16 and out.dtype == torch.float32 and epilogue == EPI_NONE
     _req(x.dtype == torch.bfloat16 or x_f16, "x must be bf16 (W4A16 kernel)")
-    _req(out.dtype == torch.bfloat16, "out must be bf16")
+    _req(out.dtype == torch.bfloat16 or out_f32, "out must be bf16")
     _req(qw.dtype == torch.int32 and qw.dim() == 4 and qw.size(2) == 32 and qw.size(3) == 4,
          "qw must be int32 [Mp/16, Kp/64, 32, 4] from quant.quantize_w4")
     _req(scales.dtype == torch.float16 and scales.dim() == 3 and scales.size(2) == 16,
@@ -88,7 +89,7 @@ def _run(x, qw, scales, out, M, epilogue, warps, unroll, ksplit, pdl, variant, m
     _req(mode in (-1, 0, 2, 3, 4), "mode in {-1 (auto), 0, 2, 3, 4}")
 
     p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None,
-                 M, K, Mp, Kp, N, x.stride(0), out.stride(0), epilogue, int(x_f16))
+                 M, K, Mp, Kp, N, x.stride(0), out.stride(0), epilogue, int(x_f16), int(out_f32))
     if x_f16:
         _req(K == Kp and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0,
              "fp16 activations need K % 128 == 0 and 16-byte aligned rows")
@@ -118,9 +119,10 @@ def gemv_swiglu(x, qw, scales, out, I, warps=0, unroll=0, ksplit=0, pdl=True, va
 
 
 def gemv_act16(x, qw, scales, out, M, swiglu=False, **kw):
-    """Engine-internal variant (not in the reference): x may be fp16. The decode engine keeps its
-    GEMV inputs as fp16 copies of bf16-rounded values (an exact conversion), because the fp16
-    unpack needs fewer integer-pipe instructions per weight than the bf16 one."""
+    """Engine-internal variant (not in the reference): x may be fp16 (an exact copy of bf16-rounded
+    values; the fp16 unpack needs fewer integer-pipe instructions per weight), and `out` may be
+    fp32 with the plain epilogue: unrounded partial sums of a matrix split along K over
+    tensor-parallel ranks."""
     cfg = dict(warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1, blocks_per_sm=0, min_units=4)
     cfg.update(kw)
     _run(x, qw, scales, out, M, EPI_SWIGLU if swiglu else EPI_NONE, cfg["warps"], cfg["unroll"], cfg["ksplit"],
@@ -162,7 +164,7 @@ def gemv_static(x, qw, scales, out, M, swiglu=False, warps=0, unroll=0, ksplit=0
     _req(scales.size(0) == qw.size(0) and scales.size(1) * 128 == Kp and Kp - 128 < K <= Kp, "shapes disagree")
     _req((Mp // 2 - 8 < M <= Mp // 2) if swiglu else (Mp - 16 < M <= Mp), "out width must match packed rows")
     p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None, M, K, Mp, Kp, N,
-                 x.stride(0), out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, 0)
+                 x.stride(0), out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, 0, 0)
     cfg = W4Cfg(int(warps), int(unroll), int(ksplit), 0, int(variant), int(mode), int(blocks_per_sm), int(min_units))
     code = lib.qe_w4_gemv_static(C.byref(p), C.byref(cfg), torch.cuda.current_stream().cuda_stream)
     _req(code != -28, "gemv_static: this shape needs more scratch than the library's fixed array "

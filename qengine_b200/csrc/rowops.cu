@@ -241,7 +241,7 @@ argmax_slab_kernel(const bf16* x, int n, long ldx, float* pv,
 
 __global__ void __launch_bounds__(256)
 argmax_final_kernel(const float* pv, const int* pi, int nb,
-                    int* out, const int* idmap) {
+                    int* out, const int* idmap, float* out_v, int base) {
   dep_release();
   dep_wait();
   __shared__ float sv[32];
@@ -253,8 +253,47 @@ argmax_final_kernel(const float* pv, const int* pi, int nb,
   block_best(v, i, sv, si);
   if (threadIdx.x == 0) {
     const int a = i == kNone ? 0 : i;  // a row of -inf only: index 0, like torch
-    out[row] = idmap ? idmap[a] : a;
+    out[row] = (idmap ? idmap[a] : a) + base;
+    if (out_v) out_v[row] = v;
   }
+}
+
+// Best of nparts (value, index) candidates per row; vals / idx are [nparts, rows]. Used to merge
+// the per-rank winners of a vocabulary-split lm_head: same ordering rule as the local argmax, so
+// the result equals the argmax over the whole vocabulary (ties go to the lowest global index).
+__global__ void argmax_merge_kernel(const float* vals, const int* idx, int nparts, int rows, int* out) {
+  dep_release();
+  dep_wait();
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  float v = vals[row];
+  int i = idx[row];
+  for (int p = 1; p < nparts; ++p) merge(v, i, vals[p * rows + row], idx[p * rows + row]);
+  out[row] = i;
+}
+
+// RMSNorm1p whose residual delta is the sum of nparts fp32 partial rows (tensor-parallel K-split
+// GEMV, all-gathered): delta = bf16(sum_p parts[p]) in ascending p, x = bf16(x + delta) written
+// back, out = bf16(x * rsqrt(mean x^2 + eps) * (1 + w)). One CTA per row, any H.
+__global__ void __launch_bounds__(256)
+rmsnorm1p_parts_kernel(bf16* x, const float* parts, int nparts, const bf16* w, bf16* out, int rows,
+                       int H, long ldx, long ldo, float eps) {
+  dep_release();
+  dep_wait();
+  __shared__ float scratch[32];
+  const int row = blockIdx.x;
+  bf16* xr = x + (long)row * ldx;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float d = 0.f;
+    for (int p = 0; p < nparts; ++p) d += parts[((size_t)p * rows + row) * H + c];
+    const float v = rnd(tofloat(xr[c]) + rnd(d));
+    xr[c] = tobf16(v);  // re-read below by the same thread only
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = rsqrtf(block_allsum(ss, scratch) / (float)H + eps);
+  for (int c = threadIdx.x; c < H; c += blockDim.x)
+    out[(long)row * ldo + c] = tobf16(tofloat(xr[c]) * inv * (1.0f + tofloat(w[c])));
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -324,13 +363,32 @@ extern "C" int qe_swiglu(const void* gu, void* out, int n, int I, long ldg, long
                      (cudaStream_t)stream, pdl_on(), (const bf16*)gu, (bf16*)out, I, ldg, ldo);
 }
 
-extern "C" int qe_argmax(const void* x, int rows, int n, long ldx, float* pv, int* pi, int nb,
-                         int* out, const int* idmap, void* stream) {
+extern "C" int qe_argmax_v(const void* x, int rows, int n, long ldx, float* pv, int* pi, int nb,
+                           int* out, float* out_v, const int* idmap, int base, void* stream) {
   if (rows < 1 || n < 1 || nb < 1) return QE_ERR_ARG;
   cudaStream_t s = (cudaStream_t)stream;
   int e = (int)launch(argmax_slab_kernel, dim3(nb, rows), dim3(256), 0, s, pdl_on(),
                       (const bf16*)x, n, ldx, pv, pi);
   if (e) return e;
   return (int)launch(argmax_final_kernel, dim3(rows), dim3(256), 0, s, pdl_on(), (const float*)pv,
-                     (const int*)pi, nb, out, idmap);
+                     (const int*)pi, nb, out, idmap, out_v, base);
+}
+
+extern "C" int qe_argmax(const void* x, int rows, int n, long ldx, float* pv, int* pi, int nb,
+                         int* out, const int* idmap, void* stream) {
+  return qe_argmax_v(x, rows, n, ldx, pv, pi, nb, out, nullptr, idmap, 0, stream);
+}
+
+extern "C" int qe_argmax_merge(const float* vals, const int* idx, int nparts, int rows, int* out,
+                               void* stream) {
+  if (nparts < 1 || rows < 1) return QE_ERR_ARG;
+  return (int)launch(argmax_merge_kernel, dim3((rows + 31) / 32), dim3(32), 0, (cudaStream_t)stream,
+                     pdl_on(), vals, idx, nparts, rows, out);
+}
+
+extern "C" int qe_rmsnorm1p_parts(void* x, const float* parts, int nparts, const void* w, void* out,
+                                  int rows, int H, long ldx, long ldo, float eps, void* stream) {
+  if (rows < 1 || H < 1 || nparts < 1) return QE_ERR_ARG;
+  return (int)launch(rmsnorm1p_parts_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, pdl_on(),
+                     (bf16*)x, parts, nparts, (const bf16*)w, (bf16*)out, rows, H, ldx, ldo, eps);
 }

@@ -58,6 +58,7 @@ struct W4Args {
   long ldx, ldo;
   int ksplit;         // mode 0: gridDim.y
   int total;          // tiles * G
+  int out_f32;        // plain epilogue only: store unrounded fp32 sums (tensor-parallel partials)
 };
 
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
@@ -182,6 +183,18 @@ __device__ __forceinline__ void store_tile(const W4Args& a, int tile, const floa
   auto bits = [](float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); };
   if constexpr (EPI == QE_EPI_NONE) {
     const int m0 = tile * 16 + r, m1 = m0 + 8;
+    if (a.out_f32) {  // partial sums of a K-split matrix, rounded only after the ranks are added
+      float* o32 = reinterpret_cast<float*>(a.out);
+      if (n0 < a.N) {
+        if (m0 < a.M) o32[(long)n0 * a.ldo + m0] = f[0];
+        if (m1 < a.M) o32[(long)n0 * a.ldo + m1] = f[2];
+      }
+      if (n1 < a.N) {
+        if (m0 < a.M) o32[(long)n1 * a.ldo + m0] = f[1];
+        if (m1 < a.M) o32[(long)n1 * a.ldo + m1] = f[3];
+      }
+      return;
+    }
     if (n0 < a.N) {
       if (m0 < a.M) out[(long)n0 * a.ldo + m0] = bits(f[0]);
       if (m1 < a.M) out[(long)n0 * a.ldo + m1] = bits(f[2]);
@@ -915,6 +928,7 @@ extern "C" int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* str
   a.scales = reinterpret_cast<const __half*>(p->scales);
   a.x = reinterpret_cast<const bf16*>(p->x);
   a.out = reinterpret_cast<bf16*>(p->out);
+  a.out_f32 = (p->out_f32 && p->epilogue == QE_EPI_NONE) ? 1 : 0;
   a.ws = p->ws;
   a.counters = p->counters;
   a.M = p->M; a.K = p->K; a.N = p->N;

@@ -73,6 +73,11 @@ class W4Linear:
         from . import _w4
         _w4.gemv_swiglu(x, p.qw, p.scales, out, p.M, ksplit=self._ks(p, x.shape[0]), **self.kw)
 
+    def partial(self, x, p, out32):
+        """Unrounded fp32 result: one rank's partial sums of a matrix split along K."""
+        from . import _w4
+        _w4.gemv_act16(x, p.qw, p.scales, out32, p.M, ksplit=self._ks(p, x.shape[0]), **self.kw)
+
     @staticmethod
     def dequantize(p):
         from .quant import dequantize_w4
@@ -84,11 +89,18 @@ class Engine:
     POS, PENDING, MODE, M, CYCLES, ACCEPTED = range(6)
 
     def __init__(self, cfg: Config, weights: dict, max_len: int = 4096, linear=None, device="cuda",
-                 mtp: bool = True, attn_splits: int | None = None, draft_vocab: int | None = None):
+                 mtp: bool = True, attn_splits: int | None = None, draft_vocab: int | None = None, tp=None):
         """weights: dict from qengine_b200.synth.build_model (already on `device`).
+        tp: a qengine_b200.tp.TPGroup for tensor parallelism; then `cfg` is still the whole model's
+        configuration and `weights` is this rank's shard (qengine_b200.tp.shard_model).
         attn_splits: flash-decoding splits per head (fixed so the graphs are static); default 16,
         more for long caches. draft_vocab: MTP drafts score only the first `draft_vocab` token ids
         (pruned draft head through the argmax id map); verify keeps the full head."""
+        self.tp, self.vocab_full, self.vocab_base = tp, cfg.vocab, 0
+        if tp is not None:
+            from .tp import local_config
+            cfg = local_config(cfg, tp.size)
+            self.vocab_base = tp.rank * cfg.vocab
         self.cfg, self.max_len = cfg, max_len
         self.dev = torch.device(device)
         self.linear = linear or W4Linear()
@@ -112,7 +124,10 @@ class Engine:
     # ------------------------------------------------------------------------------------------
     def _build_draft_head(self, nv: int):
         """Pruned draft head: the first nv rows of the packed lm_head (ids 0..nv-1), no copy of
-        the codes is re-quantised; nv must be a multiple of 16."""
+        the codes is re-quantised; nv must be a multiple of 16. Under tensor parallelism every rank
+        keeps the first nv / t rows of its own vocabulary slice."""
+        if self.tp is not None:
+            nv //= self.tp.size
         assert nv % 16 == 0 and isinstance(self.lm_head, W4Packed)
         p = self.lm_head
         self.draft_head = W4Packed(p.qw[:nv // 16].contiguous(), p.scales[:nv // 16].contiguous(), nv, p.K)
@@ -151,6 +166,13 @@ class Engine:
             self.mtp["kc"], self.mtp["vc"] = z(cfg.hkv, ml, cfg.head_dim), z(cfg.hkv, ml, cfg.head_dim)
             self.cat = z(N, 2 * H)
             self.mh, self.mout, self.chain_h = z(N, H), z(N, H), z(1, H)
+        if self.tp is not None:
+            t = self.tp.size
+            self.part32 = z(N, H, dt=F32)
+            self.parts = {n: z(t, n, H, dt=F32) for n in range(1, N + 1)}
+            self.cand_v, self.cand_i = z(N, dt=F32), z(N, dt=I32)
+            self.all_v = {n: z(t, n, dt=F32) for n in range(1, N + 1)}
+            self.all_i = {n: z(t, n, dt=I32) for n in range(1, N + 1)}
 
     def reset(self):
         """Empty sequence. KV caches need no clearing (only [0, pos] is ever read)."""
@@ -161,12 +183,41 @@ class Engine:
         self.ctl.zero_()
 
     # ------------------------------------------------------------------------------------------
+    # A matrix whose input is split over tensor-parallel ranks (out / o_proj, down, mtp.fc) leaves
+    # its result "pending": single GPU -> bf16 in self.mo; tensor parallel -> every rank's fp32
+    # partial rows gathered into self.parts[n]. The next norm adds the pending rows to the residual.
+    def _ksplit(self, x, p, n, lin):
+        if self.tp is None:
+            lin(x, p, self.mo[:n])
+        else:
+            lin.partial(x, p, self.part32[:n])
+            self.tp.all_gather(self.parts[n], self.part32[:n])
+
+    def _norm(self, h, pending, w, out, eps, n):
+        if not pending:
+            _C.rmsnorm1p(h, None, w, out, eps)
+        elif self.tp is None:
+            _C.rmsnorm1p(h, self.mo[:n], w, out, eps)
+        else:
+            _C.rmsnorm1p_parts(h, self.parts[n], w, out, eps)
+
+    def _argmax(self, logits, n, out, idmap=None):
+        """Greedy token per row (lowest id on ties); vocabulary shards exchange (value, id)."""
+        ws_v, ws_i = self.am_v[:n * 256], self.am_i[:n * 256]
+        if self.tp is None:
+            _C.argmax(logits, ws_v, ws_i, out, idmap)
+            return
+        _C.argmax_v(logits, ws_v, ws_i, self.cand_i, self.cand_v, self.vocab_base, idmap)
+        self.tp.all_gather(self.all_v[n], self.cand_v[:n])
+        self.tp.all_gather(self.all_i[n], self.cand_i[:n])
+        _C.argmax_merge(self.all_v[n], self.all_i[n], out)
+
     def _layer(self, L, n, h, eps, first, pos, lin=None):
         """One decoder layer on rows h[:n]; the previous sub-layer's output in self.mo is added by
         this layer's first norm unless `first`."""
         cfg, lin = self.cfg, lin or self.linear
-        xn, mo = self.xn[:n], self.mo[:n]
-        _C.rmsnorm1p(h, None if first else mo, L["in_norm"], xn, eps)
+        xn = self.xn[:n]
+        self._norm(h, not first, L["in_norm"], xn, eps, n)
         if L["type"] == "linear_attention":
             pr = self.proj[:n, :cfg.gdn_proj_rows]
             lin(xn, L["in_proj"], pr)
@@ -185,14 +236,14 @@ class Engine:
                          L["kc"], L["vc"], eps)
             out = self.mix[:n, :cfg.hq * cfg.head_dim]
             _C.attn_decode(q, L["kc"], L["vc"], pos, qg, self.part_o, self.part_ml, out)
-        lin(out, L["out"], mo)
-        _C.rmsnorm1p(h, mo, L["post_norm"], xn, eps)
+        self._ksplit(out, L["out"], n, lin)
+        self._norm(h, True, L["post_norm"], xn, eps, n)
         if L.get("fused_swiglu", False):
             lin.gate_up(xn, L["gate_up"], self.act[:n])
         else:
             lin(xn, L["gate_up"], self.gu[:n])
             _C.swiglu(self.gu[:n], self.act[:n])
-        lin(self.act[:n], L["down"], mo)
+        self._ksplit(self.act[:n], L["down"], n, lin)
 
     def _main(self, n, force=False):
         eps, k = self.cfg.eps, n - 1
@@ -202,7 +253,7 @@ class Engine:
         # checkpoints) is safe to read even from the early sections of this pass's kernels.
         _C.set_pdl_launch(False)
         if force:
-            _C.force_drafts(self.in_tok, self.ctl, self.truth, self.force_a, k, self.cfg.vocab)
+            _C.force_drafts(self.in_tok, self.ctl, self.truth, self.force_a, k, self.vocab_full)
             _C.set_pdl_launch(True)
             _C.embed(self.embed, self.in_tok, h)
         else:
@@ -210,9 +261,9 @@ class Engine:
             _C.set_pdl_launch(True)
         for i, L in enumerate(self.layers):
             self._layer(L, n, h, eps, i == 0, self.ctl)
-        _C.rmsnorm1p(h, self.mo[:n], self.final_norm, self.hid[:n], eps)
+        self._norm(h, True, self.final_norm, self.hid[:n], eps, n)
         self.lm_lin(self.hid[:n], self.lm_head, self.logits[:n])
-        _C.argmax(self.logits[:n], self.am_v[:n * 256], self.am_i[:n * 256], self.am)
+        self._argmax(self.logits[:n], n, self.am)
         _C.accept(self.in_tok, self.am, n, self.ctl, self.next_tok, self.log)
 
     def _mtp(self, n, hid, tok):
@@ -223,16 +274,21 @@ class Engine:
         _C.embed(self.embed, tok, mh)
         _C.rmsnorm1p(mh, None, M["pre_e"], cat[:, :H], eps)
         _C.rmsnorm1p(hid, None, M["pre_h"], cat[:, H:], eps)
-        self.linear(cat, M["fc"], mh)
-        self._layer(M, n, mh, eps, True, self.mpos)
-        _C.rmsnorm1p(mh, self.mo[:n], M["norm"], self.mout[:n], eps)
+        if self.tp is None:
+            self.linear(cat, M["fc"], mh)
+        else:  # this rank's slice of [e | h]; the summed fc rows are added to a zeroed residual
+            w = 2 * H // self.tp.size
+            self._ksplit(cat[:, self.tp.rank * w:(self.tp.rank + 1) * w], M["fc"], n, self.linear)
+            mh.zero_()
+        self._layer(M, n, mh, eps, self.tp is None, self.mpos)
+        self._norm(mh, True, M["norm"], self.mout[:n], eps, n)
         if self.draft_head is not None:
             lg = self.logits[:n, :self.draft_ids.numel()]
             self.lm_lin(self.mout[:n], self.draft_head, lg)
-            _C.argmax(lg, self.am_v[:n * 256], self.am_i[:n * 256], self.mtp_am, self.draft_ids)
+            self._argmax(lg, n, self.mtp_am, self.draft_ids)
         else:
             self.lm_lin(self.mout[:n], self.lm_head, self.logits[:n])
-            _C.argmax(self.logits[:n], self.am_v[:n * 256], self.am_i[:n * 256], self.mtp_am)
+            self._argmax(self.logits[:n], n, self.mtp_am)
 
     def _pass(self, n, mtp_rows, k, force=False):
         """Graph body: main pass on n rows; optionally MTP over the n rows (fills the MTP cache and
@@ -265,7 +321,10 @@ class Engine:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             before = launches[0]
-            with torch.cuda.graph(g):
+            # with collectives in the graph, other threads of the process group must stay free to
+            # make CUDA calls during capture
+            mode = "global" if self.tp is None else "thread_local"
+            with torch.cuda.graph(g, capture_error_mode=mode):
                 self._pass(n, mtp_rows, k, force)
             torch.cuda.synchronize()
             self.graphs[key] = g
