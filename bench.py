@@ -24,6 +24,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 from pathlib import Path
 
@@ -254,16 +255,19 @@ def mlp_pair_timing(eng, n_rows, reps=20):
 
 
 def exchange_timing(eng, reps=10, count=128):
-    """One tensor-parallel exchange (all-gather of a rank's fp32 partial row, then the residual
-    norm that sums the parts) timed as a graph of `count` of them. Every rank must call this."""
+    """One tensor-parallel exchange (every rank's fp32 partial row to every rank, summed inside the
+    residual norm) timed as a graph of `count` of them. Every rank must call this."""
     import torch
     from qengine_b200 import _C
     h, w = eng.h[:1], eng.final_norm
 
     def body():
         for _ in range(count):
-            eng.tp.all_gather(eng.parts[1], eng.part32[:1])
-            _C.rmsnorm1p_parts(h, eng.parts[1], w, eng.xn[:1], eng.cfg.eps)
+            if eng.tp.transport == "nccl":
+                eng.tp.all_gather(eng.parts[1], eng.part32[:1])
+                _C.rmsnorm1p_parts(h, eng.parts[1], w, eng.xn[:1], eng.cfg.eps)
+            else:
+                eng.tp.exchange_norm(h, eng.part32[:1], w, eng.xn[:1], eng.cfg.eps)
 
     eng.part32.zero_()
     body()
@@ -325,7 +329,7 @@ def run_ours(a):
     else:  # tensor parallel: one sequence, every matrix sharded over the ranks
         from qengine_b200 import tp
         W = tp.build_sharded_model(cfg, world, rank, seed=1, device=dev, scale_std=0.01)
-        eng = Engine(cfg, W, max_len=P + n_new + 32, device=dev, tp=tp.TPGroup())
+        eng = Engine(cfg, W, max_len=P + n_new + 32, device=dev, tp=tp.TPGroup(transport=a.transport))
     prompt = synth.prompt_ids(P, cfg.vocab, seed=1234)
 
     # ---- warm-up (captures the graphs) and timed plain decode ------------------------------
@@ -397,8 +401,9 @@ def run_ours(a):
             "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"27B-shape W4A16 plain greedy decode ({cfg.layers} layers, hidden 5120, vocab "
                                    f"248320), {P}-token seeded prompt, {n_new} tokens per step",
-                       "parallelism": "single GPU" if world == 1 else f"tp{world} (one sequence, NCCL all-gather of "
-                                                                         f"fp32 partial rows, {2 * cfg.layers + 2} exchanges per token)",
+                       "parallelism": "single GPU" if world == 1 else
+                       f"tp{world}: one sequence, every matrix sharded; {2 * cfg.layers + 2} exchanges of fp32 partial "
+                       f"rows per token, transport {a.transport}",
                        "l2": "inputs larger than L2 (13 GB of weights streamed per token)",
                        "timing": "CUDA events around the decode graph replays, max over ranks"},
             "ms_per_token": ms_tok,
@@ -419,11 +424,19 @@ def run_ours(a):
         }
         if exchange_us is not None:
             line["tp_exchange"] = {"us_per_exchange": exchange_us, "per_token": 2 * cfg.layers + 2,
-                                   "what": "all-gather of one fp32 row [hidden] + the residual norm over the parts"}
+                                   "transport": a.transport, "error": eng.tp.error(),
+                                   "what": "one fp32 row [hidden] from every rank to every rank + the residual norm "
+                                           "over the parts, back to back in one graph"}
         print(json.dumps(line), flush=True)
     if world > 1:
+        # graphs that hold collectives go first; a teardown that still stalls must not hold the GPUs
+        eng.graphs.clear()
+        torch.cuda.synchronize()
         dist.barrier()
+        sys.stdout.flush()
+        threading.Timer(30.0, lambda: os._exit(0)).start()
         dist.destroy_process_group()
+        os._exit(0)
 
 
 def main():
@@ -435,6 +448,8 @@ def main():
     ap.add_argument("--layers", type=int, default=64, help="model depth (64 = the 27B shape)")
     ap.add_argument("--tokens", type=int, default=N_NEW, help="generated tokens per step")
     ap.add_argument("--prompt", type=int, default=PROMPT_LEN, help="prompt length (profiling runs use a short one)")
+    ap.add_argument("--transport", default="peer", choices=["peer", "nccl"],
+                    help="tensor-parallel exchange: own peer-memory kernels, or NCCL all-gather + norm")
     ap.add_argument("--no-mtp", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     a = ap.parse_args()

@@ -82,6 +82,38 @@ int qe_argmax_v(const void* x, int rows, int n, long ldx, float* pv, int* pi, in
                 float* out_v, const int* idmap, int base, void* stream);
 int qe_argmax_merge(const float* vals, const int* idx, int nparts, int rows, int* out, void* stream);
 
+/* Tensor-parallel exchange over peer memory, fused with its consumer (no counterpart in the
+ * reference). Each rank owns one exchange block (qe_tp_alloc; size qe_tp_block_bytes) that every
+ * other rank of the node maps through CUDA IPC (qe_tp_export -> 64-byte handle -> qe_tp_import in
+ * the peer process). qe_tp_comm_create takes the world's block addresses as seen from this
+ * process (blocks[rank] = own) and returns an opaque communicator.
+ *   qe_tp_exchange_norm: part = this rank's fp32 partial rows [rows, H] (stride ldp) of a matrix
+ *     split along K. One kernel stores them into every peer's block, collects the peers' rows and
+ *     computes x = bf16(x + bf16(sum over ranks, ascending)), out = RMSNorm1p(x) * (1 + w): the
+ *     all-reduce and qe_rmsnorm1p in one launch, bit-identical on every rank.
+ *   qe_tp_exchange_argmax: (value, index) candidates per row from qe_argmax_v are exchanged and
+ *     merged with the argmax ordering rule; out[r] = greedy token over the whole vocabulary.
+ * All ranks must issue the same sequence of exchanges with the same row counts. Waits are bounded
+ * (qe_tp_set_timeout_ms, default 10 s per wait; after the first timeout later waits do not spin);
+ * qe_tp_error synchronises the device and returns the sticky error word (0 = none), info4 =
+ * {error, late source rank, row, kind 0 norm / 1 argmax}. Calls only enqueue work on `stream` and
+ * can be captured in CUDA graphs (sequence numbers live in the block). */
+long qe_tp_block_bytes(int H, int world);
+int qe_tp_alloc(long bytes, void** ptr);
+int qe_tp_free(void* ptr);
+int qe_tp_export(void* ptr, unsigned char* handle64);
+int qe_tp_import(const unsigned char* handle64, void** ptr);
+int qe_tp_unmap(void* ptr);
+int qe_tp_comm_create(void* const* blocks, int rank, int world, int H, void** comm);
+int qe_tp_comm_destroy(void* comm);
+int qe_tp_set_timeout_ms(void* comm, long ms);
+int qe_tp_exchange_norm(void* comm, void* x, const float* part, const void* w, void* out, int rows,
+                        long ldx, long ldp, long ldo, float eps, void* stream);
+int qe_tp_exchange_argmax(void* comm, const float* cand_v, const int* cand_i, int rows, int* out,
+                          void* stream);
+int qe_tp_error(void* comm, int* info4);
+int qe_tp_clear_error(void* comm);
+
 /* ------------------------------------------------------------------------------------------
  * Device-side bookkeeping of one pass. ctl (int32[>=24]): [0] pos, [1] pending DeltaNet rows,
  * [2] mode (0 prefill, 1 decode/verify), [3] m, [4] cycles, [5] accepted drafts, [16+m] histogram.

@@ -45,6 +45,19 @@ SIGNATURES = {
     "qe_rmsnorm1p_parts": (c_int, [P, P, c_int, P, P, c_int, c_int, c_long, c_long, c_float, P]),
     "qe_argmax_v": (c_int, [P, c_int, c_int, c_long, P, P, c_int, P, P, P, c_int, P]),
     "qe_argmax_merge": (c_int, [P, P, c_int, c_int, P, P]),
+    "qe_tp_block_bytes": (c_long, [c_int, c_int]),
+    "qe_tp_alloc": (c_int, [c_long, P]),
+    "qe_tp_free": (c_int, [P]),
+    "qe_tp_export": (c_int, [P, P]),
+    "qe_tp_import": (c_int, [P, P]),
+    "qe_tp_unmap": (c_int, [P]),
+    "qe_tp_comm_create": (c_int, [P, c_int, c_int, c_int, P]),
+    "qe_tp_comm_destroy": (c_int, [P]),
+    "qe_tp_set_timeout_ms": (c_int, [P, c_long]),
+    "qe_tp_exchange_norm": (c_int, [P, P, P, P, P, c_int, c_long, c_long, c_long, c_float, P]),
+    "qe_tp_exchange_argmax": (c_int, [P, P, P, c_int, P, P]),
+    "qe_tp_error": (c_int, [P, P]),
+    "qe_tp_clear_error": (c_int, [P]),
     "qe_accept": (c_int, [P, P, c_int, P, P, P, c_int, P]),
     "qe_commit": (c_int, [P, P, P, P, c_int, P]),
     "qe_mtp_select": (c_int, [P, P, c_int, P, c_long, P, c_int, P, P, P]),

@@ -272,29 +272,6 @@ __global__ void argmax_merge_kernel(const float* vals, const int* idx, int npart
   out[row] = i;
 }
 
-// RMSNorm1p whose residual delta is the sum of nparts fp32 partial rows (tensor-parallel K-split
-// GEMV, all-gathered): delta = bf16(sum_p parts[p]) in ascending p, x = bf16(x + delta) written
-// back, out = bf16(x * rsqrt(mean x^2 + eps) * (1 + w)). One CTA per row, any H.
-__global__ void __launch_bounds__(256)
-rmsnorm1p_parts_kernel(bf16* x, const float* parts, int nparts, const bf16* w, bf16* out, int rows,
-                       int H, long ldx, long ldo, float eps) {
-  dep_release();
-  dep_wait();
-  __shared__ float scratch[32];
-  const int row = blockIdx.x;
-  bf16* xr = x + (long)row * ldx;
-  float ss = 0.f;
-  for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    float d = 0.f;
-    for (int p = 0; p < nparts; ++p) d += parts[((size_t)p * rows + row) * H + c];
-    const float v = rnd(tofloat(xr[c]) + rnd(d));
-    xr[c] = tobf16(v);  // re-read below by the same thread only
-    ss = fmaf(v, v, ss);
-  }
-  const float inv = rsqrtf(block_allsum(ss, scratch) / (float)H + eps);
-  for (int c = threadIdx.x; c < H; c += blockDim.x)
-    out[(long)row * ldo + c] = tobf16(tofloat(xr[c]) * inv * (1.0f + tofloat(w[c])));
-}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 inline bool pdl_on() { return pdl_launch_enabled() && pdl_trigger_enabled(); }
@@ -386,9 +363,3 @@ extern "C" int qe_argmax_merge(const float* vals, const int* idx, int nparts, in
                      pdl_on(), vals, idx, nparts, rows, out);
 }
 
-extern "C" int qe_rmsnorm1p_parts(void* x, const float* parts, int nparts, const void* w, void* out,
-                                  int rows, int H, long ldx, long ldo, float eps, void* stream) {
-  if (rows < 1 || H < 1 || nparts < 1) return QE_ERR_ARG;
-  return (int)launch(rmsnorm1p_parts_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, pdl_on(),
-                     (bf16*)x, parts, nparts, (const bf16*)w, (bf16*)out, rows, H, ldx, ldo, eps);
-}

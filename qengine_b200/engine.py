@@ -99,6 +99,7 @@ class Engine:
         self.tp, self.vocab_full, self.vocab_base = tp, cfg.vocab, 0
         if tp is not None:
             from .tp import local_config
+            tp.open(cfg.hidden)
             cfg = local_config(cfg, tp.size)
             self.vocab_base = tp.rank * cfg.vocab
         self.cfg, self.max_len = cfg, max_len
@@ -191,15 +192,18 @@ class Engine:
             lin(x, p, self.mo[:n])
         else:
             lin.partial(x, p, self.part32[:n])
-            self.tp.all_gather(self.parts[n], self.part32[:n])
+            if self.tp.transport == "nccl":
+                self.tp.all_gather(self.parts[n], self.part32[:n])
 
     def _norm(self, h, pending, w, out, eps, n):
         if not pending:
             _C.rmsnorm1p(h, None, w, out, eps)
         elif self.tp is None:
             _C.rmsnorm1p(h, self.mo[:n], w, out, eps)
-        else:
+        elif self.tp.transport == "nccl":
             _C.rmsnorm1p_parts(h, self.parts[n], w, out, eps)
+        else:  # exchange of the partial rows fused into the norm, over peer memory
+            self.tp.exchange_norm(h, self.part32[:n], w, out, eps)
 
     def _argmax(self, logits, n, out, idmap=None):
         """Greedy token per row (lowest id on ties); vocabulary shards exchange (value, id)."""
@@ -208,9 +212,12 @@ class Engine:
             _C.argmax(logits, ws_v, ws_i, out, idmap)
             return
         _C.argmax_v(logits, ws_v, ws_i, self.cand_i, self.cand_v, self.vocab_base, idmap)
-        self.tp.all_gather(self.all_v[n], self.cand_v[:n])
-        self.tp.all_gather(self.all_i[n], self.cand_i[:n])
-        _C.argmax_merge(self.all_v[n], self.all_i[n], out)
+        if self.tp.transport == "nccl":
+            self.tp.all_gather(self.all_v[n], self.cand_v[:n])
+            self.tp.all_gather(self.all_i[n], self.cand_i[:n])
+            _C.argmax_merge(self.all_v[n], self.all_i[n], out)
+        else:
+            self.tp.exchange_argmax(self.cand_v, self.cand_i, n, out)
 
     def _layer(self, L, n, h, eps, first, pos, lin=None):
         """One decoder layer on rows h[:n]; the previous sub-layer's output in self.mo is added by

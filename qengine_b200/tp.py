@@ -142,13 +142,102 @@ def build_sharded_model(cfg: Config, t: int, g: int, seed=0, device="cuda", scal
 # Communicator
 # ---------------------------------------------------------------------------------------------
 class TPGroup:
-    """Thin wrapper over a torch.distributed process group: rank, size and the two exchanges the
-    decode path needs. All calls enqueue on the current CUDA stream (graph-capturable with NCCL)."""
+    """Rank, size and the exchanges of the decode path over a torch.distributed process group.
 
-    def __init__(self, group=None):
+    transport "peer" (default): the library's own exchange kernels over NVLink peer memory
+    (qe_tp_exchange_norm / qe_tp_exchange_argmax): one launch per exchange, fused with the
+    consuming norm; the process group is only used once, on the host, to swap the IPC handles of
+    the exchange blocks. transport "nccl": all-gather through torch.distributed followed by
+    `_C.rmsnorm1p_parts` / `_C.argmax_merge` (the library-collective baseline).
+    All calls enqueue on the current CUDA stream and can be captured in CUDA graphs."""
+
+    def __init__(self, group=None, transport: str = "peer", timeout_ms: int | None = None):
         import torch.distributed as dist
-        self.dist, self.group = dist, group
+        assert transport in ("peer", "nccl")
+        self.dist, self.group, self.transport = dist, group, transport
         self.rank, self.size = dist.get_rank(group), dist.get_world_size(group)
+        self.timeout_ms = timeout_ms
+        self.comm = self._block = None
+        self._maps = []
 
+    # -- peer transport -------------------------------------------------------------------------
+    def open(self, hidden: int):
+        """Allocate this rank's exchange block, map every peer's (CUDA IPC) and build the
+        communicator. Collective: every rank of the group must call it."""
+        import ctypes as C
+        from ._lib import check, lib
+        if self.comm is not None or self.transport != "peer":
+            return
+        nbytes = lib.qe_tp_block_bytes(int(hidden), self.size)
+        if nbytes < 0:
+            raise RuntimeError(f"tensor parallel exchange: hidden {hidden} / world {self.size} not supported")
+        blk = C.c_void_p()
+        check(lib.qe_tp_alloc(nbytes, C.byref(blk)), "tp alloc", kernels=0)
+        handle = (C.c_ubyte * 64)()
+        check(lib.qe_tp_export(blk, handle), "tp export", kernels=0)
+        handles = [None] * self.size
+        self.dist.all_gather_object(handles, bytes(handle), group=self.group)
+        blocks = (C.c_void_p * self.size)()
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                blocks[r] = blk.value
+            else:
+                m = C.c_void_p()
+                check(lib.qe_tp_import((C.c_ubyte * 64).from_buffer_copy(h), C.byref(m)), "tp import", kernels=0)
+                blocks[r] = m.value
+                self._maps.append(m)
+        comm = C.c_void_p()
+        check(lib.qe_tp_comm_create(blocks, self.rank, self.size, int(hidden), C.byref(comm)), "tp comm", kernels=0)
+        if self.timeout_ms:
+            check(lib.qe_tp_set_timeout_ms(comm, int(self.timeout_ms)), "tp timeout", kernels=0)
+        self._block, self.comm = blk, comm
+        self.dist.barrier(group=self.group)  # nobody pushes before every block is mapped
+
+    def close(self):
+        """Collective: unmap the peers' blocks, then free our own."""
+        from ._lib import lib
+        if self.comm is None:
+            return
+        torch.cuda.synchronize()
+        self.dist.barrier(group=self.group)
+        for m in self._maps:
+            lib.qe_tp_unmap(m)
+        self._maps = []
+        self.dist.barrier(group=self.group)
+        lib.qe_tp_comm_destroy(self.comm)
+        lib.qe_tp_free(self._block)
+        self.comm = self._block = None
+
+    def error(self):
+        """Sticky error word of the peer transport after a device sync: None, or a dict naming the
+        rank that was late."""
+        import ctypes as C
+        from ._lib import lib
+        if self.comm is None:
+            return None
+        info = (C.c_int * 4)()
+        e = lib.qe_tp_error(self.comm, info)
+        if e == 0:
+            return None
+        return {"error": e, "late_rank": info[1], "row": info[2], "kind": "argmax" if info[3] else "norm"}
+
+    def exchange_norm(self, x, part, w, out, eps):
+        """x += bf16(sum over ranks of part); out = rmsnorm1p(x) -- one launch."""
+        from ._lib import check, lib
+        assert part.dtype == torch.float32 and part.stride(1) == 1 and x.stride(1) == 1 and out.stride(1) == 1
+        assert x.shape == part.shape == out.shape
+        check(lib.qe_tp_exchange_norm(self.comm, x.data_ptr(), part.data_ptr(), w.data_ptr(), out.data_ptr(),
+                                      x.shape[0], x.stride(0), part.stride(0), out.stride(0), float(eps),
+                                      torch.cuda.current_stream().cuda_stream), "tp exchange_norm")
+
+    def exchange_argmax(self, cand_v, cand_i, rows, out):
+        from ._lib import check, lib
+        check(lib.qe_tp_exchange_argmax(self.comm, cand_v.data_ptr(), cand_i.data_ptr(), int(rows), out.data_ptr(),
+                                        torch.cuda.current_stream().cuda_stream), "tp exchange_argmax")
+
+    # -- library collective -----------------------------------------------------------------------
     def all_gather(self, out: torch.Tensor, inp: torch.Tensor):
         self.dist.all_gather_into_tensor(out, inp, group=self.group)
+
+    def barrier(self):
+        self.dist.barrier(group=self.group)

@@ -93,6 +93,175 @@ def test_argmax_shards_and_merge():
 
 
 # ---------------------------------------------------------------------------------------------
+# peer-memory exchange kernels on one GPU: the peer is a second local block that the test fills
+# (or leaves empty) BEFORE the launch, so no kernel ever waits for another kernel
+# ---------------------------------------------------------------------------------------------
+class _Raw:
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class _FakeWorld:
+    """Communicator of `rank` in a world of `world` ranks whose blocks all live on this GPU."""
+
+    def __init__(self, H, world, rank, timeout_ms=200):
+        import ctypes as C
+        from qengine_b200._lib import lib
+        self.lib, self.H, self.world, self.rank = lib, H, world, rank
+        self.nbytes = lib.qe_tp_block_bytes(H, world)
+        assert self.nbytes > 0
+        self.ptrs = []
+        for _ in range(world):
+            p = C.c_void_p()
+            assert lib.qe_tp_alloc(self.nbytes, C.byref(p)) == 0
+            self.ptrs.append(p)
+        arr = (C.c_void_p * world)(*[p.value for p in self.ptrs])
+        self.comm = C.c_void_p()
+        assert lib.qe_tp_comm_create(arr, rank, world, H, C.byref(self.comm)) == 0
+        assert lib.qe_tp_set_timeout_ms(self.comm, timeout_ms) == 0
+        self.blocks = [torch.as_tensor(_Raw(p.value, self.nbytes), device="cuda") for p in self.ptrs]
+
+    def norm_slot(self, owner, seq, src):
+        """int32 view [8 rows, H, 2] of the slot in `owner`'s block that `src` writes for exchange `seq`."""
+        off = 4096 + ((seq & 1) * self.world + src) * 8 * self.H * 8
+        return self.blocks[owner][off:off + 8 * self.H * 8].view(torch.int32).view(8, self.H, 2)
+
+    def am_slot(self, owner, seq, src):
+        off = 256 + ((seq & 1) * 8 + src) * 8 * 16
+        return self.blocks[owner][off:off + 8 * 16].view(torch.int32).view(8, 4)
+
+    def error(self):
+        import ctypes as C
+        info = (C.c_int * 4)()
+        return self.lib.qe_tp_error(self.comm, info), list(info)
+
+    def close(self):
+        torch.cuda.synchronize()
+        self.lib.qe_tp_comm_destroy(self.comm)
+        del self.blocks
+        for p in self.ptrs:
+            self.lib.qe_tp_free(p)
+
+
+def _norm_ref(x0, parts, w, eps=1e-6):
+    d = parts[0].clone()
+    for p in parts[1:]:
+        d += p
+    xr = (x0.float() + d.to(BF16).float()).to(BF16)
+    xf = xr.float()
+    return xr, (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (1.0 + w.float())).to(BF16)
+
+
+@pytest.mark.parametrize("H,world,rank", [(512, 2, 0), (5120, 2, 1), (5120, 8, 3), (2048, 4, 0)])
+def test_exchange_norm_against_prefilled_peers(H, world, rank):
+    from qengine_b200 import _C
+    from qengine_b200._lib import lib
+    fw = _FakeWorld(H, world, rank)
+    g = torch.Generator(device="cuda").manual_seed(H + world)
+    w = (torch.randn(H, generator=g, device="cuda") * 0.1).to(BF16)
+    s = torch.cuda.current_stream().cuda_stream
+    try:
+        for seq, n in [(1, 1), (2, 5), (3, 8), (4, 1)]:  # rows 1..: each row has its own sequence number
+            x = torch.randn(n, H, generator=g, device="cuda").to(BF16)
+            parts = [torch.randn(n, H, generator=g, device="cuda") for _ in range(world)]
+            x0, out = x.clone(), torch.empty_like(x)
+            # per-row sequence numbers differ (row 0 took part in every exchange, row 7 in one)
+            seqs = [sum(1 for (q, m) in [(1, 1), (2, 5), (3, 8), (4, 1)][:seq] if r < m) for r in range(n)]
+            for src in range(world):
+                if src == rank:
+                    continue
+                for r in range(n):
+                    sl = fw.norm_slot(rank, seqs[r], src)
+                    sl[r, :, 0] = parts[src][r].view(torch.int32)
+                    sl[r, :, 1] = seqs[r]
+            torch.cuda.synchronize()
+            assert lib.qe_tp_exchange_norm(fw.comm, x.data_ptr(), parts[rank].data_ptr(), w.data_ptr(), out.data_ptr(),
+                                           n, x.stride(0), parts[rank].stride(0), out.stride(0), 1e-6, s) == 0
+            assert fw.error()[0] == 0
+            xr, ref = _norm_ref(x0, parts, w)
+            assert torch.equal(x, xr)
+            # the same bits as the norm over gathered parts, and what every peer received is our row
+            x2, out2 = x0.clone(), torch.empty_like(x)
+            _C.rmsnorm1p_parts(x2, torch.stack(parts), w, out2, 1e-6)
+            assert torch.equal(out, out2) and torch.equal(x, x2)
+            assert float(((out.float() - ref.float()).abs() / ref.float().abs().clamp_min(1e-2)).max()) < 2 ** -6
+            for peer in range(world):
+                if peer == rank:
+                    continue
+                for r in range(n):
+                    got = fw.norm_slot(peer, seqs[r], rank)[r]
+                    assert torch.equal(got[:, 0], parts[rank][r].view(torch.int32)) and bool((got[:, 1] == seqs[r]).all())
+    finally:
+        fw.close()
+
+
+def test_exchange_argmax_against_prefilled_peers():
+    from qengine_b200._lib import lib
+    world, rank, n = 4, 2, 6
+    fw = _FakeWorld(512, world, rank)
+    s = torch.cuda.current_stream().cuda_stream
+    try:
+        vals = torch.tensor([[1.0, 5.0, 2.0, float("-inf"), 3.0, 0.5],
+                             [4.0, 5.0, 2.0, float("-inf"), float("nan"), 0.5],
+                             [2.0, 5.0, 7.0, float("-inf"), 9.0, 0.5],
+                             [3.0, 1.0, 7.0, float("-inf"), 1.0, 0.25]], device="cuda")
+        idx = (torch.arange(world, device="cuda", dtype=torch.int32)[:, None] * 1000
+               + torch.tensor([5, 6, 7, 0, 9, 1], device="cuda", dtype=torch.int32)[None])
+        for seq in (1, 2, 3):
+            for src in range(world):
+                if src != rank:
+                    sl = fw.am_slot(rank, seq, src)
+                    sl[:n, 0] = vals[src].view(torch.int32)
+                    sl[:n, 2] = idx[src]
+                    sl[:n, 1] = seq
+                    sl[:n, 3] = seq
+            out = torch.full((8,), -1, dtype=torch.int32, device="cuda")
+            torch.cuda.synchronize()
+            assert lib.qe_tp_exchange_argmax(fw.comm, vals[rank].contiguous().data_ptr(), idx[rank].contiguous().data_ptr(),
+                                             n, out.data_ptr(), s) == 0
+            assert fw.error()[0] == 0
+            #            max 4.0@r1  tie 5.0 -> rank 0   tie 7.0 -> rank 2   all -inf -> first   NaN wins   tie -> rank 0
+            assert out[:n].tolist() == [1005, 6, 2007, 0, 1009, 1]
+            for peer in range(world):
+                if peer != rank:
+                    got = fw.am_slot(peer, seq, rank)[:n]
+                    assert torch.equal(got[:, 2], idx[rank]) and bool((got[:, 1] == seq).all())
+    finally:
+        fw.close()
+
+
+def test_exchange_wait_runs_out_and_reports_the_late_rank():
+    """Failure detection without a fault: the peer's slot is never filled, the bounded wait gives
+    up, the kernel returns, the error word names the late rank, and the context stays usable."""
+    import time
+    from qengine_b200._lib import lib
+    H = 512
+    fw = _FakeWorld(H, 2, 0, timeout_ms=50)
+    s = torch.cuda.current_stream().cuda_stream
+    try:
+        x = torch.ones(1, H, device="cuda", dtype=BF16)
+        part = torch.ones(1, H, device="cuda")
+        w = torch.zeros(H, device="cuda", dtype=BF16)
+        out = torch.empty_like(x)
+        args = (fw.comm, x.data_ptr(), part.data_ptr(), w.data_ptr(), out.data_ptr(), 1, H, H, H, 1e-6, s)
+        t0 = time.perf_counter()
+        assert lib.qe_tp_exchange_norm(*args) == 0
+        err, info = fw.error()
+        dt = time.perf_counter() - t0
+        assert err == 1 and info[1:] == [1, 0, 0], (err, info)
+        assert 0.04 < dt < 2.0, dt
+        t0 = time.perf_counter()               # sticky: later exchanges do not spin at all
+        for _ in range(20):
+            assert lib.qe_tp_exchange_norm(*args) == 0
+        assert fw.error()[0] == 1
+        assert time.perf_counter() - t0 < 0.04
+        assert lib.qe_tp_clear_error(fw.comm) == 0 and fw.error()[0] == 0
+        assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0   # context still usable
+    finally:
+        fw.close()
+
+
+# ---------------------------------------------------------------------------------------------
 # engine under torch.distributed
 # ---------------------------------------------------------------------------------------------
 def _free_port():
@@ -101,7 +270,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _entry(rank, world, port, fn):
+def _entry(rank, world, port, fn, *extra):
     for p in (str(HERE), str(HERE.parent)):
         if p not in sys.path:
             sys.path.insert(0, p)
@@ -111,17 +280,19 @@ def _entry(rank, world, port, fn):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
                             device_id=torch.device("cuda", rank))
-    try:
-        fn(rank, world)
-        torch.cuda.synchronize()
-        dist.barrier()
-    finally:
-        dist.destroy_process_group()
+    import threading
+    fn(rank, world, *extra)
+    torch.cuda.synchronize()
+    dist.barrier()
+    # a teardown that stalls (graphs holding collectives) must not hold the GPUs: leave after 20 s
+    threading.Timer(20.0, lambda: os._exit(0)).start()
+    dist.destroy_process_group()
+    os._exit(0)
 
 
-def _spawn(fn, world):
+def _spawn(fn, world, *extra):
     import torch.multiprocessing as mp
-    mp.spawn(_entry, args=(world, _free_port(), fn), nprocs=world, join=True)
+    mp.spawn(_entry, args=(world, _free_port(), fn) + extra, nprocs=world, join=True)
 
 
 def _gather_cols(local):
@@ -131,7 +302,7 @@ def _gather_cols(local):
     return torch.cat(parts, dim=-1)
 
 
-def _engine_worker(rank, world):
+def _engine_worker(rank, world, transport):
     from oracle import model as OM
     from qengine_b200 import synth, tp
     from qengine_b200.engine import Engine
@@ -139,7 +310,7 @@ def _engine_worker(rank, world):
     cfg = synth.tiny_config()
     Wp = synth.build_model(cfg, seed=7, device="cpu", scale_std=0.01)
     W = synth.model_to(Wp, "cuda")
-    eng = Engine(cfg, tp.shard_model(W, cfg, world, rank), max_len=256, tp=tp.TPGroup())
+    eng = Engine(cfg, tp.shard_model(W, cfg, world, rank), max_len=256, tp=tp.TPGroup(transport=transport))
     g = torch.load(G / "greedy.pt")
     prompt, seq = g["prompt"], (g["prompt"] + g["tokens"])[:40]
 
@@ -153,8 +324,10 @@ def _engine_worker(rank, world):
         got = eng.generate_spec(prompt, 40, 4, force_accept=a, truth=prompt + plain + [0] * 16)
         assert got == plain, a
     assert eng.generate(prompt, 40) == plain                          # run-to-run identical
-    dv = Engine(cfg, tp.shard_model(W, cfg, world, rank), max_len=256, tp=tp.TPGroup(), draft_vocab=1024)
+    dv = Engine(cfg, tp.shard_model(W, cfg, world, rank), max_len=256, tp=tp.TPGroup(transport=transport),
+                draft_vocab=1024)
     assert dv.generate_spec(prompt, 40, 3) == plain
+    assert eng.tp.error() is None and dv.tp.error() is None
 
     # every rank must hold the same tokens (control words are replicated, never exchanged)
     import torch.distributed as dist
@@ -174,7 +347,7 @@ def _engine_worker(rank, world):
         cm = min(cosine(mlg[t], ref_mlg[t]) for t in range(12))
         agree = sum(int(lg[t].float().argmax()) == int(ref_lg[t].float().argmax()) for t in range(len(seq)))
         same = next((i for i, (a, b) in enumerate(zip(plain, ref_plain)) if a != b), len(plain))
-        print(f"\nTP={world} vs single GPU: min cosine logits {cs:.6f}, mtp {cm:.6f}, top-1 {agree}/{len(seq)}, "
+        print(f"\nTP={world} ({transport}) vs single GPU: min cosine logits {cs:.6f}, mtp {cm:.6f}, top-1 {agree}/{len(seq)}, "
               f"greedy identical for {same}/40 tokens")
         assert cs >= 0.9999 and cm >= 0.9999 and agree >= len(seq) - 1
         D, oc = dense_model(Wp), oracle_config(cfg)
@@ -187,15 +360,17 @@ def _engine_worker(rank, world):
         assert worst >= 0.9999
 
 
-def test_tp_engine_group_of_one_is_bit_identical():
-    _spawn(_engine_worker, 1)
+@pytest.mark.parametrize("transport", ["peer", "nccl"])
+def test_tp_engine_group_of_one_is_bit_identical(transport):
+    _spawn(_engine_worker, 1, transport)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tp_engine_two_gpus():
-    _spawn(_engine_worker, 2)
+@pytest.mark.parametrize("transport", ["peer", "nccl"])
+def test_tp_engine_two_gpus(transport):
+    _spawn(_engine_worker, 2, transport)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_tp_engine_four_gpus_shared_kv_heads():
-    _spawn(_engine_worker, 4)  # tiny model: 2 KV heads over 4 ranks
+    _spawn(_engine_worker, 4, "peer")  # tiny model: 2 KV heads over 4 ranks
