@@ -22,7 +22,12 @@ struct W4Args {
   int ksplit;         // mode 0: gridDim.y
   int total;          // tiles * G
   int out_f32;        // plain epilogue only: store unrounded fp32 sums (tensor-parallel partials)
+  int epi;            // QE_EPI_*, read by kernels instantiated with kEpiRuntime
 };
+// Template value "take the epilogue from W4Args::epi": lets one kernel function serve every
+// matrix of a layer, so that consecutive launches run the same code (a launch of a different
+// function starts with cold instruction caches, which costs microseconds on kernels this short).
+constexpr int kEpiRuntime = 2;
 
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
   uint32_t r;
@@ -140,6 +145,11 @@ __device__ __forceinline__ float silu_fast(float v) { return v / (1.0f + __expf(
 // Store one finished 16 x 8 tile held as the mma C fragment of warp 0.
 template <int EPI>
 __device__ __forceinline__ void store_tile(const W4Args& a, int tile, const float (&f)[4], int lane) {
+  if constexpr (EPI == kEpiRuntime) {
+    if (a.epi == QE_EPI_SWIGLU) store_tile<QE_EPI_SWIGLU>(a, tile, f, lane);
+    else store_tile<QE_EPI_NONE>(a, tile, f, lane);
+    return;
+  }
   const int r = lane >> 2, t = lane & 3;
   const int n0 = 2 * t, n1 = n0 + 1;
   unsigned short* out = reinterpret_cast<unsigned short*>(a.out);

@@ -37,6 +37,7 @@
 // (per 8 weights: 3 shifts, 4 lop3, 4 sub.bf16x2, 1 mma). It also makes the one-row and k+1-row
 // sums the same instruction sequence, hence the same bits.
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -353,10 +354,13 @@ __global__ void __launch_bounds__(256, MINB) w4_warp_ring_kernel(const W4Args a,
   bool first_seg = true;
   bool ok = true;
 
-  auto one_unit = [&](const uint4* wp, const __half* sp) {
+  // One unit (group gg of the current tile) into acc. The tile-end handling is NOT in here: this
+  // body is replicated by the unrolled fast path below, and the kernel is short enough for its
+  // code size to show up as instruction-cache misses at the start of every launch.
+  auto unit_core = [&](const uint4* wp, const __half* sp, int gg) {
     const uint4 w0 = wp[0], w1 = wp[32];
     const float slo = __half2float(sp[0]), shi = __half2float(sp[8]);
-    const uint4* xp = xlane + g * 16;
+    const uint4* xp = xlane + gg * 16;
     const uint4 x0 = xp[0], x1 = xp[1], x2 = xp[8], x3 = xp[9];
     float c[4] = {0.f, 0.f, 0.f, 0.f};
     auto ks = [&](uint32_t w, uint32_t b0, uint32_t b1) {
@@ -374,12 +378,6 @@ __global__ void __launch_bounds__(256, MINB) w4_warp_ring_kernel(const W4Args a,
     acc[1] = fmaf(slo, c[1], acc[1]);
     acc[2] = fmaf(shi, c[2], acc[2]);
     acc[3] = fmaf(shi, c[3], acc[3]);
-    if (++g == G) {  // tile finished
-      if constexpr (TWO) finish_segment_cta<EPI>(a, fx, tile, seg_gb, G, first_seg, acc, lane, nworkers, worker);
-      else finish_segment<EPI, true>(a, tile, seg_gb, G, first_seg, acc, lane, nworkers, worker);
-      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-      g = 0; seg_gb = 0; first_seg = false; ++tile;
-    }
   };
 
   for (int st = 0; st < nstage; ++st) {
@@ -392,11 +390,26 @@ __global__ void __launch_bounds__(256, MINB) w4_warp_ring_kernel(const W4Args a,
     const __half* sp = reinterpret_cast<const __half*>(sbase + (size_t)slot * kStageS) + r;
     const int cnt = min(PERW, u1 - (u0 + st * PERW));
     if (ok) {
-      if (cnt == PERW) {
+      int i = 0;
+      while (i < cnt) {
+        const int run = min(cnt - i, G - g);  // units of this stage that stay inside the tile
+        if (run == PERW) {
 #pragma unroll
-        for (int i = 0; i < PERW; ++i) one_unit(wp + i * 64, sp + i * 16);
-      } else {
-        for (int i = 0; i < cnt; ++i) one_unit(wp + i * 64, sp + i * 16);
+          for (int j = 0; j < PERW; ++j) unit_core(wp + j * 64, sp + j * 16, g + j);
+        } else {
+#pragma unroll 1
+          for (int j = 0; j < run; ++j) unit_core(wp + (i + j) * 64, sp + (i + j) * 16, g + j);
+        }
+        g += run;
+        i += run;
+        // the tile is complete, or the range ends inside it: the only call site of the finish
+        if (g == G || (st == nstage - 1 && i == cnt)) {
+          if constexpr (TWO) finish_segment_cta<EPI>(a, fx, tile, seg_gb, g, first_seg, acc, lane, nworkers, worker);
+          else finish_segment<EPI, true>(a, tile, seg_gb, g, first_seg, acc, lane, nworkers, worker);
+          acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+          g = (g == G) ? 0 : g;
+          seg_gb = g; first_seg = false; ++tile;
+        }
       }
     }
     __syncwarp();
@@ -404,10 +417,6 @@ __global__ void __launch_bounds__(256, MINB) w4_warp_ring_kernel(const W4Args a,
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       refill(st + STAGES);
     }
-  }
-  if (g != seg_gb) {  // the range ended inside a tile
-    if constexpr (TWO) finish_segment_cta<EPI>(a, fx, tile, seg_gb, g, first_seg, acc, lane, nworkers, worker);
-    else finish_segment<EPI, true>(a, tile, seg_gb, g, first_seg, acc, lane, nworkers, worker);
   }
 }
 
@@ -477,14 +486,15 @@ struct WarpGeom {
 };
 template <int PERW, int ST, int MINB>
 WarpGeom warp_geom(int bps) {
-  WarpGeom g{{w4_warp_ring_kernel<PERW, ST, QE_EPI_NONE, false, MINB, false>,
-              w4_warp_ring_kernel<PERW, ST, QE_EPI_SWIGLU, false, MINB, false>,
-              w4_warp_ring_kernel<PERW, ST, QE_EPI_NONE, true, MINB, false>,
-              w4_warp_ring_kernel<PERW, ST, QE_EPI_SWIGLU, true, MINB, false>,
-              w4_warp_ring_kernel<PERW, ST, QE_EPI_NONE, false, MINB, true>,
-              w4_warp_ring_kernel<PERW, ST, QE_EPI_SWIGLU, false, MINB, true>,
-              w4_warp_ring_kernel<PERW, ST, QE_EPI_NONE, true, MINB, true>,
-              w4_warp_ring_kernel<PERW, ST, QE_EPI_SWIGLU, true, MINB, true>},
+  // one function per (activation type, finish scheme) serves both epilogues
+  WarpGeom g{{w4_warp_ring_kernel<PERW, ST, kEpiRuntime, false, MINB, false>,
+              w4_warp_ring_kernel<PERW, ST, kEpiRuntime, false, MINB, false>,
+              w4_warp_ring_kernel<PERW, ST, kEpiRuntime, true, MINB, false>,
+              w4_warp_ring_kernel<PERW, ST, kEpiRuntime, true, MINB, false>,
+              w4_warp_ring_kernel<PERW, ST, kEpiRuntime, false, MINB, true>,
+              w4_warp_ring_kernel<PERW, ST, kEpiRuntime, false, MINB, true>,
+              w4_warp_ring_kernel<PERW, ST, kEpiRuntime, true, MINB, true>,
+              w4_warp_ring_kernel<PERW, ST, kEpiRuntime, true, MINB, true>},
              (size_t)8 * ST * PERW * (1024 + 32) + 8 * 2 * 128 * sizeof(float) + kCtaTiles * sizeof(int), bps};
   for (WarpKernelFn f : g.fn) cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
   return g;
@@ -545,7 +555,8 @@ Resolved resolve(const qe_w4_params& p, const qe_w4_cfg& in) {
     const long want = (units + std::max(1, c.min_units) - 1) / std::max(1, c.min_units);
     const long workers = std::max<long>(1, std::min<long>((long)sms * bps * 8, want));
     // tiles cut across warps are finished through shared memory when every CTA span is short enough
-    const bool two = cta_fix_ok((int)units, (int)G, (int)workers, 8);
+    static const bool one_level = getenv("QE_W4_ONE_LEVEL") != nullptr;  // A/B measurement knob
+    const bool two = !one_level && cta_fix_ok((int)units, (int)G, (int)workers, 8);
     r.wfn = wg.fn[(p.epilogue == QE_EPI_SWIGLU ? 1 : 0) + (p.x_f16 ? 2 : 0) + (two ? 4 : 0)];
     r.nworkers = (int)workers;
     r.plan.grid_x = (int)((workers + 7) / 8);
@@ -641,6 +652,7 @@ extern "C" int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* str
   a.x = reinterpret_cast<const bf16*>(p->x);
   a.out = reinterpret_cast<bf16*>(p->out);
   a.out_f32 = (p->out_f32 && p->epilogue == QE_EPI_NONE) ? 1 : 0;
+  a.epi = p->epilogue;
   a.ws = p->ws;
   a.counters = p->counters;
   a.M = p->M; a.K = p->K; a.N = p->N;
