@@ -373,6 +373,62 @@ def run_ours(a):
                           "ms_per_cycle": d * 1e3 / max(1, st["cycles"]), "identical_to_plain": out == gen}
     exchange_us = exchange_timing(eng) if world > 1 else None
 
+    # ---- verify pass alone vs plain step (one graph replay each, same weights) -----------------
+    verify = {}
+    if not a.no_mtp:
+        for n_rows in (1, 5):
+            g = eng.graph(n_rows, False, 0)
+            eng.reset()
+            eng.ctl[eng.MODE].fill_(1)
+            eng.ctl[eng.POS].fill_(P)
+            ms = []
+            for i in range(8):
+                eng.ctl[eng.POS].fill_(P)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                barrier()
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                if i >= 3:
+                    ms.append(e0.elapsed_time(e1))
+            verify[f"ms_n{n_rows}"] = statistics.median(ms)
+        verify["verify_cost_vs_plain_step"] = verify["ms_n5"] / verify["ms_n1"]
+
+    # ---- long cache: 32,768 pre-filled positions (seeded N(0,1) K/V), then the same decode ---------
+    longctx = {}
+    if a.context > 0:
+        del eng
+        torch.cuda.empty_cache()
+        n_long = min(n_new, 256)
+        kw = dict(max_len=a.context + P + n_long + 64, device=dev)
+        if world > 1:
+            kw["tp"] = tp.TPGroup(transport=a.transport)
+        eng = Engine(cfg, W, **kw)
+        eng.set_context(a.context)
+        eng.generate(prompt, n_long)
+        barrier()
+        gen_l, _, d = eng.generate(prompt, n_long, timing=True)
+        td = torch.tensor([d], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(td, op=dist.ReduceOp.MAX)
+        longctx = {"context": a.context, "tokens": n_long, "plain_tok_s": (n_long - 1) / float(td.item()),
+                   "plain_ms_per_token": float(td.item()) * 1e3 / (n_long - 1),
+                   "kv_bytes_per_token": 2 * cfg.hkv * 2 * cfg.head_dim * a.context *
+                                         sum(t == "full_attention" for t in cfg.layer_types)}
+        if not a.no_mtp:
+            truth_l = prompt + gen_l + [0] * 64
+            for label, fa in (("a0", 0), ("a4", 4)):
+                eng.generate_spec(prompt, n_long, 4, force_accept=fa, truth=truth_l)
+                barrier()
+                out, _, d, st = eng.generate_spec(prompt, n_long, 4, timing=True, force_accept=fa, truth=truth_l)
+                td = torch.tensor([d], device=dev, dtype=torch.float64)
+                if world > 1:
+                    dist.all_reduce(td, op=dist.ReduceOp.MAX)
+                d = float(td.item())
+                longctx[f"mtp_k4_{label}"] = {"tok_s": (n_long - 1) / d, "ms_per_cycle": d * 1e3 / max(1, st["cycles"]),
+                                              "identical_to_plain": out == gen_l}
+
     line = {}
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -415,6 +471,8 @@ def run_ours(a):
             "w4_sequence": {"ms_n1": seq_ms, "ms_n5": seq5_ms, "bytes": seq_bytes, "launches": seq_launches},
             "w4_mlp_pair": {"us_m1": pair1_us, "gbs_m1": pair1_gbs, "us_m5": pair5_us, "gbs_m5": pair5_gbs},
             "mtp_k4": mtp,
+            "verify_pass": verify,
+            "long_context": longctx,
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": (P // 8) * 36 + 8,
                     "d2h_bytes_per_step": n_new * 4},
             "gpu_launches": launches,
@@ -450,6 +508,8 @@ def main():
     ap.add_argument("--prompt", type=int, default=PROMPT_LEN, help="prompt length (profiling runs use a short one)")
     ap.add_argument("--transport", default="peer", choices=["peer", "nccl"],
                     help="tensor-parallel exchange: own peer-memory kernels, or NCCL all-gather + norm")
+    ap.add_argument("--context", type=int, default=32768,
+                    help="pre-filled cache length of the long-context block (0 = skip it)")
     ap.add_argument("--no-mtp", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     a = ap.parse_args()

@@ -28,13 +28,15 @@
 // One pass over the register state per row gives both S^T k and S^T q of the pre-update state:
 //   kv = decay (S^T k),  delta = beta (v - kv),  o = decay (S^T q) + delta (k . q)
 // so a row costs one block barrier (partials are double-buffered) instead of several. The gated
-// RMSNorm needs the sum of o_b^2 over all D columns of the head: every CTA publishes its partial
-// sum in shared memory and reads the others' through distributed shared memory in rank order.
+// RMSNorm needs the sum of o_b^2 over all D columns of the head: every CTA pushes its partial sum
+// into the shared memory of all CTAs of the cluster (distributed shared memory stores), one cluster
+// barrier, and each CTA adds the partials in rank order.
 //
-// Dependency handling: the state load and the per-head constants do not depend on the producer
-// of this pass's projections, so with `early` they are fetched before the programmatic-dependency
-// wait and overlap the in_proj GEMV. Everything the previous pass wrote recently (ctl, ring,
-// checkpoints) is read after the wait.
+// Dependency handling: the state, the per-head constants, ctl and the checkpoints of the previous
+// pass do not depend on the producer of this pass's projections, so with `early` the state load
+// and the whole replay (including the write-back of S) run before the programmatic-dependency
+// wait and overlap the in_proj GEMV. `early` requires that the previous pass has completed when
+// this pass starts (an engine launches the first kernel of a pass in plain stream order).
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -75,7 +77,7 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
   __shared__ float gate_s[kMaxRows][2];      // (decay, beta)
   __shared__ float kq_s[kMaxRows];           // k . q per row
   __shared__ float part[2][2][kWarps][kCols];  // [buffer][k or q][warp][column]
-  __shared__ float ss_s[kMaxRows];           // this CTA's sum of o_b^2 per row
+  __shared__ float ss_all[NCTA][kMaxRows];   // sum of o_b^2 per row of every CTA of the cluster (pushed)
 
   const int j = blockIdx.y;                  // value head
   const int cs = blockIdx.x;                 // column slice = rank in the cluster
@@ -92,8 +94,9 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
   for (int i = 0; i < RP; ++i) s[i] = Sj[(size_t)(warp * RP + i) * D];
   const float A_log = tofloat(a.A_log[j]), dt_bias = tofloat(a.dt_bias[j]);
   const float nw = tofloat(a.norm_w[c0 + lane]);
-  if (a.early) dep_wait();
-
+  // ctl and the checkpoints were written by the previous pass, which has completed (the first
+  // kernel of a pass is launched in plain stream order): with `early` the whole replay, including
+  // the write-back of S, runs before the dependency wait and overlaps the tail of the in_proj GEMV.
   const int P = a.ctl[0], pend = min(max(a.ctl[1], 0), kMaxRows);
 
   // S <- decay S + k (beta (v - decay S^T k))^T on this thread's rows of its column; with Q also
@@ -139,6 +142,9 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
 #pragma unroll
     for (int i = 0; i < RP; ++i) Sj[(size_t)(warp * RP + i) * D] = s[i];
   }
+  if (a.early) dep_wait();  // from here on: this pass's projections
+  // the gate input of this warp's row is only needed at the very end: fetch it now
+  const float z_pre = warp < n ? tofloat(a.z[(long)warp * a.ldp + j * D + c0 + lane]) : 0.f;
   __syncthreads();  // k_s / v_s are about to be overwritten by the new rows
 
   // ---- 2a. causal conv + SiLU of every new row (q, k: all D channels; v: own columns) ----
@@ -228,24 +234,26 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
   }
   __syncthreads();
 
-  // ---- 2e. gated RMSNorm over the head's D outputs: cluster-wide sum of squares ----
+  // ---- 2e. gated RMSNorm over the head's D outputs: every CTA pushes its partial sum of squares
+  // into the shared memory of all CTAs of the cluster; one cluster barrier makes them visible ----
   for (int t = warp; t < n; t += kWarps) {
     const float ob = o_s[t][lane];
     const float ssum = warp_allsum(ob * ob);
-    if (lane == 0) ss_s[t] = ssum;
+    if (lane < NCTA) *cluster.map_shared_rank(&ss_all[cs][t], lane) = ssum;
   }
   cluster.sync();
   for (int t = warp; t < n; t += kWarps) {
     float total = 0.f;
 #pragma unroll
-    for (int rk = 0; rk < NCTA; ++rk) total += *cluster.map_shared_rank(&ss_s[t], rk);
+    for (int rk = 0; rk < NCTA; ++rk) total += ss_all[rk][t];
     const float ob = o_s[t][lane];
     const float nn = rnd(ob * rsqrtf(total / (float)D + a.eps));
     const float y = rnd(nw * nn);
-    const float zz = tofloat(a.z[(long)t * a.ldp + j * D + c0 + lane]);
+    const float zz = t == warp ? z_pre : tofloat(a.z[(long)t * a.ldp + j * D + c0 + lane]);
     a.out[(long)t * a.ldo + j * D + c0 + lane] = tobf16(y * silu_acc(zz));
   }
-  cluster.sync();  // nobody leaves while a peer may still read its shared memory
+  // no second barrier: nobody reads remote shared memory after the one above, and every remote
+  // store was issued before it
 }
 
 // Off by default: the early state load assumes that no launch on the same state is still in

@@ -173,6 +173,119 @@ attn_split_kernel(const bf16* q, const bf16* kc,
   }
 }
 
+// The same split for all GQ query heads of one KV head in one CTA: every K / V row of the slice is
+// loaded once and used by the GQ heads that share it (grouped-query attention), instead of once
+// per query head. With a long cache the KV stream is the whole cost of the layer (134 MB per layer
+// at 32K positions of the 27B shape), so this divides the L2 / HBM traffic by GQ. Position-to-warp
+// assignment, step size and the order of every sum are those of attn_split_kernel: per head the
+// result is bit-identical to it.
+template <int HD, int GQ>
+__global__ void __launch_bounds__(kSplitWarps * 32)
+attn_split_gqa_kernel(const bf16* q, const bf16* kc, const bf16* vc, const int* pos_ptr, float* part_o,
+                      float* part_ml, int Hq, int max_len, float scale) {
+  constexpr int E = HD / 32;
+  dep_release();
+  dep_wait();
+  __shared__ float sm[kSplitWarps], sl[kSplitWarps];
+  __shared__ float so[kSplitWarps][HD];
+  const int g = blockIdx.x, s = blockIdx.y, NS = gridDim.y, t = blockIdx.z;
+  const int len = min(max(pos_ptr[0] + t + 1, 0), max_len);
+  const int chunk = (len + NS - 1) / NS;
+  const int start = s * chunk, end = min(len, start + chunk);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  float qf[GQ][E], acc[GQ][E], m[GQ], l[GQ];
+#pragma unroll
+  for (int j = 0; j < GQ; ++j) {
+    load_lane<HD>(q + ((size_t)t * Hq + g * GQ + j) * HD, lane, qf[j]);
+    m[j] = -INFINITY;
+    l[j] = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[j][e] = 0.f;
+  }
+  const bf16* kb = kc + (size_t)g * max_len * HD;
+  const bf16* vb = vc + (size_t)g * max_len * HD;
+
+  for (int p0 = start + kStep * warp; p0 < end; p0 += kStep * kSplitWarps) {
+    float kf[kStep][E], vf[kStep][E];
+#pragma unroll
+    for (int u = 0; u < kStep; ++u)
+      if (p0 + u < end) load_lane<HD>(kb + (size_t)(p0 + u) * HD, lane, kf[u]);
+#pragma unroll
+    for (int u = 0; u < kStep; ++u)
+      if (p0 + u < end) load_lane<HD>(vb + (size_t)(p0 + u) * HD, lane, vf[u]);
+#pragma unroll
+    for (int j = 0; j < GQ; ++j) {
+      float sc[kStep];
+#pragma unroll
+      for (int u = 0; u < kStep; ++u) {
+        float dsum = 0.f;
+        if (p0 + u < end) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) dsum = fmaf(qf[j][e], kf[u][e], dsum);
+        }
+        sc[u] = dsum;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int u = 0; u < kStep; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+      }
+      float mn = m[j];
+#pragma unroll
+      for (int u = 0; u < kStep; ++u) {
+        sc[u] = (p0 + u < end) ? sc[u] * scale : -INFINITY;
+        mn = fmaxf(mn, sc[u]);
+      }
+      const float corr = expf(m[j] - mn);
+      l[j] *= corr;
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[j][e] *= corr;
+#pragma unroll
+      for (int u = 0; u < kStep; ++u) {
+        if (p0 + u < end) {
+          const float pe = expf(sc[u] - mn);
+          l[j] += pe;
+#pragma unroll
+          for (int e = 0; e < E; ++e) acc[j][e] = fmaf(pe, vf[u][e], acc[j][e]);
+        }
+      }
+      m[j] = mn;
+    }
+  }
+  // per head: merge the warps in warp order (thread c owns output dim c), as attn_split_kernel
+#pragma unroll
+  for (int j = 0; j < GQ; ++j) {
+    if (lane == 0) { sm[warp] = m[j]; sl[warp] = l[j]; }
+#pragma unroll
+    for (int e = 0; e < E; ++e) so[warp][lane * E + e] = acc[j][e];
+    __syncthreads();
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kSplitWarps; ++w) M = fmaxf(M, sm[w]);
+    float L = 0.f;
+    const size_t slot = ((size_t)t * Hq + g * GQ + j) * NS + s;
+    for (int c = threadIdx.x; c < HD; c += blockDim.x) {
+      float O = 0.f;
+      L = 0.f;
+      if (M != -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < kSplitWarps; ++w) {
+          const float f = expf(sm[w] - M);
+          L += sl[w] * f;
+          O += so[w][c] * f;
+        }
+      }
+      part_o[slot * HD + c] = O;
+    }
+    if (threadIdx.x == 0) {
+      part_ml[slot * 2] = M;
+      part_ml[slot * 2 + 1] = L;
+    }
+    __syncthreads();
+  }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(HD)
 attn_merge_kernel(const float* part_o, const float* part_ml,
@@ -229,11 +342,22 @@ extern "C" int qe_attn_decode(const void* q, const void* kc, const void* vc, con
   if (n < 1 || n > QE_MAX_ROWS || Hq < 1 || Hkv < 1 || Hq % Hkv || NS < 1) return QE_ERR_ARG;
   cudaStream_t s = (cudaStream_t)stream;
   const dim3 grid(Hq, NS, n);
+  const int gq = Hq / Hkv;
+  const dim3 ggrid(Hkv, NS, n);
+#define QB_GQA(HD, GQ)                                                                            \
+  launch(attn_split_gqa_kernel<HD, GQ>, ggrid, dim3(kSplitWarps * 32), 0, s, pdl_on(),            \
+         (const bf16*)q, (const bf16*)kc, (const bf16*)vc, pos, part_o, part_ml, Hq, max_len, scale)
 #define QB_DEC(HD)                                                                                \
   {                                                                                               \
-    int e = (int)launch(attn_split_kernel<HD>, grid, dim3(kSplitWarps * 32), 0, s, pdl_on(),      \
-                        (const bf16*)q, (const bf16*)kc, (const bf16*)vc, pos, part_o, part_ml,   \
-                        Hq, Hkv, max_len, scale);                                                 \
+    int e;                                                                                        \
+    if (gq == 2) e = (int)QB_GQA(HD, 2);                                                          \
+    else if (gq == 3) e = (int)QB_GQA(HD, 3);                                                     \
+    else if (gq == 4) e = (int)QB_GQA(HD, 4);                                                     \
+    else if (gq == 6) e = (int)QB_GQA(HD, 6);                                                     \
+    else                                                                                          \
+      e = (int)launch(attn_split_kernel<HD>, grid, dim3(kSplitWarps * 32), 0, s, pdl_on(),        \
+                      (const bf16*)q, (const bf16*)kc, (const bf16*)vc, pos, part_o, part_ml,     \
+                      Hq, Hkv, max_len, scale);                                                   \
     if (e) return e;                                                                              \
     return (int)launch(attn_merge_kernel<HD>, dim3(Hq, n), dim3(HD), 0, s, pdl_on(),              \
                        (const float*)part_o, (const float*)part_ml, (const bf16*)qg, ldp,         \
@@ -243,5 +367,6 @@ extern "C" int qe_attn_decode(const void* q, const void* kc, const void* vc, con
   if (hd == 128) QB_DEC(128)
   if (hd == 64) QB_DEC(64)
 #undef QB_DEC
+#undef QB_GQA
   return QE_ERR_ARG;
 }

@@ -118,6 +118,7 @@ class Engine:
         self._alloc()
         self.graphs = {}
         self.graph_kernels = {}  # kernels of this library per captured graph
+        self.start_pos = 0     # positions [0, start_pos) hold a pre-filled context (set_context)
         self.force_a = -1      # forced acceptance length for verify passes (< 0: off)
         self.truth = torch.zeros(1, dtype=I32, device=self.dev)
         _C.set_gdn_early(True)  # safe here: passes start with a fully ordered kernel (see _main)
@@ -182,6 +183,23 @@ class Engine:
                 L["ring"].zero_()
                 L["S"].zero_()
         self.ctl.zero_()
+        if self.start_pos:
+            self.ctl[self.POS].fill_(self.start_pos)
+
+    @torch.no_grad()
+    def set_context(self, length: int, seed: int = 99):
+        """Measurement harness for long caches: pretend `length` positions were already decoded.
+        K and V rows [0, length) of every attention layer (and the draft head's) are filled with
+        seeded N(0, 1) values; sequences then start at position `length` (DeltaNet state empty)."""
+        assert 0 <= length < self.max_len - 2 * NMAX
+        g = torch.Generator(device=self.dev).manual_seed(seed)
+        for L in self.layers + ([self.mtp] if self.has_mtp else []):
+            if "kc" in L:
+                for c in (L["kc"], L["vc"]):
+                    for h in range(c.shape[0]):
+                        c[h, :length].copy_(torch.randn(length, c.shape[2], generator=g, device=self.dev))
+        self.start_pos = int(length)
+        self.reset()
 
     # ------------------------------------------------------------------------------------------
     # A matrix whose input is split over tensor-parallel ranks (out / o_proj, down, mtp.fc) leaves
@@ -377,8 +395,8 @@ class Engine:
     def generate(self, prompt, n_new, timing=False, chunk=NMAX):
         """Plain greedy: prefill, then n_new - 1 one-row passes. Returns n_new token ids
         (timing=True adds prefill_s, decode_s)."""
-        P = len(prompt)
-        assert P + n_new + 1 <= self.max_len
+        P, P0 = len(prompt), self.start_pos + len(prompt)
+        assert P0 + n_new + 1 <= self.max_len
         self._ensure(self._prefill_keys(P, False, 0, chunk) | {(1, False, 0, False)})
         self.reset()
         e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
@@ -390,7 +408,7 @@ class Engine:
             g.replay()
         e2.record()
         torch.cuda.synchronize()
-        gen = self.log[P:P + n_new].tolist()
+        gen = self.log[P0:P0 + n_new].tolist()
         if timing:
             return gen, e0.elapsed_time(e1) / 1e3, e1.elapsed_time(e2) / 1e3
         return gen
@@ -402,12 +420,13 @@ class Engine:
         greedy continuation replaces the drafts before every verify so that exactly `a` are
         accepted (measurement harness). timing=True adds prefill_s, decode_s and a stats dict."""
         assert self.has_mtp and 1 <= k <= NMAX - 1
-        P = len(prompt)
-        assert P + n_new + 2 * NMAX + 2 <= self.max_len
+        P, P0 = len(prompt), self.start_pos + len(prompt)
+        assert P0 + n_new + 2 * NMAX + 2 <= self.max_len
         force = force_accept is not None
         if force:
             assert truth is not None and 0 <= force_accept <= k
-            self.truth = torch.tensor(list(truth), dtype=I32, device=self.dev)
+            # indexed by absolute position
+            self.truth = torch.tensor([0] * self.start_pos + list(truth), dtype=I32, device=self.dev)
             self.force_a = int(force_accept)
             self.graphs.pop((k + 1, True, k, True), None)  # truth buffer address changed
         self._ensure(self._prefill_keys(P, True, k, chunk) | {(k + 1, True, k, force)})
@@ -419,15 +438,15 @@ class Engine:
         self.ctl[16:].zero_()
         e1.record()
         g = self.graphs[(k + 1, True, k, force)]
-        target = P + n_new - 1
-        pos = P
+        target = P0 + n_new - 1
+        pos = P0
         while pos < target:
             for _ in range(max(1, (target - pos) // (k + 1))):
                 g.replay()
             pos = int(self.ctl[self.POS].item())  # the only host sync: once per batch of cycles
         e2.record()
         torch.cuda.synchronize()
-        gen = self.log[P:P + n_new].tolist()
+        gen = self.log[P0:P0 + n_new].tolist()
         if not timing:
             return gen
         c = self.ctl.tolist()

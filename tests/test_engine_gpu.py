@@ -138,3 +138,22 @@ def test_oracle_greedy_agreement_reported(setup):
     same = next((i for i, (a, b) in enumerate(zip(gen, g["tokens"])) if a != b), 64)
     print(f"\nengine greedy == reference CPU greedy for the first {same} of 64 tokens")
     assert same >= 8
+
+
+def test_prefilled_context_spec_equals_plain(setup):
+    """Long-cache harness: positions [0, 300) hold seeded K/V, the sequence starts at 300; the
+    speculative output must still equal the plain output token for token (rollback indices,
+    forced drafts and the log are all in absolute positions)."""
+    from qengine_b200.engine import Engine
+    from qengine_b200 import synth
+    cfg, Wp, _ = setup
+    eng = Engine(cfg, synth.model_to(Wp, "cuda"), max_len=512, attn_splits=8)
+    eng.set_context(300)
+    g = torch.load(G / "greedy.pt")
+    plain = eng.generate(g["prompt"], 40)
+    assert int(eng.ctl[eng.POS]) == 300 + 32 + 39
+    assert eng.generate_spec(g["prompt"], 40, 3) == plain
+    for a in (0, 2, 4):
+        assert eng.generate_spec(g["prompt"], 40, 4, force_accept=a, truth=g["prompt"] + plain + [0] * 16) == plain
+    base = Engine(cfg, synth.model_to(Wp, "cuda"), max_len=512, attn_splits=8).generate(g["prompt"], 40)
+    assert base != plain  # the context is really attended to
