@@ -169,6 +169,9 @@ int qe_attn_prep(const void* qg, const void* k, const void* v, long ldp, const v
 int qe_attn_decode(const void* q, const void* kc, const void* vc, const int* pos, const void* qg,
                    long ldp, float* part_o, float* part_ml, void* out, long ldo, int n, int Hq,
                    int Hkv, int hd, int max_len, int NS, float scale, void* stream);
+/* Sticky error word of the attention ring waits (0 = none, 1 producer, 2 consumer wait ran out);
+ * synchronises. No counterpart in the reference. */
+int qe_attn_error(void);
 
 /* ------------------------------------------------------------------------------------------
  * Run-time switches and L2 controls (csrc/ops.h:31-36).

@@ -139,6 +139,11 @@ def argmax_merge(vals, idx, out):
                               _stream()), "argmax_merge")
 
 
+def attn_error():
+    """Sticky error word of the attention kernel's bounded ring waits (0 = none); synchronises."""
+    return int(lib.qe_attn_error())
+
+
 def accept(in_tok, am, n, ctl, next_tok, log):
     for t in (in_tok, am, ctl, next_tok, log):
         _chk(t, I32, "int buffer")

@@ -68,6 +68,7 @@ SIGNATURES = {
                              c_int, c_int, c_float, P]),
     "qe_attn_decode": (c_int, [P, P, P, P, P, c_long, P, P, P, c_long, c_int, c_int, c_int, c_int,
                                c_int, c_int, c_float, P]),
+    "qe_attn_error": (c_int, []),
     "qe_set_pdl_trigger": (None, [c_int]),
     "qe_set_pdl_launch": (None, [c_int]),
     "qe_set_gdn_early": (None, [c_int]),

@@ -6,11 +6,12 @@
 //   prep    per head: xn = bf16(x * rsqrt(mean x^2 + eps) * (1 + w)); rotate-half RoPE on the
 //           first rd dims with bf16 rounding after every elementwise op (cos/sin rounded to
 //           bf16 first); q -> q_out, k and raw v -> cache row pos + t (skipped past max_len).
-//   decode  split-KV flash decoding: CTA (head, split, row) reduces its slice of the row's
-//           causal prefix [0, pos + t] with an online softmax in fp32, four cache positions per
-//           warp step so that four independent 16-byte K loads and V loads are in flight per
-//           lane; a second kernel merges the NS partials, rounds o = bf16(O / L) and applies
-//           bf16(sigmoid(gate)).
+//   decode  split-KV flash decoding: the row's causal prefix [0, pos + t] is cut into NS slices; a
+//           CTA (KV head, split, row) streams its slice through shared memory once for all query
+//           heads of the group (attn_stream_kernel; attn_split_kernel, one CTA per query head with
+//           direct loads, serves group sizes outside {2, 3, 4, 6}); online softmax in fp32, four
+//           positions per step; a second kernel merges the NS partials, rounds o = bf16(O / L)
+//           and applies bf16(sigmoid(gate)).
 // Row independence: the slice boundaries of row t depend only on its own prefix length, so row t
 // of an n-row call is bit-identical to a 1-row call at position pos + t.
 #include "common.cuh"
@@ -173,116 +174,161 @@ attn_split_kernel(const bf16* q, const bf16* kc,
   }
 }
 
-// The same split for all GQ query heads of one KV head in one CTA: every K / V row of the slice is
-// loaded once and used by the GQ heads that share it (grouped-query attention), instead of once
-// per query head. With a long cache the KV stream is the whole cost of the layer (134 MB per layer
-// at 32K positions of the 27B shape), so this divides the L2 / HBM traffic by GQ. Position-to-warp
-// assignment, step size and the order of every sum are those of attn_split_kernel: per head the
-// result is bit-identical to it.
+// Grouped-query split fed through shared memory. CTA (KV head, split, row) = GQ consumer warps, one
+// per query head of the group, + one producer warp whose lane 0 streams the K and V rows of the
+// slice into a ring of kRingStages stages of kRingPos positions with bulk copies (cp.async.bulk,
+// completion on an mbarrier). Every row is fetched from L2 / HBM once per group instead of once per
+// query head, and a CTA needs few registers and 32 KB of shared memory, so several CTAs (dozens of
+// warps) are resident per SM: with a long cache the layer is a pure KV stream (134 MB per layer at
+// 32K positions of the 27B shape) and needs that many copies in flight. A consumer warp walks the
+// positions of the slice in order, four at a time (lane = 8 consecutive dims, butterfly reduction,
+// online softmax in fp32), and writes its own partial (no cross-warp merge). Slice boundaries
+// depend only on the row's prefix length: row t of an n-row call is bit-identical to a 1-row call.
+// Waits are bounded; a wait that runs out sets g_attn_error and the warp leaves.
+constexpr int kRingPos = 8, kRingStages = 4;
+__device__ int g_attn_error = 0;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ bool bar_wait(uint64_t* b, uint32_t parity, int limit = 1 << 22) {
+  const uint32_t addr = smem_addr(b);
+  for (int it = 0; it < limit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
 template <int HD, int GQ>
-__global__ void __launch_bounds__(kSplitWarps * 32)
-attn_split_gqa_kernel(const bf16* q, const bf16* kc, const bf16* vc, const int* pos_ptr, float* part_o,
-                      float* part_ml, int Hq, int max_len, float scale) {
+__global__ void __launch_bounds__((GQ + 1) * 32)
+attn_stream_kernel(const bf16* q, const bf16* kc, const bf16* vc, const int* pos_ptr, float* part_o,
+                   float* part_ml, int Hq, int max_len, float scale) {
   constexpr int E = HD / 32;
+  constexpr uint32_t kStageBytes = kRingPos * HD * 2;  // K (or V) rows of one stage
   dep_release();
-  dep_wait();
-  __shared__ float sm[kSplitWarps], sl[kSplitWarps];
-  __shared__ float so[kSplitWarps][HD];
+  extern __shared__ __align__(128) unsigned char ring[];  // [stage][K rows | V rows]
+  __shared__ uint64_t full[kRingStages], empty[kRingStages];
   const int g = blockIdx.x, s = blockIdx.y, NS = gridDim.y, t = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kRingStages; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&full[i])), "r"(1));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&empty[i])), "r"(GQ));
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  dep_wait();  // pos, q and the newest cache rows come from kernels just before this one
   const int len = min(max(pos_ptr[0] + t + 1, 0), max_len);
   const int chunk = (len + NS - 1) / NS;
   const int start = s * chunk, end = min(len, start + chunk);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nstage = end > start ? (end - start + kRingPos - 1) / kRingPos : 0;
 
-  float qf[GQ][E], acc[GQ][E], m[GQ], l[GQ];
-#pragma unroll
-  for (int j = 0; j < GQ; ++j) {
-    load_lane<HD>(q + ((size_t)t * Hq + g * GQ + j) * HD, lane, qf[j]);
-    m[j] = -INFINITY;
-    l[j] = 0.f;
-#pragma unroll
-    for (int e = 0; e < E; ++e) acc[j][e] = 0.f;
+  if (warp == GQ) {  // producer
+    if (lane == 0) {
+      const bf16* kb = kc + ((size_t)g * max_len + start) * HD;
+      const bf16* vb = vc + ((size_t)g * max_len + start) * HD;
+      for (int st = 0; st < nstage; ++st) {
+        const int slot = st % kRingStages;
+        if (st >= kRingStages && !bar_wait(&empty[slot], ((st / kRingStages) - 1) & 1)) {
+          atomicExch(&g_attn_error, 1);
+          break;
+        }
+        const uint32_t cnt = (uint32_t)min(kRingPos, end - start - st * kRingPos);
+        const uint32_t bytes = cnt * HD * 2;
+        unsigned char* dst = ring + (size_t)slot * 2 * kStageBytes;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(&full[slot])),
+                     "r"(2 * bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         smem_addr(dst)), "l"(kb + (size_t)st * kRingPos * HD), "r"(bytes), "r"(smem_addr(&full[slot]))
+                     : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         smem_addr(dst + kStageBytes)), "l"(vb + (size_t)st * kRingPos * HD), "r"(bytes),
+                     "r"(smem_addr(&full[slot]))
+                     : "memory");
+      }
+    }
+    return;
   }
-  const bf16* kb = kc + (size_t)g * max_len * HD;
-  const bf16* vb = vc + (size_t)g * max_len * HD;
 
-  for (int p0 = start + kStep * warp; p0 < end; p0 += kStep * kSplitWarps) {
-    float kf[kStep][E], vf[kStep][E];
+  const int h = g * GQ + warp;
+  float qf[E], acc[E], m = -INFINITY, l = 0.f;
+  load_lane<HD>(q + ((size_t)t * Hq + h) * HD, lane, qf);
 #pragma unroll
-    for (int u = 0; u < kStep; ++u)
-      if (p0 + u < end) load_lane<HD>(kb + (size_t)(p0 + u) * HD, lane, kf[u]);
-#pragma unroll
-    for (int u = 0; u < kStep; ++u)
-      if (p0 + u < end) load_lane<HD>(vb + (size_t)(p0 + u) * HD, lane, vf[u]);
-#pragma unroll
-    for (int j = 0; j < GQ; ++j) {
-      float sc[kStep];
-#pragma unroll
-      for (int u = 0; u < kStep; ++u) {
-        float dsum = 0.f;
-        if (p0 + u < end) {
-#pragma unroll
-          for (int e = 0; e < E; ++e) dsum = fmaf(qf[j][e], kf[u][e], dsum);
-        }
-        sc[u] = dsum;
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-        for (int u = 0; u < kStep; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
-      }
-      float mn = m[j];
-#pragma unroll
-      for (int u = 0; u < kStep; ++u) {
-        sc[u] = (p0 + u < end) ? sc[u] * scale : -INFINITY;
-        mn = fmaxf(mn, sc[u]);
-      }
-      const float corr = expf(m[j] - mn);
-      l[j] *= corr;
-#pragma unroll
-      for (int e = 0; e < E; ++e) acc[j][e] *= corr;
-#pragma unroll
-      for (int u = 0; u < kStep; ++u) {
-        if (p0 + u < end) {
-          const float pe = expf(sc[u] - mn);
-          l[j] += pe;
-#pragma unroll
-          for (int e = 0; e < E; ++e) acc[j][e] = fmaf(pe, vf[u][e], acc[j][e]);
-        }
-      }
-      m[j] = mn;
+  for (int e = 0; e < E; ++e) acc[e] = 0.f;
+
+  for (int st = 0; st < nstage; ++st) {
+    const int slot = st % kRingStages;
+    if (!bar_wait(&full[slot], (st / kRingStages) & 1)) {
+      atomicExch(&g_attn_error, 2);
+      break;
     }
+    const bf16* ks = reinterpret_cast<const bf16*>(ring + (size_t)slot * 2 * kStageBytes);
+    const bf16* vs = reinterpret_cast<const bf16*>(ring + (size_t)slot * 2 * kStageBytes + kStageBytes);
+    const int cnt = min(kRingPos, end - start - st * kRingPos);
+#pragma unroll
+    for (int p0 = 0; p0 < kRingPos; p0 += kStep) {
+      if (p0 < cnt) {
+        float sc[kStep];
+#pragma unroll
+        for (int u = 0; u < kStep; ++u) {
+          float dsum = 0.f;
+          if (p0 + u < cnt) {
+            float kf[E];
+            load_lane<HD>(ks + (size_t)(p0 + u) * HD, lane, kf);
+#pragma unroll
+            for (int e = 0; e < E; ++e) dsum = fmaf(qf[e], kf[e], dsum);
+          }
+          sc[u] = dsum;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+          for (int u = 0; u < kStep; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+        }
+        float mn = m;
+#pragma unroll
+        for (int u = 0; u < kStep; ++u) {
+          sc[u] = (p0 + u < cnt) ? sc[u] * scale : -INFINITY;
+          mn = fmaxf(mn, sc[u]);
+        }
+        const float corr = expf(m - mn);  // first step: exp(-inf) = 0
+        l *= corr;
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] *= corr;
+#pragma unroll
+        for (int u = 0; u < kStep; ++u) {
+          if (p0 + u < cnt) {
+            const float pe = expf(sc[u] - mn);
+            l += pe;
+            float vf[E];
+            load_lane<HD>(vs + (size_t)(p0 + u) * HD, lane, vf);
+#pragma unroll
+            for (int e = 0; e < E; ++e) acc[e] = fmaf(pe, vf[e], acc[e]);
+          }
+        }
+        m = mn;
+      }
+    }
+    __syncwarp();
+    if (lane == 0)
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(&empty[slot])) : "memory");
   }
-  // per head: merge the warps in warp order (thread c owns output dim c), as attn_split_kernel
+  // one warp = one head of one split: its running (m, l, acc) is the partial (acc is not yet
+  // divided by l, as in attn_split_kernel)
+  const size_t slot_o = ((size_t)t * Hq + h) * NS + s;
+  float* po = part_o + slot_o * HD + lane * E;
 #pragma unroll
-  for (int j = 0; j < GQ; ++j) {
-    if (lane == 0) { sm[warp] = m[j]; sl[warp] = l[j]; }
-#pragma unroll
-    for (int e = 0; e < E; ++e) so[warp][lane * E + e] = acc[j][e];
-    __syncthreads();
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kSplitWarps; ++w) M = fmaxf(M, sm[w]);
-    float L = 0.f;
-    const size_t slot = ((size_t)t * Hq + g * GQ + j) * NS + s;
-    for (int c = threadIdx.x; c < HD; c += blockDim.x) {
-      float O = 0.f;
-      L = 0.f;
-      if (M != -INFINITY) {
-#pragma unroll
-        for (int w = 0; w < kSplitWarps; ++w) {
-          const float f = expf(sm[w] - M);
-          L += sl[w] * f;
-          O += so[w][c] * f;
-        }
-      }
-      part_o[slot * HD + c] = O;
-    }
-    if (threadIdx.x == 0) {
-      part_ml[slot * 2] = M;
-      part_ml[slot * 2 + 1] = L;
-    }
-    __syncthreads();
+  for (int e = 0; e < E; ++e) po[e] = (m == -INFINITY) ? 0.f : acc[e];
+  if (lane == 0) {
+    part_ml[slot_o * 2] = m;
+    part_ml[slot_o * 2 + 1] = (m == -INFINITY) ? 0.f : l;
   }
 }
 
@@ -312,6 +358,14 @@ attn_merge_kernel(const float* part_o, const float* part_ml,
 
 inline bool pdl_on() { return pdl_launch_enabled() && pdl_trigger_enabled(); }
 
+template <int HD, int GQ>
+cudaError_t launch_stream(dim3 grid, cudaStream_t s, bool pdl, const bf16* q, const bf16* kc, const bf16* vc,
+                          const int* pos, float* part_o, float* part_ml, int Hq, int max_len, float scale) {
+  constexpr size_t smem = (size_t)kRingStages * 2 * kRingPos * HD * 2;
+  return launch(attn_stream_kernel<HD, GQ>, grid, dim3((GQ + 1) * 32), smem, s, pdl, q, kc, vc, pos, part_o,
+                part_ml, Hq, max_len, scale);
+}
+
 }  // namespace
 }  // namespace qb
 
@@ -335,6 +389,13 @@ extern "C" int qe_attn_prep(const void* qg, const void* k, const void* v, long l
   return QE_ERR_ARG;
 }
 
+extern "C" int qe_attn_error(void) {
+  int h = 0;
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(&h, g_attn_error, sizeof(int));
+  return h;
+}
+
 extern "C" int qe_attn_decode(const void* q, const void* kc, const void* vc, const int* pos,
                               const void* qg, long ldp, float* part_o, float* part_ml, void* out,
                               long ldo, int n, int Hq, int Hkv, int hd, int max_len, int NS,
@@ -345,8 +406,8 @@ extern "C" int qe_attn_decode(const void* q, const void* kc, const void* vc, con
   const int gq = Hq / Hkv;
   const dim3 ggrid(Hkv, NS, n);
 #define QB_GQA(HD, GQ)                                                                            \
-  launch(attn_split_gqa_kernel<HD, GQ>, ggrid, dim3(kSplitWarps * 32), 0, s, pdl_on(),            \
-         (const bf16*)q, (const bf16*)kc, (const bf16*)vc, pos, part_o, part_ml, Hq, max_len, scale)
+  launch_stream<HD, GQ>(ggrid, s, pdl_on(), (const bf16*)q, (const bf16*)kc, (const bf16*)vc, pos,  \
+                        part_o, part_ml, Hq, max_len, scale)
 #define QB_DEC(HD)                                                                                \
   {                                                                                               \
     int e;                                                                                        \

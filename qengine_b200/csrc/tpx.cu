@@ -2,7 +2,7 @@
 // single-GPU reference).
 //
 // A matrix split along K over t ranks leaves every rank with fp32 partial rows [n, H]. The
-// consumer is always "residual += sum of the partial rows; RMSNorm1p". tp_norm_kernel does the
+// consumer is always "residual += sum of the partial rows; RMSNorm1p". tp_xnorm_kernel does the
 // exchange and the norm in ONE kernel over peer memory: every rank stores its partial row straight
 // into a slot of every peer's exchange block (NVLink peer stores), and reads the other ranks'
 // rows from its own block as they land. Transport is a flag-in-data protocol: each 8-byte store
@@ -94,43 +94,17 @@ __device__ __forceinline__ char* norm_slot(char* base, const TpView& tv, uint32_
   return base + kNormOff + ((((long)(e & 1u) * tv.world + src) * kRows + row) * (long)tv.H) * 8;
 }
 
-// RMSNorm1p with residual delta = bf16(sum over ranks of the fp32 partial rows). Thread layout and
-// arithmetic follow rmsnorm1p_vec_kernel (rowops.cu), so one rank / one part gives its bits.
-// EXCHANGE: part = this rank's rows [rows, H] (stride ldp), pushed to the peers and summed with
-// theirs. Otherwise part = gathered rows [nparts, rows, H] contiguous, summed in order.
-template <int PKT, bool EXCHANGE>
+// RMSNorm1p with residual delta = bf16(sum over p of parts[p]), parts = gathered fp32 partial rows
+// [nparts, rows, H] contiguous, summed in ascending p. Thread layout and arithmetic follow
+// rmsnorm1p_vec_kernel (rowops.cu), so one part gives its bits.
+template <int PKT>
 __global__ void __launch_bounds__(256)
-tp_norm_kernel(TpView tv, bf16* x, const float* part, int nparts, const bf16* w, bf16* out, int rows, int H,
-               long ldx, long ldp, long ldo, float eps) {
+tp_norm_kernel(bf16* x, const float* part, int nparts, const bf16* w, bf16* out, int rows, int H, long ldx,
+               long ldo, float eps) {
   dep_release();
   dep_wait();
   __shared__ float scratch[32];
   const int row = blockIdx.x, npk = H >> 3;
-  int* hdr = EXCHANGE ? reinterpret_cast<int*>(tv.base[tv.rank]) : nullptr;
-  uint32_t e = 0;
-  bool dead = false;
-  float mine[PKT][8];
-  if (EXCHANGE) {
-    e = (uint32_t)(*(volatile int*)(hdr + row)) + 1u;
-    dead = *(volatile int*)(hdr + kErrWord) != 0;
-#pragma unroll
-    for (int p = 0; p < PKT; ++p) {
-      const int i = threadIdx.x + p * blockDim.x;
-      if (i < npk) {
-        const float4* pr = reinterpret_cast<const float4*>(part + (long)row * ldp) + 2 * i;
-        const float4 a = pr[0], b = pr[1];
-        mine[p][0] = a.x; mine[p][1] = a.y; mine[p][2] = a.z; mine[p][3] = a.w;
-        mine[p][4] = b.x; mine[p][5] = b.y; mine[p][6] = b.z; mine[p][7] = b.w;
-        for (int r = 0; r < tv.world; ++r) {
-          if (r == tv.rank) continue;
-          char* d = norm_slot(tv.base[r], tv, e, tv.rank, row) + (long)i * 64;
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            st_v4(d + 16 * q, __float_as_uint(mine[p][2 * q]), e, __float_as_uint(mine[p][2 * q + 1]), e);
-        }
-      }
-    }
-  }
   uint4* xr = reinterpret_cast<uint4*>(x + (long)row * ldx);
   float v[PKT][8];
   float ss = 0.f;
@@ -141,28 +115,11 @@ tp_norm_kernel(TpView tv, bf16* x, const float* part, int nparts, const bf16* w,
       float d[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) d[k] = 0.f;
-      if (EXCHANGE) {
-        for (int src = 0; src < tv.world; ++src) {
-          if (src == tv.rank) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) d[k] += mine[p][k];
-          } else {
-            const char* s = norm_slot(tv.base[tv.rank], tv, e, src, row) + (long)i * 64;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 t = ll_wait(s + 16 * q, e, hdr, tv, src, row, 0, dead);
-              d[2 * q] += __uint_as_float(t.x);
-              d[2 * q + 1] += __uint_as_float(t.z);
-            }
-          }
-        }
-      } else {
-        for (int src = 0; src < nparts; ++src) {
-          const float4* pr = reinterpret_cast<const float4*>(part + ((size_t)src * rows + row) * H) + 2 * i;
-          const float4 a = pr[0], b = pr[1];
-          d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w;
-          d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
-        }
+      for (int src = 0; src < nparts; ++src) {
+        const float4* pr = reinterpret_cast<const float4*>(part + ((size_t)src * rows + row) * H) + 2 * i;
+        const float4 a = pr[0], b = pr[1];
+        d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w;
+        d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
       }
       widen8(xr[i], v[p]);
 #pragma unroll
@@ -185,8 +142,116 @@ tp_norm_kernel(TpView tv, bf16* x, const float* part, int nparts, const bf16* w,
       orow[i] = narrow8(y);
     }
   }
-  // every thread read the sequence number before the barriers inside block_allsum
-  if (EXCHANGE && threadIdx.x == 0) *(volatile int*)(hdr + row) = (int)e;
+}
+
+// The exchange + norm kernel. Two phases with different thread layouts:
+//  gather  all threads (up to 640), one 8-element packet each: push our partial to every peer,
+//          issue the loads of up to four peers' slots at once (a blocking wait per 16 bytes would
+//          serialise ~0.6 us L2 round trips: 30 of them at 4 ranks), re-poll only what has not
+//          landed, add the ranks in ascending order, round once to bf16 -> shared memory;
+//  norm    the first VT threads in the exact layout of rmsnorm1p_vec_kernel (packets tid + p * VT,
+//          same block reduction; idle threads add zeros), so a group of one rank reproduces the
+//          single-GPU bits.
+constexpr int kXThreads = 640;
+template <int PKT>
+__global__ void __launch_bounds__(kXThreads)
+tp_xnorm_kernel(TpView tv, bf16* x, const float* part, const bf16* w, bf16* out, int H, int VT, long ldx,
+                long ldp, long ldo, float eps) {
+  dep_release();
+  dep_wait();
+  extern __shared__ float delta_s[];  // [H] bf16-rounded sum of the ranks' partial rows
+  __shared__ float scratch[32];
+  const int row = blockIdx.x, npk = H >> 3, tid = threadIdx.x;
+  int* hdr = reinterpret_cast<int*>(tv.base[tv.rank]);
+  const uint32_t e = (uint32_t)(*(volatile int*)(hdr + row)) + 1u;
+  bool dead = *(volatile int*)(hdr + kErrWord) != 0;
+
+  for (int i = tid; i < npk; i += blockDim.x) {
+    float mine[8];
+    {
+      const float4* pr = reinterpret_cast<const float4*>(part + (long)row * ldp) + 2 * i;
+      const float4 a = pr[0], b = pr[1];
+      mine[0] = a.x; mine[1] = a.y; mine[2] = a.z; mine[3] = a.w;
+      mine[4] = b.x; mine[5] = b.y; mine[6] = b.z; mine[7] = b.w;
+    }
+    for (int r = 0; r < tv.world; ++r) {
+      if (r == tv.rank) continue;
+      char* d = norm_slot(tv.base[r], tv, e, tv.rank, row) + (long)i * 64;
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        st_v4(d + 16 * q, __float_as_uint(mine[2 * q]), e, __float_as_uint(mine[2 * q + 1]), e);
+    }
+    float d[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) d[k] = 0.f;
+    for (int b0 = 0; b0 < tv.world; b0 += 4) {
+      uint4 rv[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int src = b0 + u;
+        if (src < tv.world && src != tv.rank) {
+          const char* sp = norm_slot(tv.base[tv.rank], tv, e, src, row) + (long)i * 64;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) rv[u][q] = ld_v4(sp + 16 * q);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int src = b0 + u;
+        if (src >= tv.world) continue;
+        if (src == tv.rank) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) d[k] += mine[k];
+          continue;
+        }
+        const char* sp = norm_slot(tv.base[tv.rank], tv, e, src, row) + (long)i * 64;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (rv[u][q].y != e || rv[u][q].w != e) rv[u][q] = ll_wait(sp + 16 * q, e, hdr, tv, src, row, 0, dead);
+          d[2 * q] += __uint_as_float(rv[u][q].x);
+          d[2 * q + 1] += __uint_as_float(rv[u][q].z);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) delta_s[i * 8 + k] = rnd(d[k]);
+  }
+  __syncthreads();
+
+  uint4* xr = reinterpret_cast<uint4*>(x + (long)row * ldx);
+  float v[PKT][8];
+  float ss = 0.f;
+  if (tid < VT) {
+#pragma unroll
+    for (int p = 0; p < PKT; ++p) {
+      const int i = tid + p * VT;
+      if (i < npk) {
+        widen8(xr[i], v[p]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[p][k] = rnd(v[p][k] + delta_s[i * 8 + k]);
+        xr[i] = narrow8(v[p]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss = fmaf(v[p][k], v[p][k], ss);
+      }
+    }
+  }
+  const float inv = rsqrtf(block_allsum(ss, scratch) / (float)H + eps);
+  if (tid < VT) {
+    uint4* orow = reinterpret_cast<uint4*>(out + (long)row * ldo);
+#pragma unroll
+    for (int p = 0; p < PKT; ++p) {
+      const int i = tid + p * VT;
+      if (i < npk) {
+        float g[8], y[8];
+        widen8(__ldg(reinterpret_cast<const uint4*>(w) + i), g);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) y[k] = v[p][k] * inv * (1.0f + g[k]);
+        orow[i] = narrow8(y);
+      }
+    }
+  }
+  // every thread read the sequence number before the barriers above
+  if (tid == 0) *(volatile int*)(hdr + row) = (int)e;
 }
 
 __device__ __forceinline__ bool beats(float a, int ia, float b, int ib) {
@@ -243,11 +308,10 @@ tp_argmax_kernel(TpView tv, const float* cand_v, const int* cand_i, int rows, in
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 inline bool pdl_on() { return pdl_launch_enabled(); }
 
-template <bool EX>
-int launch_norm(const TpView& tv, void* x, const float* part, int nparts, const void* w, void* out, int rows,
-                int H, long ldx, long ldp, long ldo, float eps, cudaStream_t s) {
-  if (rows < 1 || rows > kRows || H < 8 || H % 8 || H > 8 * 256 * 4 || ldx % 8 || ldo % 8 || ldp % 4 ||
-      !aligned16(x) || !aligned16(out) || !aligned16(w) || !aligned16(part))
+int launch_parts_norm(void* x, const float* part, int nparts, const void* w, void* out, int rows, int H, long ldx,
+                      long ldo, float eps, cudaStream_t s) {
+  if (rows < 1 || rows > kRows || H < 8 || H % 8 || H > 8 * 256 * 4 || ldx % 8 || ldo % 8 || !aligned16(x) ||
+      !aligned16(out) || !aligned16(w) || !aligned16(part))
     return QE_ERR_ARG;
   bf16* X = (bf16*)x;
   const bf16* W = (const bf16*)w;
@@ -255,14 +319,14 @@ int launch_norm(const TpView& tv, void* x, const float* part, int nparts, const 
   const int npk = H / 8;
   if (npk <= 256) {
     const int threads = std::max(32, (npk + 31) / 32 * 32);
-    return (int)launch(tp_norm_kernel<1, EX>, dim3(rows), dim3(threads), 0, s, pdl_on(), tv, X, part, nparts, W,
-                       O, rows, H, ldx, ldp, ldo, eps);
+    return (int)launch(tp_norm_kernel<1>, dim3(rows), dim3(threads), 0, s, pdl_on(), X, part, nparts, W, O, rows, H,
+                       ldx, ldo, eps);
   }
   if (npk <= 512)
-    return (int)launch(tp_norm_kernel<2, EX>, dim3(rows), dim3(256), 0, s, pdl_on(), tv, X, part, nparts, W, O,
-                       rows, H, ldx, ldp, ldo, eps);
-  return (int)launch(tp_norm_kernel<4, EX>, dim3(rows), dim3(256), 0, s, pdl_on(), tv, X, part, nparts, W, O,
-                     rows, H, ldx, ldp, ldo, eps);
+    return (int)launch(tp_norm_kernel<2>, dim3(rows), dim3(256), 0, s, pdl_on(), X, part, nparts, W, O, rows, H, ldx,
+                       ldo, eps);
+  return (int)launch(tp_norm_kernel<4>, dim3(rows), dim3(256), 0, s, pdl_on(), X, part, nparts, W, O, rows, H, ldx,
+                     ldo, eps);
 }
 
 }  // namespace
@@ -273,8 +337,7 @@ using namespace qb;
 extern "C" int qe_rmsnorm1p_parts(void* x, const float* parts, int nparts, const void* w, void* out, int rows,
                                   int H, long ldx, long ldo, float eps, void* stream) {
   if (nparts < 1) return QE_ERR_ARG;
-  TpView none = {};
-  return launch_norm<false>(none, x, parts, nparts, w, out, rows, H, ldx, H, ldo, eps, (cudaStream_t)stream);
+  return launch_parts_norm(x, parts, nparts, w, out, rows, H, ldx, ldo, eps, (cudaStream_t)stream);
 }
 
 extern "C" long qe_tp_block_bytes(int H, int world) {
@@ -341,7 +404,26 @@ extern "C" int qe_tp_exchange_norm(void* comm, void* x, const float* part, const
                                    long ldx, long ldp, long ldo, float eps, void* stream) {
   if (!comm) return QE_ERR_ARG;
   const Comm* c = static_cast<Comm*>(comm);
-  return launch_norm<true>(c->v, x, part, 1, w, out, rows, c->v.H, ldx, ldp, ldo, eps, (cudaStream_t)stream);
+  const int H = c->v.H, npk = H / 8;
+  if (rows < 1 || rows > kRows || H > 8 * 256 * 4 || ldx % 8 || ldo % 8 || ldp % 4 || !aligned16(x) ||
+      !aligned16(out) || !aligned16(w) || !aligned16(part))
+    return QE_ERR_ARG;
+  // norm layout of qe_rmsnorm1p: VT threads x PKT packets
+  const int VT = npk <= 256 ? std::max(32, (npk + 31) / 32 * 32) : 256;
+  const int threads = std::max(VT, std::min(kXThreads, (npk + 31) / 32 * 32));
+  const size_t smem = (size_t)H * sizeof(float);
+  cudaStream_t s = (cudaStream_t)stream;
+  bf16* X = (bf16*)x;
+  const bf16* W = (const bf16*)w;
+  bf16* O = (bf16*)out;
+  if (npk <= 256)
+    return (int)launch(tp_xnorm_kernel<1>, dim3(rows), dim3(threads), smem, s, pdl_on(), c->v, X, part, W, O, H, VT,
+                       ldx, ldp, ldo, eps);
+  if (npk <= 512)
+    return (int)launch(tp_xnorm_kernel<2>, dim3(rows), dim3(threads), smem, s, pdl_on(), c->v, X, part, W, O, H, VT,
+                       ldx, ldp, ldo, eps);
+  return (int)launch(tp_xnorm_kernel<4>, dim3(rows), dim3(threads), smem, s, pdl_on(), c->v, X, part, W, O, H, VT,
+                     ldx, ldp, ldo, eps);
 }
 
 extern "C" int qe_tp_exchange_argmax(void* comm, const float* cand_v, const int* cand_i, int rows, int* out,

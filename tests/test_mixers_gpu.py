@@ -147,7 +147,9 @@ def attn_cfg(hq, hkv, hd, rd):
 
 @pytest.mark.parametrize("hq,hkv,hd,rd,steps,start,n", [
     (8, 2, 256, 64, 20, 0, 1), (24, 4, 256, 64, 6, 0, 1), (8, 2, 256, 64, 3, 4094, 1), (1, 1, 256, 64, 5, 125, 1),
-    (8, 2, 256, 64, 24, 0, 8), (24, 4, 256, 64, 12, 100, 3), (8, 2, 64, 16, 20, 0, 5), (4, 2, 128, 32, 9, 33, 3)])
+    (8, 2, 256, 64, 24, 0, 8), (24, 4, 256, 64, 12, 100, 3), (8, 2, 64, 16, 20, 0, 5), (4, 2, 128, 32, 9, 33, 3),
+    # long slices: the shared-memory ring of the grouped-query kernel wraps many times (groups of 6, 3)
+    (12, 2, 256, 64, 4, 5000, 2), (3, 1, 256, 64, 3, 2100, 3), (16, 2, 128, 32, 2, 700, 1)])
 def test_attention_vs_oracle_and_row_independence(C, hq, hkv, hd, rd, steps, start, n):
     g = torch.Generator().manual_seed(1)
     cfg = attn_cfg(hq, hkv, hd, rd)
@@ -202,6 +204,7 @@ def test_attention_vs_oracle_and_row_independence(C, hq, hkv, hd, rd, steps, sta
             o1 = torch.empty(1, hq * hd, dtype=BF, device=dev)
             C.attn_decode(qr[t:t + 1], kcr, vcr, pos_t + t, qg[t:t + 1], po, pml, o1)
             assert torch.equal(o1[0], out[t]), "row differs from the 1-row pass"
+    assert C.attn_error() == 0
 
 
 def test_attention_never_writes_past_the_cache(C):
