@@ -371,6 +371,25 @@ def run_ours(a):
             d = float(td.item())
             mtp[label] = {"tok_s": (n_new - 1) / d, "tokens_per_cycle": st["tokens_per_cycle"],
                           "ms_per_cycle": d * 1e3 / max(1, st["cycles"]), "identical_to_plain": out == gen}
+    # ---- the same cycle with a pruned draft head (drafts scored over the first --draft-vocab ids) ----
+    if not a.no_mtp and a.draft_vocab > 0:
+        kw = dict(max_len=P + n_new + 32, device=dev, draft_vocab=a.draft_vocab)
+        if world > 1:
+            kw["tp"] = tp.TPGroup(transport=a.transport)
+        eng_d = Engine(cfg, W, **kw)
+        for label, fa in (("a0", 0), ("a4", 4)):
+            eng_d.generate_spec(prompt, n_new, 4, force_accept=fa, truth=truth)
+            barrier()
+            out, _, d, st = eng_d.generate_spec(prompt, n_new, 4, timing=True, force_accept=fa, truth=truth)
+            td = torch.tensor([d], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(td, op=dist.ReduceOp.MAX)
+            d = float(td.item())
+            mtp[f"draft_vocab_{a.draft_vocab}_{label}"] = {
+                "tok_s": (n_new - 1) / d, "tokens_per_cycle": st["tokens_per_cycle"],
+                "ms_per_cycle": d * 1e3 / max(1, st["cycles"]), "identical_to_plain": out == gen}
+        del eng_d
+        torch.cuda.empty_cache()
     exchange_us = exchange_timing(eng) if world > 1 else None
 
     # ---- verify pass alone vs plain step (one graph replay each, same weights) -----------------
@@ -510,6 +529,8 @@ def main():
                     help="tensor-parallel exchange: own peer-memory kernels, or NCCL all-gather + norm")
     ap.add_argument("--context", type=int, default=32768,
                     help="pre-filled cache length of the long-context block (0 = skip it)")
+    ap.add_argument("--draft-vocab", type=int, default=49152,
+                    help="also time the MTP cycle with the draft head pruned to this many ids (0 = skip)")
     ap.add_argument("--no-mtp", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     a = ap.parse_args()

@@ -332,28 +332,57 @@ attn_stream_kernel(const bf16* q, const bf16* kc, const bf16* vc, const int* pos
   }
 }
 
+// Merge of the NS split partials of one (head, row): warp w folds splits w, w + 8, ... into a
+// running (M, L, O) in ascending order (lane = HD / 32 consecutive dims), the 8 warps are combined
+// in warp order, then o = bf16(O / L) * bf16(sigmoid(gate)). The order depends on NS only.
 template <int HD>
-__global__ void __launch_bounds__(HD)
-attn_merge_kernel(const float* part_o, const float* part_ml,
-                  const bf16* qg, long ldp, bf16* out, long ldo, int Hq,
-                  int NS) {
+__global__ void __launch_bounds__(kSplitWarps * 32)
+attn_merge_kernel(const float* part_o, const float* part_ml, const bf16* qg, long ldp, bf16* out, long ldo,
+                  int Hq, int NS) {
+  constexpr int E = HD / 32;
   dep_release();
   dep_wait();
-  const int h = blockIdx.x, c = threadIdx.x, t = blockIdx.y;
+  __shared__ float sm[kSplitWarps], sl[kSplitWarps];
+  __shared__ float so[kSplitWarps][HD];
+  const int h = blockIdx.x, t = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const size_t base = ((size_t)t * Hq + h) * NS;
-  float M = -INFINITY;
-  for (int s = 0; s < NS; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  float L = 0.f, O = 0.f;
-  for (int s = 0; s < NS; ++s) {
+  float m = -INFINITY, l = 0.f, o[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) o[e] = 0.f;
+#pragma unroll 4
+  for (int s = warp; s < NS; s += kSplitWarps) {
     const float ms = part_ml[(base + s) * 2];
     if (ms == -INFINITY) continue;
-    const float f = expf(ms - M);
-    L += part_ml[(base + s) * 2 + 1] * f;
-    O += part_o[(base + s) * HD + c] * f;
+    const float ls = part_ml[(base + s) * 2 + 1];
+    const float* po = part_o + (base + s) * HD + lane * E;
+    const float mn = fmaxf(m, ms);
+    const float c1 = expf(m - mn), c2 = expf(ms - mn);  // first split: exp(-inf) = 0
+    l = l * c1 + ls * c2;
+#pragma unroll
+    for (int e = 0; e < E; ++e) o[e] = o[e] * c1 + po[e] * c2;
+    m = mn;
   }
-  const float o = rnd(O / L);
-  const float gate = tofloat(qg[(long)t * ldp + (size_t)h * 2 * HD + HD + c]);
-  out[(long)t * ldo + (size_t)h * HD + c] = tobf16(o * rnd(sigmoid_acc(gate)));
+  if (lane == 0) { sm[warp] = m; sl[warp] = l; }
+#pragma unroll
+  for (int e = 0; e < E; ++e) so[warp][lane * E + e] = o[e];
+  __syncthreads();
+  float M = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < kSplitWarps; ++w) M = fmaxf(M, sm[w]);
+  for (int c = threadIdx.x; c < HD; c += blockDim.x) {
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < kSplitWarps; ++w) {
+      if (sm[w] == -INFINITY) continue;
+      const float f = expf(sm[w] - M);
+      L += sl[w] * f;
+      O += so[w][c] * f;
+    }
+    const float ob = rnd(O / L);
+    const float gate = tofloat(qg[(long)t * ldp + (size_t)h * 2 * HD + HD + c]);
+    out[(long)t * ldo + (size_t)h * HD + c] = tobf16(ob * rnd(sigmoid_acc(gate)));
+  }
 }
 
 inline bool pdl_on() { return pdl_launch_enabled() && pdl_trigger_enabled(); }
@@ -420,7 +449,7 @@ extern "C" int qe_attn_decode(const void* q, const void* kc, const void* vc, con
                       (const bf16*)q, (const bf16*)kc, (const bf16*)vc, pos, part_o, part_ml,     \
                       Hq, Hkv, max_len, scale);                                                   \
     if (e) return e;                                                                              \
-    return (int)launch(attn_merge_kernel<HD>, dim3(Hq, n), dim3(HD), 0, s, pdl_on(),              \
+    return (int)launch(attn_merge_kernel<HD>, dim3(Hq, n), dim3(kSplitWarps * 32), 0, s, pdl_on(),              \
                        (const float*)part_o, (const float*)part_ml, (const bf16*)qg, ldp,         \
                        (bf16*)out, ldo, Hq, NS);                                                  \
   }

@@ -94,7 +94,7 @@ class Engine:
         tp: a qengine_b200.tp.TPGroup for tensor parallelism; then `cfg` is still the whole model's
         configuration and `weights` is this rank's shard (qengine_b200.tp.shard_model).
         attn_splits: flash-decoding splits per head (fixed so the graphs are static); default 16,
-        256 for caches longer than 8192 positions. draft_vocab: MTP drafts score only the first `draft_vocab` token ids
+        more for caches longer than 8192 positions. draft_vocab: MTP drafts score only the first `draft_vocab` token ids
         (pruned draft head through the argmax id map); verify keeps the full head."""
         self.tp, self.vocab_full, self.vocab_base = tp, cfg.vocab, 0
         if tp is not None:
@@ -111,7 +111,8 @@ class Engine:
         self.layers = [dict(L) for L in weights["layers"]]
         self.has_mtp = bool(mtp and weights.get("mtp"))
         self.mtp = dict(weights["mtp"]) if self.has_mtp else None
-        self.ATTN_SPLITS = attn_splits or (16 if max_len <= 8192 else 256)
+        # long caches: enough (KV head, split) CTAs to fill the GPU about five times over
+        self.ATTN_SPLITS = attn_splits or (16 if max_len <= 8192 else min(512, -(-740 // cfg.hkv)))
         self.draft_head = self.draft_ids = None
         if draft_vocab and self.has_mtp:
             self._build_draft_head(draft_vocab)
