@@ -332,6 +332,183 @@ attn_stream_kernel(const bf16* q, const bf16* kc, const bf16* vc, const int* pos
   }
 }
 
+// Tensor-core split for head dim 256 and long caches. The query heads of a KV group are the M rows
+// of mma.m16n8k16 (GQ <= 8 of 16 rows used): S = Q K^T and O += P V run on the tensor cores, which
+// removes the per-(position, head) widening, FMAs and butterfly reductions that make the CUDA-core
+// kernels issue-bound (72 warp-instructions per position and head there, about 2 here), so that the
+// layer becomes what it should be: a stream of the KV cache.
+//   CTA (KV head, 6 consecutive splits, row) = 6 warps, each a pipeline of its own on its own split
+//   (sub-slice of the row's causal prefix): it streams 16 positions per stage (K rows, V rows,
+//   512 B each, one bulk copy per row issued by lane = row, into a 528-byte pitch so that LDS.128 and ldmatrix are
+//   conflict-free) into a warp-private ring of 2 stages (33 KB per warp, 198 KB per SM in flight).
+//   Q K^T: the k index of the mma is permuted so that thread (g, t) feeds dims (4c + t) * 8 .. + 7
+//   of its position / head from ONE 16-byte load per two k-steps -- a dot product does not care
+//   about the order as long as A and B agree. P (bf16, as a flash-attention kernel keeps it) goes
+//   from the score accumulators straight into A fragments; V^T fragments come from
+//   ldmatrix.x4.trans. Online softmax state (m, l) is per head row; l is kept as per-thread partial
+//   sums and reduced once at the end.
+// The partial of a split is written like the other split kernels' (unnormalised O, m, l) and merged
+// by attn_merge_kernel. Split boundaries depend on the row's prefix length and NS only: row t of an
+// n-row call is bit-identical to a 1-row call. Waits are bounded (g_attn_error = 3).
+constexpr int kMmaWarps = 6, kMmaPos = 16, kMmaStages = 2, kRowPitch = 528;
+constexpr int kMmaStageBytes = 2 * kMmaPos * kRowPitch;  // K rows, then V rows
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int GQ>
+__global__ void __launch_bounds__(kMmaWarps * 32, 1)
+attn_mma_kernel(const bf16* q, const bf16* kc, const bf16* vc, const int* pos_ptr, float* part_o, float* part_ml,
+                int Hq, int max_len, float scale) {
+  constexpr int HD = 256;
+  dep_release();
+  extern __shared__ __align__(128) unsigned char ring[];
+  __shared__ uint64_t full[kMmaWarps][kMmaStages];
+  const int g = blockIdx.x, NS = gridDim.y * kMmaWarps, t = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int s = blockIdx.y * kMmaWarps + warp;
+  unsigned char* wring = ring + (size_t)warp * kMmaStages * kMmaStageBytes;
+  if (lane == 0) {
+    for (int i = 0; i < kMmaStages; ++i)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&full[warp][i])), "r"(1));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  dep_wait();
+  const int len = min(max(pos_ptr[0] + t + 1, 0), max_len);
+  const int chunk = (len + NS - 1) / NS;
+  const int start = s * chunk, end = min(len, start + chunk);
+  const int nstage = end > start ? (end - start + kMmaPos - 1) / kMmaPos : 0;
+  const bf16* kb = kc + (size_t)g * max_len * HD;
+  const bf16* vb = vc + (size_t)g * max_len * HD;
+
+  // whole warp: lane 0 arms the barrier, then lane r issues the two row copies of position r
+  // (32 copies issued by one lane would serialise into microseconds per stage)
+  auto refill = [&](int st) {
+    const int slot = st % kMmaStages;
+    const int p0 = start + st * kMmaPos, cnt = min(kMmaPos, end - p0);
+    unsigned char* dst = wring + (size_t)slot * kMmaStageBytes;
+    const uint32_t bar = smem_addr(&full[warp][slot]);
+    if (lane == 0)
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)cnt * 1024u) : "memory");
+    __syncwarp();
+    if (lane < cnt) {
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                       smem_addr(dst + lane * kRowPitch)), "l"(kb + (size_t)(p0 + lane) * HD), "r"(512u), "r"(bar) : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                       smem_addr(dst + (kMmaPos + lane) * kRowPitch)), "l"(vb + (size_t)(p0 + lane) * HD), "r"(512u),
+                   "r"(bar)
+                   : "memory");
+    }
+  };
+  for (int st = 0; st < min(kMmaStages, nstage); ++st) refill(st);
+
+  // A fragments of Q: row = head g * GQ + gi, thread column tq; chunk 4c + tq of the row (8 dims)
+  // serves k-steps 2c (words 0, 1) and 2c + 1 (words 2, 3). Rows >= GQ are zero.
+  const int gi = lane >> 2, tq = lane & 3;
+  uint32_t qa[8][4];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (gi < GQ) v = reinterpret_cast<const uint4*>(q + ((size_t)t * Hq + g * GQ + gi) * HD)[4 * c + tq];
+    qa[c][0] = v.x; qa[c][1] = v.y; qa[c][2] = v.z; qa[c][3] = v.w;
+  }
+  float oacc[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+  float m = -INFINITY, lsum = 0.f;
+  bool ok = true;
+
+  for (int st = 0; st < nstage && ok; ++st) {
+    const int slot = st % kMmaStages;
+    if (!bar_wait(&full[warp][slot], (st / kMmaStages) & 1)) {
+      atomicExch(&g_attn_error, 3);
+      ok = false;
+      break;
+    }
+    unsigned char* kst = wring + (size_t)slot * kMmaStageBytes;
+    unsigned char* vst = kst + kMmaPos * kRowPitch;
+    const int cnt = min(kMmaPos, end - start - st * kMmaPos);
+    if (cnt < kMmaPos) {  // stale rows behind a short last stage must not reach the P V product
+      for (int r = cnt; r < kMmaPos; ++r)
+        reinterpret_cast<uint4*>(vst + r * kRowPitch)[lane] = make_uint4(0u, 0u, 0u, 0u);
+      __syncwarp();
+    }
+    // S = Q K^T for the two 8-position blocks of the stage
+    float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        const uint4 kw = *reinterpret_cast<const uint4*>(kst + (nb * 8 + gi) * kRowPitch + (4 * c + tq) * 16);
+        mma_bf16(sacc[nb], qa[c][0], 0u, qa[c][1], 0u, kw.x, kw.y);
+        mma_bf16(sacc[nb], qa[c][2], 0u, qa[c][3], 0u, kw.z, kw.w);
+      }
+    }
+    // online softmax of head row gi over positions 8 nb + 2 tq + {0, 1}
+    float sc[2][2], bm = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        sc[nb][j] = (nb * 8 + 2 * tq + j < cnt) ? sacc[nb][j] * scale : -INFINITY;
+        bm = fmaxf(bm, sc[nb][j]);
+      }
+    }
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+    const float mn = fmaxf(m, bm);
+    const float corr = expf(m - mn);  // first stage: exp(-inf) = 0
+    float pr[2][2];
+    lsum *= corr;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        pr[nb][j] = expf(sc[nb][j] - mn);
+        lsum += pr[nb][j];
+      }
+    }
+    m = mn;
+    const uint32_t pa0 = pack2(pr[0][0], pr[0][1]), pa2 = pack2(pr[1][0], pr[1][1]);
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { oacc[i][0] *= corr; oacc[i][1] *= corr; }
+    // O += P V: V^T fragments for two 8-dim blocks per ldmatrix.x4.trans
+    const uint32_t vaddr = smem_addr(vst + (((lane >> 3) & 1) * 8 + (lane & 7)) * kRowPitch + (lane >> 4) * 16);
+#pragma unroll
+    for (int i = 0; i < HD / 8; i += 2) {
+      uint32_t b0, b1, b2, b3;
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(vaddr + i * 16));
+      mma_bf16(oacc[i], pa0, 0u, pa2, 0u, b0, b1);
+      mma_bf16(oacc[i + 1], pa0, 0u, pa2, 0u, b2, b3);
+    }
+    __syncwarp();
+    if (st + kMmaStages < nstage) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      refill(st + kMmaStages);
+    }
+  }
+  lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+  lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+  if (gi < GQ) {
+    const bool none = m == -INFINITY;
+    const size_t slot_o = ((size_t)t * Hq + g * GQ + gi) * NS + s;
+    float2* po = reinterpret_cast<float2*>(part_o + slot_o * HD) + tq;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) po[i * 4] = none ? make_float2(0.f, 0.f) : make_float2(oacc[i][0], oacc[i][1]);
+    if (tq == 0) {
+      part_ml[slot_o * 2] = m;
+      part_ml[slot_o * 2 + 1] = none ? 0.f : lsum;
+    }
+  }
+}
+
 // Merge of the NS split partials of one (head, row): warp w folds splits w, w + 8, ... into a
 // running (M, L, O) in ascending order (lane = HD / 32 consecutive dims), the 8 warps are combined
 // in warp order, then o = bf16(O / L) * bf16(sigmoid(gate)). The order depends on NS only.
@@ -452,6 +629,35 @@ extern "C" int qe_attn_decode(const void* q, const void* kc, const void* vc, con
     return (int)launch(attn_merge_kernel<HD>, dim3(Hq, n), dim3(kSplitWarps * 32), 0, s, pdl_on(),              \
                        (const float*)part_o, (const float*)part_ml, (const bf16*)qg, ldp,         \
                        (bf16*)out, ldo, Hq, NS);                                                  \
+  }
+  if (hd == 256 && NS % kMmaWarps == 0 && gq >= 1 && gq <= 8) {
+    const dim3 mgrid(Hkv, NS / kMmaWarps, n);
+    constexpr size_t msmem = (size_t)kMmaWarps * kMmaStages * kMmaStageBytes;
+    int e = QE_ERR_ARG;
+#define QB_MMA(GQ)                                                                                \
+  {                                                                                               \
+    static bool attr = false;                                                                     \
+    if (!attr) {                                                                                  \
+      cudaFuncSetAttribute(attn_mma_kernel<GQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem); \
+      attr = true;                                                                                \
+    }                                                                                             \
+    e = (int)launch(attn_mma_kernel<GQ>, mgrid, dim3(kMmaWarps * 32), msmem, s, pdl_on(), (const bf16*)q, \
+                    (const bf16*)kc, (const bf16*)vc, pos, part_o, part_ml, Hq, max_len, scale);   \
+  }
+    switch (gq) {
+      case 1: QB_MMA(1) break;
+      case 2: QB_MMA(2) break;
+      case 3: QB_MMA(3) break;
+      case 4: QB_MMA(4) break;
+      case 6: QB_MMA(6) break;
+      case 8: QB_MMA(8) break;
+      default: e = -1; break;
+    }
+#undef QB_MMA
+    if (e == 0)
+      return (int)launch(attn_merge_kernel<256>, dim3(Hq, n), dim3(kSplitWarps * 32), 0, s, pdl_on(),
+                         (const float*)part_o, (const float*)part_ml, (const bf16*)qg, ldp, (bf16*)out, ldo, Hq, NS);
+    if (e > 0) return e;
   }
   if (hd == 256) QB_DEC(256)
   if (hd == 128) QB_DEC(128)

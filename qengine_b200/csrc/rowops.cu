@@ -48,9 +48,16 @@ rmsnorm1p_vec_kernel(bf16* x, const bf16* delta,
                      const bf16* w, bf16* out, int H, long ldx, long ldd,
                      long ldo, float eps) {
   dep_release();
-  dep_wait();
   __shared__ float scratch[32];
   const int row = blockIdx.x, npk = H >> 3;
+  // the weight is a constant: fetch it while the producer of x is still running
+  uint4 wq[PKT];
+#pragma unroll
+  for (int p = 0; p < PKT; ++p) {
+    const int i = threadIdx.x + p * blockDim.x;
+    if (i < npk) wq[p] = __ldg(reinterpret_cast<const uint4*>(w) + i);
+  }
+  dep_wait();
   uint4* xr = reinterpret_cast<uint4*>(x + (long)row * ldx);
   const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + (long)row * ldd) : nullptr;
   float v[PKT][8];
@@ -78,7 +85,7 @@ rmsnorm1p_vec_kernel(bf16* x, const bf16* delta,
     const int i = threadIdx.x + p * blockDim.x;
     if (i < npk) {
       float g[8], y[8];
-      widen8(__ldg(reinterpret_cast<const uint4*>(w) + i), g);
+      widen8(wq[p], g);
 #pragma unroll
       for (int e = 0; e < 8; ++e) y[e] = v[p][e] * inv * (1.0f + g[e]);
       orow[i] = narrow8(y);

@@ -30,6 +30,11 @@ from .quant import W4Packed
 from .synth import Config
 
 BF16, I32, F32 = torch.bfloat16, torch.int32, torch.float32
+
+
+def _lib_sm_count() -> int:
+    from ._lib import lib
+    return max(1, int(lib.qe_sm_count()))
 NMAX = 8  # rows per pass
 
 
@@ -111,8 +116,9 @@ class Engine:
         self.layers = [dict(L) for L in weights["layers"]]
         self.has_mtp = bool(mtp and weights.get("mtp"))
         self.mtp = dict(weights["mtp"]) if self.has_mtp else None
-        # long caches: enough (KV head, split) CTAs to fill the GPU about five times over
-        self.ATTN_SPLITS = attn_splits or (16 if max_len <= 8192 else min(512, -(-740 // cfg.hkv)))
+        # long caches: a multiple of 6 selects the tensor-core split kernel (6 splits per CTA);
+        # one CTA per SM and row, i.e. 6 * ceil(SMs / KV heads) splits
+        self.ATTN_SPLITS = attn_splits or (16 if max_len <= 8192 else 6 * -(-_lib_sm_count() // cfg.hkv))
         self.draft_head = self.draft_ids = None
         if draft_vocab and self.has_mtp:
             self._build_draft_head(draft_vocab)

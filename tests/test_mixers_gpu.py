@@ -145,12 +145,16 @@ def attn_cfg(hq, hkv, hd, rd):
                      hkv=hkv, head_dim=hd, rope_theta=1e7, rotary_dim=rd, hk=1, hv=1, dk=128, dv=128)
 
 
-@pytest.mark.parametrize("hq,hkv,hd,rd,steps,start,n", [
-    (8, 2, 256, 64, 20, 0, 1), (24, 4, 256, 64, 6, 0, 1), (8, 2, 256, 64, 3, 4094, 1), (1, 1, 256, 64, 5, 125, 1),
-    (8, 2, 256, 64, 24, 0, 8), (24, 4, 256, 64, 12, 100, 3), (8, 2, 64, 16, 20, 0, 5), (4, 2, 128, 32, 9, 33, 3),
+@pytest.mark.parametrize("hq,hkv,hd,rd,steps,start,n,NS", [
+    (8, 2, 256, 64, 20, 0, 1, 16), (24, 4, 256, 64, 6, 0, 1, 16), (8, 2, 256, 64, 3, 4094, 1, 16),
+    (1, 1, 256, 64, 5, 125, 1, 16), (8, 2, 256, 64, 24, 0, 8, 16), (24, 4, 256, 64, 12, 100, 3, 16),
+    (8, 2, 64, 16, 20, 0, 5, 16), (4, 2, 128, 32, 9, 33, 3, 16),
     # long slices: the shared-memory ring of the grouped-query kernel wraps many times (groups of 6, 3)
-    (12, 2, 256, 64, 4, 5000, 2), (3, 1, 256, 64, 3, 2100, 3), (16, 2, 128, 32, 2, 700, 1)])
-def test_attention_vs_oracle_and_row_independence(C, hq, hkv, hd, rd, steps, start, n):
+    (12, 2, 256, 64, 4, 5000, 2, 16), (3, 1, 256, 64, 3, 2100, 3, 16), (16, 2, 128, 32, 2, 700, 1, 16),
+    # a number of splits that is a multiple of 6 selects the tensor-core kernel (head dim 256)
+    (24, 4, 256, 64, 6, 0, 1, 12), (8, 2, 256, 64, 24, 0, 8, 6), (12, 2, 256, 64, 4, 5000, 2, 12),
+    (3, 1, 256, 64, 3, 2100, 3, 24), (1, 1, 256, 64, 5, 125, 1, 6), (16, 2, 256, 64, 3, 1000, 3, 18)])
+def test_attention_vs_oracle_and_row_independence(C, hq, hkv, hd, rd, steps, start, n, NS):
     g = torch.Generator().manual_seed(1)
     cfg = attn_cfg(hq, hkv, hd, rd)
     max_len = start + steps
@@ -162,7 +166,6 @@ def test_attention_vs_oracle_and_row_independence(C, hq, hkv, hd, rd, steps, sta
     kc, vc = kc_ref.to(dev), vc_ref.to(dev)
     inv = OM.inv_freq(cfg).to(dev)
     qn, kn = L["q_norm"].to(dev), L["k_norm"].to(dev)
-    NS = 16
     pos_t = torch.zeros(1, dtype=torch.int32, device=dev)
     po = torch.empty(8, hq, NS, hd, device=dev)
     pml = torch.empty(8, hq, NS, 2, device=dev)
