@@ -509,9 +509,14 @@ attn_mma_kernel(const bf16* q, const bf16* kc, const bf16* vc, const int* pos_pt
   }
 }
 
-// Merge of the NS split partials of one (head, row): warp w folds splits w, w + 8, ... into a
-// running (M, L, O) in ascending order (lane = HD / 32 consecutive dims), the 8 warps are combined
-// in warp order, then o = bf16(O / L) * bf16(sigmoid(gate)). The order depends on NS only.
+// Merge of the NS split partials of one (head, row). Phase 1: the (m, l) pairs of all splits go to
+// shared memory in one coalesced sweep, M = max m, weight f_s = exp(m_s - M), L = sum l_s f_s
+// (block reduction in a fixed order). Phase 2: warp w adds O_s f_s over splits w, w + 8, ... in
+// ascending order with independent 16-byte loads in flight (lane = HD / 32 consecutive dims), the 8
+// warps are combined in warp order, then o = bf16(O / L) * bf16(sigmoid(gate)). With hundreds of
+// splits (long caches) a loop whose loads wait for each other would cost as much as the split
+// kernel itself. The order depends on NS only.
+constexpr int kMergeMaxSplits = 1024;
 template <int HD>
 __global__ void __launch_bounds__(kSplitWarps * 32)
 attn_merge_kernel(const float* part_o, const float* part_ml, const bf16* qg, long ldp, bf16* out, long ldo,
@@ -519,43 +524,57 @@ attn_merge_kernel(const float* part_o, const float* part_ml, const bf16* qg, lon
   constexpr int E = HD / 32;
   dep_release();
   dep_wait();
-  __shared__ float sm[kSplitWarps], sl[kSplitWarps];
+  __shared__ float fs[kMergeMaxSplits];
+  __shared__ float red[32];
   __shared__ float so[kSplitWarps][HD];
   const int h = blockIdx.x, t = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const size_t base = ((size_t)t * Hq + h) * NS;
-  float m = -INFINITY, l = 0.f, o[E];
+  const float2* ml = reinterpret_cast<const float2*>(part_ml) + base;
+  // phase 1
+  float mymax = -INFINITY;
+  for (int s = threadIdx.x; s < NS; s += blockDim.x) mymax = fmaxf(mymax, ml[s].x);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mymax = fmaxf(mymax, __shfl_xor_sync(0xffffffffu, mymax, o));
+  if (lane == 0) red[warp] = mymax;
+  __syncthreads();
+  float M = red[0];
+#pragma unroll
+  for (int w = 1; w < kSplitWarps; ++w) M = fmaxf(M, red[w]);
+  float lpart = 0.f;
+  for (int s = threadIdx.x; s < NS; s += blockDim.x) {
+    const float2 v = ml[s];
+    const float f = v.x == -INFINITY ? 0.f : expf(v.x - M);
+    fs[s] = f;
+    lpart += v.y * f;
+  }
+  const float L = block_allsum(lpart, red);  // barriers inside also publish fs
+  // phase 2
+  float o[E];
 #pragma unroll
   for (int e = 0; e < E; ++e) o[e] = 0.f;
 #pragma unroll 4
   for (int s = warp; s < NS; s += kSplitWarps) {
-    const float ms = part_ml[(base + s) * 2];
-    if (ms == -INFINITY) continue;
-    const float ls = part_ml[(base + s) * 2 + 1];
+    const float f = fs[s];
     const float* po = part_o + (base + s) * HD + lane * E;
-    const float mn = fmaxf(m, ms);
-    const float c1 = expf(m - mn), c2 = expf(ms - mn);  // first split: exp(-inf) = 0
-    l = l * c1 + ls * c2;
+    float v[E];
+    if constexpr (E == 8) {
+      const float4 a = reinterpret_cast<const float4*>(po)[0], b = reinterpret_cast<const float4*>(po)[1];
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
 #pragma unroll
-    for (int e = 0; e < E; ++e) o[e] = o[e] * c1 + po[e] * c2;
-    m = mn;
+      for (int e = 0; e < E; ++e) v[e] = po[e];
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) o[e] = fmaf(v[e], f, o[e]);
   }
-  if (lane == 0) { sm[warp] = m; sl[warp] = l; }
 #pragma unroll
   for (int e = 0; e < E; ++e) so[warp][lane * E + e] = o[e];
   __syncthreads();
-  float M = -INFINITY;
-#pragma unroll
-  for (int w = 0; w < kSplitWarps; ++w) M = fmaxf(M, sm[w]);
   for (int c = threadIdx.x; c < HD; c += blockDim.x) {
-    float L = 0.f, O = 0.f;
+    float O = 0.f;
 #pragma unroll
-    for (int w = 0; w < kSplitWarps; ++w) {
-      if (sm[w] == -INFINITY) continue;
-      const float f = expf(sm[w] - M);
-      L += sl[w] * f;
-      O += so[w][c] * f;
-    }
+    for (int w = 0; w < kSplitWarps; ++w) O += so[w][c];
     const float ob = rnd(O / L);
     const float gate = tofloat(qg[(long)t * ldp + (size_t)h * 2 * HD + HD + c]);
     out[(long)t * ldo + (size_t)h * HD + c] = tobf16(ob * rnd(sigmoid_acc(gate)));
@@ -606,7 +625,7 @@ extern "C" int qe_attn_decode(const void* q, const void* kc, const void* vc, con
                               const void* qg, long ldp, float* part_o, float* part_ml, void* out,
                               long ldo, int n, int Hq, int Hkv, int hd, int max_len, int NS,
                               float scale, void* stream) {
-  if (n < 1 || n > QE_MAX_ROWS || Hq < 1 || Hkv < 1 || Hq % Hkv || NS < 1) return QE_ERR_ARG;
+  if (n < 1 || n > QE_MAX_ROWS || Hq < 1 || Hkv < 1 || Hq % Hkv || NS < 1 || NS > kMergeMaxSplits) return QE_ERR_ARG;
   cudaStream_t s = (cudaStream_t)stream;
   const dim3 grid(Hq, NS, n);
   const int gq = Hq / Hkv;
