@@ -185,14 +185,43 @@ tp_xnorm_kernel(TpView tv, bf16* x, const float* part, const bf16* w, bf16* out,
 #pragma unroll
     for (int k = 0; k < 8; ++k) d[k] = 0.f;
     for (int b0 = 0; b0 < tv.world; b0 += 4) {
+      // up to four peers at a time: all 16 loads of the batch are issued together and the whole
+      // batch is re-read until every flag matches (one L2 round trip per try, never one per word)
       uint4 rv[4][4];
+      const unsigned long long t0 = now_ns();
+      for (unsigned tries = 1;; ++tries) {
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int src = b0 + u;
-        if (src < tv.world && src != tv.rank) {
-          const char* sp = norm_slot(tv.base[tv.rank], tv, e, src, row) + (long)i * 64;
+        for (int u = 0; u < 4; ++u) {
+          const int src = b0 + u;
+          if (src < tv.world && src != tv.rank) {
+            const char* sp = norm_slot(tv.base[tv.rank], tv, e, src, row) + (long)i * 64;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) rv[u][q] = ld_v4(sp + 16 * q);
+            for (int q = 0; q < 4; ++q) rv[u][q] = ld_v4(sp + 16 * q);
+          }
+        }
+        bool all = true;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int src = b0 + u;
+          if (src < tv.world && src != tv.rank) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) all = all && rv[u][q].y == e && rv[u][q].w == e;
+          }
+        }
+        if (all || dead) break;
+        if ((tries & 63u) == 0) {
+          volatile int* err = hdr + kErrWord;
+          if (err[0] != 0 || now_ns() - t0 > tv.timeout_ns) {
+            if (atomicCAS(hdr + kErrWord, 0, 1) == 0) {
+              int late = b0;  // first source of the batch whose data has not landed
+#pragma unroll
+              for (int u = 3; u >= 0; --u)
+                if (b0 + u < tv.world && b0 + u != tv.rank && (rv[u][0].y != e || rv[u][3].w != e)) late = b0 + u;
+              err[1] = late; err[2] = row; err[3] = 0;
+            }
+            dead = true;
+            break;
+          }
         }
       }
 #pragma unroll
@@ -204,10 +233,8 @@ tp_xnorm_kernel(TpView tv, bf16* x, const float* part, const bf16* w, bf16* out,
           for (int k = 0; k < 8; ++k) d[k] += mine[k];
           continue;
         }
-        const char* sp = norm_slot(tv.base[tv.rank], tv, e, src, row) + (long)i * 64;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          if (rv[u][q].y != e || rv[u][q].w != e) rv[u][q] = ll_wait(sp + 16 * q, e, hdr, tv, src, row, 0, dead);
           d[2 * q] += __uint_as_float(rv[u][q].x);
           d[2 * q + 1] += __uint_as_float(rv[u][q].z);
         }
