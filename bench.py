@@ -34,10 +34,10 @@ sys.path.insert(0, str(ROOT))
 PROMPT_LEN, N_NEW = 128, 1024
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of w4_warp_ring_kernel, from the
-# ncu capture summarised in profiles/w4_warp_ring_kernel_27b_shapes.md: 16.28 / 16.22, 95.87 / 91.95
-# and 46.07 / 45.99 MB on out_proj, gate_up and down (the excess on gate_up is partial-tile scratch
+# ncu capture summarised in profiles/w4_warp_ring_kernel_27b_shapes.md: 16.28 / 16.22, 97.28 / 91.91
+# and 46.06 / 45.96 MB on out_proj, gate_up and down (the excess on gate_up is partial-tile scratch
 # written back from L2). Scaled to an average launch of the 257-launch sequence below.
-NCU_TRAFFIC_RATIO = (16.28 + 95.87 + 46.07) / (16.22 + 91.95 + 45.99)
+NCU_TRAFFIC_RATIO = (16.28 + 97.28 + 46.06) / (16.22 + 91.91 + 45.96)
 
 
 def measured_peak():

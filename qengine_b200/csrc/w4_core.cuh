@@ -39,12 +39,6 @@ __device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
   asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
-template <int S>
-__device__ __forceinline__ uint32_t shr_fma(uint32_t w) {
-  uint32_t r;
-  asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(w), "r"(1u << (32 - S)));
-  return r;
-}
 // One k-step of 16: four A registers from one packed word, times two x pairs.
 __device__ __forceinline__ void kstep(float (&c)[4], uint32_t w, uint32_t b0, uint32_t b1) {
   constexpr uint32_t kNib = 0x000F000Fu, k128 = 0x43004300u, k136 = 0x43084308u;

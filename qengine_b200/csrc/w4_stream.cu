@@ -37,7 +37,6 @@
 // (per 8 weights: 3 shifts, 4 lop3, 4 sub.bf16x2, 1 mma). It also makes the one-row and k+1-row
 // sums the same instruction sequence, hence the same bits.
 #include <algorithm>
-#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -555,8 +554,7 @@ Resolved resolve(const qe_w4_params& p, const qe_w4_cfg& in) {
     const long want = (units + std::max(1, c.min_units) - 1) / std::max(1, c.min_units);
     const long workers = std::max<long>(1, std::min<long>((long)sms * bps * 8, want));
     // tiles cut across warps are finished through shared memory when every CTA span is short enough
-    static const bool one_level = getenv("QE_W4_ONE_LEVEL") != nullptr;  // A/B measurement knob
-    const bool two = !one_level && cta_fix_ok((int)units, (int)G, (int)workers, 8);
+    const bool two = cta_fix_ok((int)units, (int)G, (int)workers, 8);
     r.wfn = wg.fn[(p.epilogue == QE_EPI_SWIGLU ? 1 : 0) + (p.x_f16 ? 2 : 0) + (two ? 4 : 0)];
     r.nworkers = (int)workers;
     r.plan.grid_x = (int)((workers + 7) / 8);
