@@ -165,7 +165,9 @@ int qe_attn_prep(const void* qg, const void* k, const void* v, long ldp, const v
                  void* stream);
 
 /* Split-KV flash decoding + combine + sigmoid gate. part_o fp32 [>=n, Hq, NS, hd], part_ml fp32
- * [>=n, Hq, NS, 2]. Replaces launch_attn_decode (csrc/ops.h:28-30). */
+ * [>=n, Hq, NS, 2], 1 <= NS <= 1024. hd == 256 with NS a multiple of 6 runs the tensor-core split
+ * kernel (long caches), otherwise the shared-memory-ring kernel. Rows are independent: row t of an
+ * n-row call equals the 1-row call at pos + t. Replaces launch_attn_decode (csrc/ops.h:28-30). */
 int qe_attn_decode(const void* q, const void* kc, const void* vc, const int* pos, const void* qg,
                    long ldp, float* part_o, float* part_ml, void* out, long ldo, int n, int Hq,
                    int Hkv, int hd, int max_len, int NS, float scale, void* stream);
