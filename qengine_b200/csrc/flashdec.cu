@@ -337,7 +337,7 @@ attn_stream_kernel(const bf16* q, const bf16* kc, const bf16* vc, const int* pos
 // removes the per-(position, head) widening, FMAs and butterfly reductions that make the CUDA-core
 // kernels issue-bound (72 warp-instructions per position and head there, about 2 here), so that the
 // layer becomes what it should be: a stream of the KV cache.
-//   CTA (KV head, 6 consecutive splits, row) = 6 warps, each a pipeline of its own on its own split
+//   CTA (row, KV head, 6 consecutive splits) = 6 warps, each a pipeline of its own on its own split
 //   (sub-slice of the row's causal prefix): it streams 16 positions per stage (K rows, V rows,
 //   512 B each, one bulk copy per row issued by lane = row, into a 528-byte pitch so that LDS.128 and ldmatrix are
 //   conflict-free) into a warp-private ring of 2 stages (33 KB per warp, 198 KB per SM in flight).
@@ -369,9 +369,11 @@ attn_mma_kernel(const bf16* q, const bf16* kc, const bf16* vc, const int* pos_pt
   dep_release();
   extern __shared__ __align__(128) unsigned char ring[];
   __shared__ uint64_t full[kMmaWarps][kMmaStages];
-  const int g = blockIdx.x, NS = gridDim.y * kMmaWarps, t = blockIdx.z;
+  // the row is the fastest grid index: the CTAs of the rows of a verify pass that read the same
+  // slice of the cache run at the same time, so the slice comes from HBM once and from L2 after
+  const int t = blockIdx.x, g = blockIdx.y, NS = gridDim.z * kMmaWarps;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int s = blockIdx.y * kMmaWarps + warp;
+  const int s = blockIdx.z * kMmaWarps + warp;
   unsigned char* wring = ring + (size_t)warp * kMmaStages * kMmaStageBytes;
   if (lane == 0) {
     for (int i = 0; i < kMmaStages; ++i)
@@ -650,7 +652,7 @@ extern "C" int qe_attn_decode(const void* q, const void* kc, const void* vc, con
                        (bf16*)out, ldo, Hq, NS);                                                  \
   }
   if (hd == 256 && NS % kMmaWarps == 0 && gq >= 1 && gq <= 8) {
-    const dim3 mgrid(Hkv, NS / kMmaWarps, n);
+    const dim3 mgrid(n, Hkv, NS / kMmaWarps);
     constexpr size_t msmem = (size_t)kMmaWarps * kMmaStages * kMmaStageBytes;
     int e = QE_ERR_ARG;
 #define QB_MMA(GQ)                                                                                \
