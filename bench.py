@@ -156,7 +156,8 @@ def run_reference_arm(a):
     line = {
         "impl": "reference", "metric": "batch-1 decode tok/s (plain)", "value": tok_s, "unit": "tok/s",
         "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": per_tok * 1e3,
-        "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "higher_is_better": True, "scaling": "weak" if a.gpus == 1 else "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "27B-shape W4A16 plain greedy decode, 128-token prompt, 1,024 tokens",
                    "timing": "host wall clock, CPU only"},
         "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": desc},
