@@ -56,6 +56,9 @@ class W4Linear:
 
     def __init__(self, ksplit_max=64, **kw):
         self.ksplit_max, self.kw = ksplit_max, dict(kw)
+        # at least 6 units per warp: the 5120 x 6144 out_proj (15,360 units) then runs on 2,560 warps
+        # instead of all 3,552, which is 3 % of the whole W4 time of a token (measured)
+        self.kw.setdefault("min_units", 6)
 
     def prepare(self, w):
         from .quant import quantize_w4
