@@ -112,7 +112,9 @@ class Engine:
             self.vocab_base = tp.rank * cfg.vocab
         self.cfg, self.max_len = cfg, max_len
         self.dev = torch.device(device)
-        self.linear = linear or W4Linear()
+        # the shards of a tensor-parallel rank are small enough that every warp should get work:
+        # 4 units per warp there (measured: 2.17 vs 2.45 ms per token at 4 ranks), 6 on one GPU
+        self.linear = linear or (W4Linear() if tp is None else W4Linear(min_units=4))
         self.lm_lin = self.linear
         self.embed, self.final_norm = weights["embed"], weights["final_norm"]
         self.lm_head = weights["lm_head"]
