@@ -56,8 +56,11 @@ class W4Linear:
 
     def __init__(self, ksplit_max=64, **kw):
         self.ksplit_max, self.kw = ksplit_max, dict(kw)
-        # at least 6 units per warp: the 5120 x 6144 out_proj (15,360 units) then runs on 2,560 warps
-        # instead of all 3,552, which is 3 % of the whole W4 time of a token (measured)
+        # at least 6 units per warp: the 5120 x 6144 out_proj (320 tiles of 48 units) then runs on
+        # 2,560 warps = 320 CTAs of exactly one tile each, so no tile crosses a CTA boundary and all
+        # of them finish through shared memory: 3 % of the whole W4 time of a token (measured; 5 and
+        # 7 are both slower, and forcing the same alignment on `down` or the lm_head costs more in
+        # idle warp slots than it saves)
         self.kw.setdefault("min_units", 6)
 
     def prepare(self, w):
