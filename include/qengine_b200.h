@@ -128,6 +128,17 @@ int qe_accept(const int* in_tok, const int* am, int n, int* ctl, int* next_tok, 
  * Replaces launch_commit (csrc/ops.h:17). */
 int qe_commit(int* ctl, int* in_tok, const int* am, const int* drafts, int k, void* stream);
 
+/* qe_accept followed by qe_commit in one launch, for passes that run nothing in between (plain
+ * decode, prefill). No counterpart in the reference, which always launches the two kernels. */
+int qe_accept_commit(int* in_tok, const int* am, int n, int* ctl, int* next_tok, int* log,
+                     int max_len, const int* drafts, int k, void* stream);
+
+/* End of a chained single-row draft pass: draft_out[0] = mtp_am[0] and dst[0..H) = src[0..H).
+ * Replaces the two device-to-device copies the reference issues there
+ * (python/qengine/engine.py:516-517). */
+int qe_chain_draft(const int* mtp_am, int* draft_out, const void* src, void* dst, int H,
+                   void* stream);
+
 /* mpos[0] = off < 0 ? pos : pos + m + 1 + off; optional dst[:] = src[m, :]; optional
  * draft0[0] = mtp_am[m]. Replaces launch_mtp_select (csrc/ops.h:18-19). */
 int qe_mtp_select(const int* ctl, int* mpos, int off, const void* src, long lds, void* dst, int H,
@@ -195,39 +206,37 @@ int qe_stream_access_window(uintptr_t base, size_t bytes, float hit_ratio, void*
 enum { QE_EPI_NONE = 0, QE_EPI_SWIGLU = 1 };
 
 typedef struct qe_w4_params {
-  const void* qw;      /* packed int4 weights */
-  const void* scales;  /* fp16 group scales */
-  const void* x;       /* bf16 activations, N rows, stride ldx */
+  const void* qw;      /* packed int4 weights (16-byte aligned) */
+  const void* scales;  /* fp16 group scales (16-byte aligned) */
+  const void* x;       /* bf16 activations, N rows, stride ldx; any alignment (16-byte aligned rows
+                          with ldx % 8 == 0 take the vector path). Ignored by qe_w4_gemv_ex when a
+                          prologue is given. */
   void* out;           /* bf16 output, N rows, stride ldo */
   float* ws;           /* fp32 partial-sum slots, qe_w4_plan::ws_floats entries, any contents */
   int* counters;       /* int32 arrival counters, qe_w4_plan::counters entries, zero between calls */
   int M;               /* logical output rows (QE_EPI_SWIGLU: intermediate size I) */
-  int K;               /* logical reduction length */
+  int K;               /* logical reduction length, Kp - 128 < K <= Kp */
   int Mp, Kp;          /* padded sizes (multiples of 16 / 128) */
   int N;               /* activation rows, 1..8 */
   long ldx, ldo;
   int epilogue;        /* QE_EPI_* */
-  int x_f16;           /* 0: x is bf16 (the reference's contract). 1: x is fp16 -- same row layout;
-                          needs K == Kp, 16-byte aligned x and ldx % 8 == 0. No counterpart in the
-                          reference; used by the decode engine, whose GEMV inputs are bf16-rounded
-                          values that convert to fp16 exactly. */
   int out_f32;         /* 0: out is bf16 (the reference's contract). 1 (plain epilogue only): out is
                           fp32, ldo in floats, sums stored unrounded -- the partial sums of a matrix
                           split along K over tensor-parallel ranks. No counterpart in the reference. */
 } qe_w4_params;
 
 /* Launch options with the reference's names (csrc/gemv_w4.h:27-39). 0 / -1 mean "auto by shape".
- * Every accepted combination is deterministic and independent of N. */
+ * One kernel family serves every shape, so most of them only steer its geometry; every accepted
+ * combination is deterministic and independent of N. */
 typedef struct qe_w4_cfg {
-  int warps;         /* warps per block: 0 (auto), 4, 8, 16 */
-  int unroll;        /* weight groups (1 KB each) in flight per warp: 0 (auto), 1, 2, 4 */
-  int ksplit;        /* mode 0: blocks along K; 0 = auto */
+  int warps;         /* warps per block: 0 (auto) / 16 -> 16, 4 / 8 -> 8 */
+  int unroll;        /* weight units (1 KB) per ring stage: 0 / 4 -> 2 stages of 4, 1 / 2 -> 3 stages of 2 */
+  int ksplit;        /* > 0: at least this many warps share a 16-row tile; 0 = by min_units */
   int pdl;           /* launch with programmatic stream serialization */
-  int variant;       /* load flavour, 0..3 (see w4_stream.cu) */
-  int mode;          /* -1 auto, 0 = (tile, ksplit) grid, 2 = persistent unit stream,
-                        3 = unit stream through a shared-memory ring fed by bulk copies */
-  int blocks_per_sm; /* mode 2: 0 = auto */
-  int min_units;     /* mode 2: minimum 1-KB units per warp */
+  int variant;       /* 1: 24 warps per block; other values: as `warps` says */
+  int mode;          /* accepted for compatibility (-1, 0, 2, 3, 4); the plan always reports 4 */
+  int blocks_per_sm; /* accepted for compatibility; the kernel runs one block per SM */
+  int min_units;     /* minimum 1-KB units per warp (fewer warps for small matrices) */
 } qe_w4_cfg;
 
 typedef struct qe_w4_plan {
@@ -237,6 +246,34 @@ typedef struct qe_w4_plan {
   long counters;  /* required size of qe_w4_params::counters */
 } qe_w4_plan;
 
+/* Optional work fused into the GEMV launch; no counterpart in the reference, whose engine runs
+ * launch_rmsnorm1p (csrc/ops.h:8-9) and launch_embed (csrc/ops.h:6-7) as kernels of their own in
+ * front of launch_gemv_w4 (python/qengine/engine.py:434-466).
+ *   Prologue (h_in != NULL): the GEMV input is x = RMSNorm1p(h_in + delta) * (1 + norm_w), with
+ *   the arithmetic of qe_rmsnorm1p (bf16 residual sum, fp32 statistics, one rounding), computed
+ *   by every block into shared memory. h_out (optional) receives bf16(h_in + delta), xn_out
+ *   (optional) receives x; both are written by one block. h_out must not alias h_in. With tok !=
+ *   NULL, h_in is an embedding table [vocab, K] and row r is table[tok[r]] (zeros when out of
+ *   range). Needs K == Kp, 16-byte aligned rows, row strides that are multiples of 8, and
+ *   N * (2 K + 16) bytes of shared memory beside the weight rings (QE_ERR_ARG otherwise: run
+ *   qe_rmsnorm1p and qe_w4_gemv instead).
+ *   Prefetch (prefetch_bytes > 0): every block asks L2 for its slice of [prefetch,
+ *   prefetch + prefetch_bytes) before it waits for its input -- the weights of a later GEMV, so
+ *   that HBM keeps working while short dependent kernels run. A hint; no effect on results. */
+typedef struct qe_w4_norm {
+  const void* h_in;    /* bf16 [N, K] rows (stride ldh), or the embedding table when tok != NULL */
+  const int* tok;      /* optional token ids [N] */
+  int vocab;           /* rows of the table (tok != NULL) */
+  const void* delta;   /* optional bf16 [N, K] residual update, stride ldd */
+  const void* norm_w;  /* bf16 [K] */
+  void* h_out;         /* optional bf16 [N, K], stride ldho */
+  void* xn_out;        /* optional bf16 [N, K], stride ldxo */
+  long ldh, ldd, ldho, ldxo;
+  float eps;
+  const void* prefetch;
+  size_t prefetch_bytes;
+} qe_w4_norm;
+
 /* Default-initialise a cfg (all auto, pdl on, min_units 4). */
 void qe_w4_cfg_default(qe_w4_cfg* cfg);
 /* Resolve the launch for a shape; never depends on N. Replaces plan_gemv_w4 (gemv_w4.h:50). */
@@ -245,6 +282,8 @@ int qe_w4_plan_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, qe_w4_plan* pla
 int qe_w4_auto_ksplit(int Mp, int Kp, int N, int warps);
 /* Replaces launch_gemv_w4 (gemv_w4.h:56). */
 int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
+/* qe_w4_gemv with the fused prologue / prefetch hint described at qe_w4_norm (nrm may be NULL). */
+int qe_w4_gemv_ex(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg, void* stream);
 /* Has no counterpart in the reference. The same GEMV as qe_w4_gemv for callers that cannot
  * allocate device memory (a plugin inside another runtime's callback, code running between the
  * capture and the replay of a graph, an embedder that may not call its allocator): p->ws and
@@ -259,10 +298,11 @@ int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
 #define QE_ERR_SCRATCH (-28)
 int qe_w4_gemv_static(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
 
-/* Mode 3 (shared-memory ring fed by bulk copies) bounds every barrier wait; this returns the
- * sticky error word those waits set on expiry (0 = none). Synchronises with the device. No
- * counterpart in the reference. */
+/* The weight rings are fed by bulk copies whose completion waits are bounded; this returns the
+ * sticky error word those waits set on expiry (0 = none) and qe_w4_clear_error resets it. Both
+ * synchronise with the device. No counterpart in the reference. */
 int qe_w4_ring_error(void);
+int qe_w4_clear_error(void);
 
 #ifdef __cplusplus
 }

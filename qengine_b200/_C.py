@@ -163,6 +163,27 @@ def commit(ctl, in_tok, am, drafts, k):
                         _stream()), "commit")
 
 
+def accept_commit(in_tok, am, n, ctl, next_tok, log, drafts, k):
+    """`accept` then `commit` in one launch (passes without draft rows; not in the reference)."""
+    for t in (in_tok, am, ctl, next_tok, log, drafts):
+        _chk(t, I32, "int buffer")
+    n, k = int(n), int(k)
+    _req(in_tok.numel() > max(n, k) and am.numel() >= n and next_tok.numel() >= n and ctl.numel() >= 24 and
+         drafts.numel() >= k, "accept_commit: buffers too small")
+    check(lib.qe_accept_commit(in_tok.data_ptr(), am.data_ptr(), n, ctl.data_ptr(), next_tok.data_ptr(),
+                               log.data_ptr(), log.numel(), drafts.data_ptr(), k, _stream()), "accept_commit")
+
+
+def chain_draft(mtp_am, draft_out, src, dst):
+    """draft_out[0] = mtp_am[0]; dst = src (one hidden row): the hand-over between two chained
+    single-row draft passes (not in the reference, which uses two tensor copies)."""
+    _chk(mtp_am, I32, "mtp_am"); _chk(draft_out, I32, "draft_out")
+    _req(src.dtype == BF and dst.dtype == BF and src.is_cuda and dst.is_cuda and src.is_contiguous() and
+         dst.is_contiguous() and src.numel() == dst.numel() and draft_out.numel() >= 1, "chain_draft: row shapes")
+    check(lib.qe_chain_draft(mtp_am.data_ptr(), draft_out.data_ptr(), src.data_ptr(), dst.data_ptr(),
+                             src.numel(), _stream()), "chain_draft")
+
+
 def mtp_select(ctl, mpos, off, src=None, dst=None, mtp_am=None, draft0=None):
     """mpos = off < 0 ? pos : pos + m + 1 + off; optional: dst = src[m], draft0 = mtp_am[m]."""
     _chk(ctl, I32, "ctl"); _chk(mpos, I32, "mpos")

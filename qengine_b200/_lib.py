@@ -18,13 +18,20 @@ class W4Params(C.Structure):
     """struct qe_w4_params"""
     _fields_ = [("qw", P), ("scales", P), ("x", P), ("out", P), ("ws", P), ("counters", P),
                 ("M", c_int), ("K", c_int), ("Mp", c_int), ("Kp", c_int), ("N", c_int),
-                ("ldx", c_long), ("ldo", c_long), ("epilogue", c_int), ("x_f16", c_int), ("out_f32", c_int)]
+                ("ldx", c_long), ("ldo", c_long), ("epilogue", c_int), ("out_f32", c_int)]
 
 
 class W4Cfg(C.Structure):
     """struct qe_w4_cfg"""
     _fields_ = [("warps", c_int), ("unroll", c_int), ("ksplit", c_int), ("pdl", c_int),
                 ("variant", c_int), ("mode", c_int), ("blocks_per_sm", c_int), ("min_units", c_int)]
+
+
+class W4Norm(C.Structure):
+    """struct qe_w4_norm"""
+    _fields_ = [("h_in", P), ("tok", P), ("vocab", c_int), ("delta", P), ("norm_w", P), ("h_out", P),
+                ("xn_out", P), ("ldh", c_long), ("ldd", c_long), ("ldho", c_long), ("ldxo", c_long),
+                ("eps", c_float), ("prefetch", P), ("prefetch_bytes", c_size_t)]
 
 
 class W4Plan(C.Structure):
@@ -60,6 +67,8 @@ SIGNATURES = {
     "qe_tp_clear_error": (c_int, [P]),
     "qe_accept": (c_int, [P, P, c_int, P, P, P, c_int, P]),
     "qe_commit": (c_int, [P, P, P, P, c_int, P]),
+    "qe_accept_commit": (c_int, [P, P, c_int, P, P, P, c_int, P, c_int, P]),
+    "qe_chain_draft": (c_int, [P, P, P, P, c_int, P]),
     "qe_mtp_select": (c_int, [P, P, c_int, P, c_long, P, c_int, P, P, P]),
     "qe_force_drafts": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P]),
     "qe_gdn_step_n": (c_int, [P, P, P, P, c_long, P, P, P, P, P, P, P, P, P, P, P, c_long, c_int,
@@ -79,7 +88,9 @@ SIGNATURES = {
     "qe_w4_plan_gemv": (c_int, [C.POINTER(W4Params), C.POINTER(W4Cfg), C.POINTER(W4Plan)]),
     "qe_w4_auto_ksplit": (c_int, [c_int, c_int, c_int, c_int]),
     "qe_w4_gemv": (c_int, [C.POINTER(W4Params), C.POINTER(W4Cfg), P]),
+    "qe_w4_gemv_ex": (c_int, [C.POINTER(W4Params), C.POINTER(W4Norm), C.POINTER(W4Cfg), P]),
     "qe_w4_ring_error": (c_int, []),
+    "qe_w4_clear_error": (c_int, []),
     "qe_w4_gemv_static": (c_int, [C.POINTER(W4Params), C.POINTER(W4Cfg), P]),
 }
 

@@ -7,6 +7,10 @@ libqengine_b200.so through ctypes.
     gemv_swiglu(x, qw, scales, out, I, ...same...)
     auto_ksplit(Mp, Kp, N, warps=8)
 
+Additions without a counterpart in the reference: `gemv_partial` (fp32 partial sums of a matrix
+split along K over tensor-parallel ranks), `gemv_fused` (the GEMV with the residual add + RMSNorm
+that produces its input fused into the launch) and `gemv_static` (no allocation).
+
 Workspace: like the reference binding (gemv_w4_bind.cpp:12-22, 71-79) a per-device, grow-only
 pair of buffers is kept here -- fp32 partial-sum slots (contents irrelevant) and int32 arrival
 counters that the kernel leaves zeroed. They grow only outside CUDA-graph capture (the first,
@@ -19,7 +23,7 @@ import ctypes as C
 
 import torch
 
-from ._lib import W4Cfg, W4Params, W4Plan, check, launches, lib
+from ._lib import W4Cfg, W4Norm, W4Params, W4Plan, check, launches, lib
 
 EPI_NONE, EPI_SWIGLU = 0, 1
 _MIN_WS_FLOATS, _MIN_COUNTERS = 1 << 18, 1 << 14
@@ -56,59 +60,87 @@ def _workspace(dev: torch.device, ws_floats: int, counters: int) -> _Workspace:
     return W
 
 
-def _run(x, qw, scales, out, M, epilogue, warps, unroll, ksplit, pdl, variant, mode, bps, min_units,
-         allow_f16=False):
-    for t in (x, qw, scales, out):
-        _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
-    x_f16 = allow_f16 and x.dtype == torch.float16
-    out_f32 = allow_f16 and out.dtype == torch.float32 and epilogue == EPI_NONE
-    _req(x.dtype == torch.bfloat16 or x_f16, "x must be bf16 (W4A16 kernel)")
-    _req(out.dtype == torch.bfloat16 or out_f32, "out must be bf16")
+def reset_workspaces():
+    """Zero the arrival counters of every device's workspace. Only needed after a launch that
+    reported a ring error (`ring_error() != 0`): such a launch may leave counters non-zero."""
+    for W in _per_device.values():
+        if W.counters is not None:
+            W.counters.zero_()
+
+
+def _packed(qw, scales):
     _req(qw.dtype == torch.int32 and qw.dim() == 4 and qw.size(2) == 32 and qw.size(3) == 4,
          "qw must be int32 [Mp/16, Kp/64, 32, 4] from quant.quantize_w4")
     _req(scales.dtype == torch.float16 and scales.dim() == 3 and scales.size(2) == 16,
          "scales must be fp16 [Mp/16, Kp/128, 16]")
     _req(qw.is_contiguous() and scales.is_contiguous(), "packed tensors must be contiguous")
+    Mp, Kp = qw.size(0) * 16, qw.size(1) * 64
+    _req(Kp % 128 == 0 and scales.size(0) == qw.size(0) and scales.size(1) == Kp // 128,
+         "qw / scales shapes disagree")
+    _req(qw.data_ptr() % 16 == 0 and scales.data_ptr() % 16 == 0, "packed tensors must be 16-byte aligned")
+    return Mp, Kp
+
+
+def _cfg(warps, unroll, ksplit, pdl, variant, mode, bps, min_units):
+    _req(warps in (0, 4, 8, 16), "warps in {0 (auto),4,8,16}")
+    _req(unroll in (0, 1, 2, 4), "unroll in {0 (auto),1,2,4}")
+    _req(mode in (-1, 0, 2, 3, 4), "mode in {-1 (auto), 0, 2, 3, 4}")
+    return W4Cfg(int(warps), int(unroll), int(ksplit), int(bool(pdl)), int(variant), int(mode), int(bps),
+                 int(min_units))
+
+
+def _launch(p, cfg, nrm, dev, what):
+    plan = W4Plan()
+    check(lib.qe_w4_plan_gemv(C.byref(p), C.byref(cfg), C.byref(plan)), f"{what} plan", kernels=0)
+    W = _workspace(dev, plan.ws_floats, plan.counters)
+    p.ws, p.counters = W.ws.data_ptr(), W.counters.data_ptr()
+    stream = torch.cuda.current_stream().cuda_stream
+    if nrm is None:
+        code = lib.qe_w4_gemv(C.byref(p), C.byref(cfg), stream)
+    else:
+        code = lib.qe_w4_gemv_ex(C.byref(p), C.byref(nrm), C.byref(cfg), stream)
+    _req(code != -22, f"{what}: argument combination not supported by the kernel")
+    _req(code == 0, f"{what} launch failed: CUDA error {code}")
+    launches[0] += 1
+
+
+def _run(x, qw, scales, out, M, epilogue, warps, unroll, ksplit, pdl, variant, mode, bps, min_units,
+         allow_f32_out=False, prefetch=None):
+    for t in (x, qw, scales, out):
+        _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
+    out_f32 = allow_f32_out and out.dtype == torch.float32 and epilogue == EPI_NONE
+    _req(x.dtype == torch.bfloat16, "x must be bf16 (W4A16 kernel)")
+    _req(out.dtype == torch.bfloat16 or out_f32, "out must be bf16")
+    Mp, Kp = _packed(qw, scales)
     _req(x.dim() == 2 and out.dim() == 2, "x [N,K], out [N,M]")
     _req(x.stride(1) == 1 and out.stride(1) == 1, "x and out need unit stride along K / M")
     N, K = x.size(0), x.size(1)
     M = int(M)
     _req(1 <= N <= 8, "N must be 1..8")
     _req(out.size(0) == N and out.size(1) == M, "out shape must be [N, M]")
-    Mp, Kp = qw.size(0) * 16, qw.size(1) * 64
-    _req(Kp % 128 == 0 and scales.size(0) == qw.size(0) and scales.size(1) == Kp // 128,
-         "qw / scales shapes disagree")
     _req(Kp - 128 < K <= Kp, f"x has K={K} but the packed weight has Kp={Kp}")
     if epilogue == EPI_SWIGLU:
         _req(Mp // 2 - 8 < M <= Mp // 2, "SwiGLU: out width I must match packed rows/2")
     else:
         _req(Mp - 16 < M <= Mp, "out width M must match packed rows")
     _req(x.data_ptr() != out.data_ptr(), "in-place not supported")
-    _req(warps in (0, 4, 8, 16), "warps in {0 (auto),4,8,16}")
-    _req(unroll in (0, 1, 2, 4), "unroll in {0 (auto),1,2,4}")
-    _req(mode in (-1, 0, 2, 3, 4), "mode in {-1 (auto), 0, 2, 3, 4}")
-
+    cfg = _cfg(warps, unroll, ksplit, pdl, variant, mode, bps, min_units)
     p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None,
-                 M, K, Mp, Kp, N, x.stride(0), out.stride(0), epilogue, int(x_f16), int(out_f32))
-    if x_f16:
-        _req(K == Kp and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0,
-             "fp16 activations need K % 128 == 0 and 16-byte aligned rows")
-    cfg = W4Cfg(int(warps), int(unroll), int(ksplit), int(bool(pdl)), int(variant), int(mode),
-                int(bps), int(min_units))
-    plan = W4Plan()
-    check(lib.qe_w4_plan_gemv(C.byref(p), C.byref(cfg), C.byref(plan)), "gemv_w4 plan", kernels=0)
-    W = _workspace(x.device, plan.ws_floats, plan.counters)
-    p.ws, p.counters = W.ws.data_ptr(), W.counters.data_ptr()
-    code = lib.qe_w4_gemv(C.byref(p), C.byref(cfg), torch.cuda.current_stream().cuda_stream)
-    _req(code == 0, f"gemv_w4 launch failed: CUDA error {code}")
-    launches[0] += 1
+                 M, K, Mp, Kp, N, x.stride(0), out.stride(0), epilogue, int(out_f32))
+    nrm = None
+    if prefetch is not None:  # L2 hint only: no prologue
+        nrm = W4Norm()
+        nrm.prefetch, nrm.prefetch_bytes = prefetch.data_ptr(), prefetch.numel() * prefetch.element_size()
+    _launch(p, cfg, nrm, x.device, "gemv_w4")
 
 
 def gemv(x, qw, scales, out, M, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
-         blocks_per_sm=0, min_units=4):
-    """out[N, M] = x[N, K] @ W~^T (W packed by quant.quantize_w4)."""
+         blocks_per_sm=0, min_units=4, prefetch=None):
+    """out[N, M] = x[N, K] @ W~^T (W packed by quant.quantize_w4). prefetch (not in the reference):
+    a tensor whose bytes a later kernel will stream; the launch asks L2 for them before it waits
+    for its own input."""
     _run(x, qw, scales, out, M, EPI_NONE, warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm,
-         min_units)
+         min_units, prefetch=prefetch)
 
 
 def gemv_swiglu(x, qw, scales, out, I, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
@@ -118,15 +150,61 @@ def gemv_swiglu(x, qw, scales, out, I, warps=0, unroll=0, ksplit=0, pdl=True, va
          min_units)
 
 
-def gemv_act16(x, qw, scales, out, M, swiglu=False, **kw):
-    """Engine-internal variant (not in the reference): x may be fp16 (an exact copy of bf16-rounded
-    values; the fp16 unpack needs fewer integer-pipe instructions per weight), and `out` may be
-    fp32 with the plain epilogue: unrounded partial sums of a matrix split along K over
-    tensor-parallel ranks."""
-    cfg = dict(warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1, blocks_per_sm=0, min_units=4)
-    cfg.update(kw)
-    _run(x, qw, scales, out, M, EPI_SWIGLU if swiglu else EPI_NONE, cfg["warps"], cfg["unroll"], cfg["ksplit"],
-         cfg["pdl"], cfg["variant"], cfg["mode"], cfg["blocks_per_sm"], cfg["min_units"], allow_f16=True)
+def gemv_partial(x, qw, scales, out32, M, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
+                 blocks_per_sm=0, min_units=4):
+    """Not in the reference: `out32` is fp32 [N, M] and receives the unrounded sums -- one rank's
+    partial result of a matrix split along K over tensor-parallel ranks."""
+    _req(out32.dtype == torch.float32, "out32 must be fp32")
+    _run(x, qw, scales, out32, M, EPI_NONE, warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm,
+         min_units, allow_f32_out=True)
+
+
+def gemv_fused(h_in, delta, norm_w, eps, qw, scales, out, M, *, h_out=None, xn_out=None, tok=None,
+               swiglu=False, prefetch=None, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
+               blocks_per_sm=0, min_units=4):
+    """Not in the reference: out = gemv(RMSNorm1p(h_in + delta) * (1 + norm_w)) in one launch.
+
+    h_in bf16 [N, K]; delta bf16 [N, K] or None; h_out (optional, must not alias h_in) receives
+    bf16(h_in + delta) and xn_out (optional) the normed rows. With `tok` (int32 [>= N]) h_in is an
+    embedding table [V, K] and row r is table[tok[r]]. `prefetch` = a tensor whose bytes a later
+    kernel will stream (an L2 hint). Same arithmetic as `_C.rmsnorm1p` followed by `gemv`."""
+    for t in (h_in, norm_w, qw, scales, out):
+        _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
+    Mp, Kp = _packed(qw, scales)
+    bf = torch.bfloat16
+    _req(h_in.dtype == bf and norm_w.dtype == bf and out.dtype == bf, "h_in, norm_w and out must be bf16")
+    _req(out.dim() == 2 and out.stride(1) == 1, "out [N, M] rows")
+    N, M = out.size(0), int(M)
+    _req(1 <= N <= 8 and out.size(1) == M, "N in 1..8 and out [N, M]")
+    _req(h_in.dim() == 2 and h_in.stride(1) == 1 and h_in.size(1) == Kp and norm_w.numel() == Kp and
+         norm_w.is_contiguous(), "h_in [*, K] with K == Kp, norm_w [K]")
+    _req((Mp // 2 - 8 < M <= Mp // 2) if swiglu else (Mp - 16 < M <= Mp), "out width must match packed rows")
+    nrm = W4Norm()
+    nrm.h_in, nrm.ldh, nrm.norm_w, nrm.eps = h_in.data_ptr(), h_in.stride(0), norm_w.data_ptr(), float(eps)
+    if tok is not None:
+        _req(tok.dtype == torch.int32 and tok.is_contiguous() and tok.numel() >= N and h_in.is_contiguous(),
+             "tok int32 [>= N], contiguous table")
+        nrm.tok, nrm.vocab = tok.data_ptr(), h_in.size(0)
+    else:
+        _req(h_in.size(0) == N, "h_in must have N rows")
+    for name, t in (("delta", delta), ("h_out", h_out), ("xn_out", xn_out)):
+        if t is None:
+            continue
+        _req(t.is_cuda and t.dtype == bf and t.dim() == 2 and t.stride(1) == 1 and t.size(0) == N and
+             t.size(1) == Kp, f"{name} must be bf16 [N, K]")
+    if delta is not None:
+        nrm.delta, nrm.ldd = delta.data_ptr(), delta.stride(0)
+    if h_out is not None:
+        _req(h_out.data_ptr() != h_in.data_ptr(), "h_out must not alias h_in")
+        nrm.h_out, nrm.ldho = h_out.data_ptr(), h_out.stride(0)
+    if xn_out is not None:
+        nrm.xn_out, nrm.ldxo = xn_out.data_ptr(), xn_out.stride(0)
+    if prefetch is not None:
+        nrm.prefetch, nrm.prefetch_bytes = prefetch.data_ptr(), prefetch.numel() * prefetch.element_size()
+    cfg = _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units)
+    p = W4Params(qw.data_ptr(), scales.data_ptr(), None, out.data_ptr(), None, None, M, Kp, Mp, Kp, N,
+                 0, out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, 0)
+    _launch(p, cfg, nrm, out.device, "gemv_w4 fused")
 
 
 def auto_ksplit(Mp, Kp, N, warps=8):
@@ -134,8 +212,12 @@ def auto_ksplit(Mp, Kp, N, warps=8):
 
 
 def ring_error():
-    """Sticky error word of mode 3's bounded barrier waits (0 = none); synchronises."""
+    """Sticky error word of the weight rings' bounded barrier waits (0 = none); synchronises."""
     return int(lib.qe_w4_ring_error())
+
+
+def clear_error():
+    lib.qe_w4_clear_error()
 
 
 def gemv_static(x, qw, scales, out, M, swiglu=False, warps=0, unroll=0, ksplit=0, variant=0, mode=-1,
@@ -153,18 +235,14 @@ def gemv_static(x, qw, scales, out, M, swiglu=False, warps=0, unroll=0, ksplit=0
     for t in (x, qw, scales, out):
         _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
     _req(x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "x and out must be bf16")
-    _req(qw.dtype == torch.int32 and qw.dim() == 4 and qw.size(2) == 32 and qw.size(3) == 4 and qw.is_contiguous(),
-         "qw must be contiguous int32 [Mp/16, Kp/64, 32, 4]")
-    _req(scales.dtype == torch.float16 and scales.dim() == 3 and scales.size(2) == 16 and scales.is_contiguous(),
-         "scales must be contiguous fp16 [Mp/16, Kp/128, 16]")
+    Mp, Kp = _packed(qw, scales)
     _req(x.dim() == 2 and out.dim() == 2 and x.stride(1) == 1 and out.stride(1) == 1, "x [N,K], out [N,M] rows")
     N, K, M = x.size(0), x.size(1), int(M)
-    Mp, Kp = qw.size(0) * 16, qw.size(1) * 64
     _req(1 <= N <= 8 and out.size(0) == N and out.size(1) == M, "N in 1..8 and out [N, M]")
-    _req(scales.size(0) == qw.size(0) and scales.size(1) * 128 == Kp and Kp - 128 < K <= Kp, "shapes disagree")
+    _req(Kp - 128 < K <= Kp, "shapes disagree")
     _req((Mp // 2 - 8 < M <= Mp // 2) if swiglu else (Mp - 16 < M <= Mp), "out width must match packed rows")
     p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None, M, K, Mp, Kp, N,
-                 x.stride(0), out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, 0, 0)
+                 x.stride(0), out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, 0)
     cfg = W4Cfg(int(warps), int(unroll), int(ksplit), 0, int(variant), int(mode), int(blocks_per_sm), int(min_units))
     code = lib.qe_w4_gemv_static(C.byref(p), C.byref(cfg), torch.cuda.current_stream().cuda_stream)
     _req(code != -28, "gemv_static: this shape needs more scratch than the library's fixed array "

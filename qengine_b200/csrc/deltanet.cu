@@ -138,6 +138,10 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
                0.f, buf, false);
     buf ^= 1;
   }
+  // This CTA is done reading the checkpoints of the previous pass. The CTA with cs == 0 overwrites
+  // st_k / st_g in step 2c while its siblings may still be replaying from them: split cluster
+  // barrier, arrive here, wait just before 2c (the conv and l2norm work in between hides it).
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   if (pend > 0) {
 #pragma unroll
     for (int i = 0; i < RP; ++i) Sj[(size_t)(warp * RP + i) * D] = s[i];
@@ -215,6 +219,7 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
   __syncthreads();
 
   // ---- 2c. checkpoint every row for the next pass (k, gates: one CTA per head; v: own slice) ----
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // siblings finished their replay
   for (int t = 0; t < n; ++t) {
     if (cs == 0) {
       for (int i = tid; i < D; i += NT) a.st_k[((size_t)t * a.Hv + j) * D + i] = k_s[t][i];

@@ -13,12 +13,9 @@
 namespace qb {
 namespace {
 
-__global__ void accept_rows_kernel(const int* in_tok, const int* am, int n,
-                                   int* ctl, int* next_tok,
-                                   int* log, int max_len) {
-  dep_release();
-  dep_wait();
-  if (threadIdx.x != 0) return;
+// One thread: acceptance of a pass over n rows. Returns m, the index of the last kept row.
+__device__ __forceinline__ int accept_rows(const int* in_tok, const int* am, int n, int* ctl, int* next_tok,
+                                           int* log, int max_len) {
   const int pos = ctl[0], mode = ctl[2];
   int m;
   if (mode == 1) {
@@ -40,18 +37,48 @@ __global__ void accept_rows_kernel(const int* in_tok, const int* am, int n,
     next_tok[n - 1] = follow >= 0 ? follow : am[n - 1];
   }
   ctl[3] = m;
+  return m;
 }
 
-__global__ void commit_rows_kernel(int* ctl, int* in_tok,
-                                   const int* am, const int* drafts, int k) {
-  dep_release();
-  dep_wait();
-  if (threadIdx.x != 0) return;
-  const int m = ctl[3];
+// One thread: the kept rows become the sequence, the next pass starts from the model's token.
+__device__ __forceinline__ void commit_rows(int m, int* ctl, int* in_tok, const int* am, const int* drafts, int k) {
   ctl[0] += m + 1;
   ctl[1] = m + 1;
   in_tok[0] = am[m];
   for (int j = 0; j < k; ++j) in_tok[1 + j] = drafts[j];
+}
+
+__global__ void accept_rows_kernel(const int* in_tok, const int* am, int n, int* ctl, int* next_tok, int* log,
+                                   int max_len) {
+  dep_release();
+  dep_wait();
+  if (threadIdx.x == 0) accept_rows(in_tok, am, n, ctl, next_tok, log, max_len);
+}
+
+__global__ void commit_rows_kernel(int* ctl, int* in_tok, const int* am, const int* drafts, int k) {
+  dep_release();
+  dep_wait();
+  if (threadIdx.x == 0) commit_rows(ctl[3], ctl, in_tok, am, drafts, k);
+}
+
+// A pass without draft rows (plain decode, prefill) has nothing between acceptance and commit:
+// both in one launch.
+__global__ void accept_commit_kernel(int* in_tok, const int* am, int n, int* ctl, int* next_tok, int* log,
+                                     int max_len, const int* drafts, int k) {
+  dep_release();
+  dep_wait();
+  if (threadIdx.x != 0) return;
+  const int m = accept_rows(in_tok, am, n, ctl, next_tok, log, max_len);
+  commit_rows(m, ctl, in_tok, am, drafts, k);
+}
+
+// End of a chained draft pass (one row): the drafted token joins the draft list and the draft
+// layer's output row becomes the hidden input of the next chained pass.
+__global__ void chain_draft_kernel(const int* mtp_am, int* draft_out, const bf16* src, bf16* dst, int H) {
+  dep_release();
+  dep_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) draft_out[0] = mtp_am[0];
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) dst[i] = src[i];
 }
 
 __global__ void mtp_select_rows_kernel(const int* ctl, int* mpos, int off,
@@ -109,6 +136,20 @@ extern "C" int qe_commit(int* ctl, int* in_tok, const int* am, const int* drafts
   if (k < 0 || k >= QE_MAX_ROWS) return QE_ERR_ARG;
   return (int)launch(commit_rows_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, pdl_on(), ctl,
                      in_tok, am, drafts, k);
+}
+
+extern "C" int qe_accept_commit(int* in_tok, const int* am, int n, int* ctl, int* next_tok, int* log,
+                                int max_len, const int* drafts, int k, void* stream) {
+  if (n < 1 || n > QE_MAX_ROWS || k < 0 || k >= QE_MAX_ROWS) return QE_ERR_ARG;
+  return (int)launch(accept_commit_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, pdl_on(), in_tok, am, n,
+                     ctl, next_tok, log, max_len, drafts, k);
+}
+
+extern "C" int qe_chain_draft(const int* mtp_am, int* draft_out, const void* src, void* dst, int H,
+                              void* stream) {
+  if (H < 1) return QE_ERR_ARG;
+  return (int)launch(chain_draft_kernel, dim3((H + 255) / 256), dim3(256), 0, (cudaStream_t)stream, pdl_on(),
+                     mtp_am, draft_out, (const bf16*)src, (bf16*)dst, H);
 }
 
 extern "C" int qe_mtp_select(const int* ctl, int* mpos, int off, const void* src, long lds, void* dst,

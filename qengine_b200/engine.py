@@ -1,45 +1,55 @@
-"""Batch-1 decode engine: plain greedy decoding and MTP speculative decoding, every pass captured
-as one CUDA graph with all bookkeeping on the device.
+"""Batch-1 decode engine for B200: plain greedy decoding and MTP speculative decoding, each pass
+variant captured once as a CUDA graph, all bookkeeping on the device.
 
-Public surface mirrors the reference engine (python/qengine/engine.py:189-687): `Engine`,
-`.generate`, `.generate_spec`, `.prefill`, `.graph`, `.sequence_logits`, `.mtp_rows_logits`,
-`.reset`, and the linear backends `W4Linear` / `BF16Linear`. The model comes as a weights dict
-in the fused layout (see qengine_b200.synth) instead of a checkpoint directory: weight loading,
-quantisation caches and tokenizers are outside this library.
+The public names mirror the reference engine (python/qengine/engine.py:189-687) so that its
+callers can switch: `Engine` with `generate`, `generate_spec`, `prefill`, `graph`,
+`sequence_logits`, `mtp_rows_logits`, `reset`, `pin_mtp_l2`, and the linear backends `W4Linear` /
+`BF16Linear`. The model arrives as a weights dict in the fused layout (qengine_b200.synth or
+qengine_b200.cache) rather than as a checkpoint directory.
+
+What is different from the reference is the graph itself. The reference launches one kernel per
+operator (487 per token at the 27B shape); here the residual stream is an object (`_Residual`)
+that remembers which sub-layer output is still to be added, and the add + RMSNorm is executed
+inside the next W4 GEMV launch (qe_w4_gemv_ex): every block of the GEMV recomputes the ten
+kilobytes of normalised input in its shared memory while its weight rings are already filling.
+The embedding gather rides on the first GEMV the same way, the final norm on the lm_head GEMV,
+accept + commit are one kernel in plain decoding. A 27B-shape token is 4 GEMV launches per layer
+plus the mixer.
 
 A pass runs n = 1..8 rows (tokens at positions pos .. pos + n - 1):
-  plain decode  n = 1;
-  verify        n = k + 1 rows [last token, draft 1..k]; the longest prefix of drafts equal to
-                the model's own argmax is kept, plus the model's next token;
-  prefill       up to 8 prompt tokens per pass.
-One graph replay = one decode step or one whole speculative cycle (verify, MTP rows, k - 1
-chained drafts, commit); the host only reads `pos` once per batch of cycles.
+  decode   n = 1
+  verify   n = k + 1 rows [last token, draft 1 .. draft k]; the longest prefix of drafts that
+           equals the model's own greedy choice is kept, plus the model's next token
+  prefill  up to 8 prompt tokens per pass
+One graph replay is one decode step or one whole speculative cycle (verify, MTP rows, k - 1
+chained drafts, commit); the host reads the position once per batch of cycles.
 
-Rollback: KV rows of rejected drafts are overwritten later; DeltaNet rows are staged as
-per-position checkpoints and only the kept ones are replayed by the next pass (deltanet.cu).
-Every kernel computes row r of an n-row pass exactly as a 1-row pass would, so speculative output
-is token-identical to plain greedy output.
+Rollback costs nothing: K/V rows of rejected drafts are simply overwritten, DeltaNet rows are
+staged as per-position checkpoints of which the next pass replays only the kept ones
+(csrc/deltanet.cu). Every kernel computes row r of an n-row pass exactly as a 1-row pass would,
+which makes speculative output token-identical to plain greedy output.
 """
 from __future__ import annotations
 
+import os
+from contextlib import contextmanager
+
 import torch
 
-from . import _C
-from ._lib import launches
+from . import _C, _w4
+from ._lib import launches, lib
 from .quant import W4Packed
 from .synth import Config
 
 BF16, I32, F32 = torch.bfloat16, torch.int32, torch.float32
-
-
-def _lib_sm_count() -> int:
-    from ._lib import lib
-    return max(1, int(lib.qe_sm_count()))
 NMAX = 8  # rows per pass
 
 
+# ----------------------------------------------------------------------------------------------
+# Linear backends
+# ----------------------------------------------------------------------------------------------
 class BF16Linear:
-    """BF16 GEMV backend (weights read once for all rows, fp32 accumulate)."""
+    """Unquantised GEMV backend (weights read once for all rows, fp32 accumulate)."""
     name = "bf16"
 
     def prepare(self, w):
@@ -50,18 +60,13 @@ class BF16Linear:
 
 
 class W4Linear:
-    """Adapter over the W4A16 GEMV (`_w4`), the only caller of that API
-    (reference python/qengine/engine.py:74-115). Launch keyword arguments are passed through."""
+    """Adapter over the W4A16 GEMV (`_w4`); like its namesake in the reference
+    (python/qengine/engine.py:74-115) it is the only place that touches that API. Keyword
+    arguments given at construction are forwarded to every launch."""
     name = "w4"
 
-    def __init__(self, ksplit_max=64, **kw):
-        self.ksplit_max, self.kw = ksplit_max, dict(kw)
-        # at least 6 units per warp: the 5120 x 6144 out_proj (320 tiles of 48 units) then runs on
-        # 2,560 warps = 320 CTAs of exactly one tile each, so no tile crosses a CTA boundary and all
-        # of them finish through shared memory: 3 % of the whole W4 time of a token (measured; 5 and
-        # 7 are both slower, and forcing the same alignment on `down` or the lm_head costs more in
-        # idle warp slots than it saves)
-        self.kw.setdefault("min_units", 6)
+    def __init__(self, **launch_kw):
+        self.kw = dict(launch_kw)
 
     def prepare(self, w):
         from .quant import quantize_w4
@@ -71,130 +76,271 @@ class W4Linear:
         from .quant import quantize_w4_gate_up
         return quantize_w4_gate_up(wg, wu)
 
-    def _ks(self, p, n):
-        from . import _w4
-        ks = _w4.auto_ksplit(p.qw.shape[0] * 16, p.qw.shape[1] * 64, n, self.kw.get("warps", 8) or 8)
-        return min(ks, self.ksplit_max)
-
-    def __call__(self, x, p, out):
-        from . import _w4
-        _w4.gemv(x, p.qw, p.scales, out, p.M, ksplit=self._ks(p, x.shape[0]), **self.kw)
-
-    def gate_up(self, x, p, out):
-        from . import _w4
-        _w4.gemv_swiglu(x, p.qw, p.scales, out, p.M, ksplit=self._ks(p, x.shape[0]), **self.kw)
-
-    def partial(self, x, p, out32):
-        """Unrounded fp32 result: one rank's partial sums of a matrix split along K."""
-        from . import _w4
-        _w4.gemv_act16(x, p.qw, p.scales, out32, p.M, ksplit=self._ks(p, x.shape[0]), **self.kw)
-
     @staticmethod
     def dequantize(p):
         from .quant import dequantize_w4
         return dequantize_w4(p)
 
+    def __call__(self, x, p, out, **kw):
+        _w4.gemv(x, p.qw, p.scales, out, p.M, **{**self.kw, **kw})
 
+    def gate_up(self, x, p, out):
+        _w4.gemv_swiglu(x, p.qw, p.scales, out, p.M, **self.kw)
+
+    def partial(self, x, p, out32):
+        """fp32 partial sums of a matrix whose K dimension is split over tensor-parallel ranks."""
+        _w4.gemv_partial(x, p.qw, p.scales, out32, p.M, **self.kw)
+
+    def after_norm(self, h, delta, w, eps, p, out, **kw):
+        """out = p(RMSNorm1p(h + delta)) in one launch (see `_w4.gemv_fused`)."""
+        kw = {**self.kw, **kw}
+        if out.shape[0] > 7:  # eight rows of x only fit beside the smaller ring geometry
+            kw.setdefault("unroll", 2)
+        _w4.gemv_fused(h, delta, w, eps, p.qw, p.scales, out, p.M, swiglu=p.gate_up, **kw)
+
+
+# ----------------------------------------------------------------------------------------------
+# The residual stream of one pass
+# ----------------------------------------------------------------------------------------------
+class _Residual:
+    """Rows h[:n] of a residual stream plus whatever has been produced but not yet added to it.
+
+    `owed` is the output of the last K-split matrix (attention / DeltaNet out-projection, MLP
+    down-projection, MTP fc): one bf16 buffer on a single GPU, fp32 partial rows per rank under
+    tensor parallelism. It is added by the next norm, which is where the three execution modes
+    differ:
+      fused   the add + norm run inside the next GEMV (`W4Linear.after_norm`); the updated stream
+              is written to the spare buffer by one block, so the two buffers swap roles;
+      plain   `_C.rmsnorm1p` with its residual argument, then the GEMV;
+      tp      the ranks' partial rows are exchanged and summed inside the norm kernel
+              (`TPGroup.exchange_norm`, or all-gather + `_C.rmsnorm1p_parts`).
+    """
+
+    def __init__(self, eng, n, rows, spare, xn):
+        self.e, self.n = eng, n
+        self.h, self.spare, self.xn = rows[:n], spare[:n], xn[:n]
+        self.owed = False
+        self.tok = None  # set: the rows are embedding rows that have not been gathered yet
+
+    def start_from_tokens(self, tok, ordered):
+        """Rows = embedding rows of `tok`. Returns True when the plain-stream-order launch that
+        opens a pass (Engine._ordered_first_launch) is still to come."""
+        e = self.e
+        self.owed = False
+        if e.fuse and isinstance(e.layers[0]["in_proj"], W4Packed) and isinstance(e.linear, W4Linear):
+            self.tok = tok  # gathered by the prologue of the first GEMV
+            return ordered
+        if ordered:
+            with e._ordered_first_launch():
+                _C.embed(e.embed, tok, self.h)
+        else:
+            _C.embed(e.embed, tok, self.h)
+        return False
+
+    def start_from_rows(self):
+        self.owed, self.tok = False, None
+
+    def owe(self, x, p, lin, prefetch=None):
+        """A matrix split along K on the ranks: its result is added by the next norm."""
+        e, n = self.e, self.n
+        if e.tp is None:
+            if prefetch is not None and isinstance(lin, W4Linear):
+                lin(x, p, e.mo[:n], prefetch=prefetch)
+            else:
+                lin(x, p, e.mo[:n])
+        else:
+            lin.partial(x, p, e.part32[:n])
+            if e.tp.transport == "nccl":
+                e.tp.all_gather(e.parts[n], e.part32[:n])
+        self.owed = True
+
+    def zero_then_owe(self, x, p, lin):
+        """Tensor parallel only: the stream starts as the sum of the ranks' partial rows."""
+        self.h.zero_()
+        self.owe(x, p, lin)
+
+    def _norm(self, w, out):
+        e, n = self.e, self.n
+        if not self.owed:
+            _C.rmsnorm1p(self.h, None, w, out, e.cfg.eps)
+        elif e.tp is None:
+            _C.rmsnorm1p(self.h, e.mo[:n], w, out, e.cfg.eps)
+        elif e.tp.transport == "nccl":
+            _C.rmsnorm1p_parts(self.h, e.parts[n], w, out, e.cfg.eps)
+        else:
+            e.tp.exchange_norm(self.h, e.part32[:n], w, out, e.cfg.eps)
+        self.owed = False
+
+    def through(self, w, p, out, lin, keep_normed=None, ordered=False):
+        """out = p(norm(h + owed)); keep_normed optionally receives the normed rows. ordered: this
+        is the launch that opens a pass (no programmatic overlap with the previous pass)."""
+        e, n = self.e, self.n
+        fused = e.fuse and isinstance(p, W4Packed) and isinstance(lin, W4Linear)
+        if fused:
+            kw = {"pdl": False} if ordered else {}
+            if self.tok is not None:
+                lin.after_norm(e.embed, None, w, e.cfg.eps, p, out, tok=self.tok, h_out=self.h,
+                               xn_out=keep_normed, **kw)
+                self.tok = None
+            elif self.owed:
+                lin.after_norm(self.h, e.mo[:n], w, e.cfg.eps, p, out, h_out=self.spare, xn_out=keep_normed, **kw)
+                self.h, self.spare = self.spare, self.h
+            else:
+                lin.after_norm(self.h, None, w, e.cfg.eps, p, out, xn_out=keep_normed, **kw)
+            self.owed = False
+            return
+        xn = keep_normed if keep_normed is not None else self.xn
+        self._norm(w, xn)
+        if isinstance(p, W4Packed):
+            (lin.gate_up if p.gate_up else lin)(xn, p, out)
+        else:
+            lin(xn, p, out)
+
+
+# ----------------------------------------------------------------------------------------------
 class Engine:
     GDN_Q = 4
     POS, PENDING, MODE, M, CYCLES, ACCEPTED = range(6)
 
     def __init__(self, cfg: Config, weights: dict, max_len: int = 4096, linear=None, device="cuda",
-                 mtp: bool = True, attn_splits: int | None = None, draft_vocab: int | None = None, tp=None):
-        """weights: dict from qengine_b200.synth.build_model (already on `device`).
-        tp: a qengine_b200.tp.TPGroup for tensor parallelism; then `cfg` is still the whole model's
-        configuration and `weights` is this rank's shard (qengine_b200.tp.shard_model).
-        attn_splits: flash-decoding splits per head (fixed so the graphs are static); default 16,
-        more for caches longer than 8192 positions. draft_vocab: MTP drafts score only the first `draft_vocab` token ids
-        (pruned draft head through the argmax id map); verify keeps the full head."""
+                 mtp: bool = True, attn_splits: int | None = None, draft_vocab: int | None = None, tp=None,
+                 fuse: bool | None = None, prefetch: bool | None = None):
+        """weights: dict in the fused layout (qengine_b200.synth.build_model), already on `device`.
+        tp: a qengine_b200.tp.TPGroup for tensor parallelism; `cfg` then still describes the whole
+        model and `weights` is this rank's shard (qengine_b200.tp.shard_model).
+        attn_splits: flash-decoding splits per head (fixed, so graphs stay static); default 16, more
+        for caches beyond 8192 positions. draft_vocab: drafts score only the first `draft_vocab`
+        token ids (pruned draft head through the argmax id map); verify keeps the full head.
+        fuse: run residual add + RMSNorm inside the following W4 GEMV launch (default: on for a
+        single GPU; under tensor parallelism the norm is fused with the exchange instead).
+        prefetch: let each GEMV ask L2 for the weights of the next one (default: QE_PREFETCH=1)."""
         self.tp, self.vocab_full, self.vocab_base = tp, cfg.vocab, 0
         if tp is not None:
             from .tp import local_config
             tp.open(cfg.hidden)
             cfg = local_config(cfg, tp.size)
             self.vocab_base = tp.rank * cfg.vocab
-        self.cfg, self.max_len = cfg, max_len
-        self.dev = torch.device(device)
-        # the shards of a tensor-parallel rank are small enough that every warp should get work:
-        # 4 units per warp there (measured: 2.17 vs 2.45 ms per token at 4 ranks), 6 on one GPU
-        self.linear = linear or (W4Linear() if tp is None else W4Linear(min_units=4))
-        self.lm_lin = self.linear
+        self.cfg, self.max_len, self.dev = cfg, max_len, torch.device(device)
+        self.linear = linear or W4Linear()
+        self.fuse = (tp is None) if fuse is None else (bool(fuse) and tp is None)
+        self.prefetch = (os.environ.get("QE_PREFETCH", "0") == "1") if prefetch is None else bool(prefetch)
+        self.prefetch_words = int(os.environ.get("QE_PREFETCH_MB", "48")) * (1 << 20) // 4  # int32 words of a hint
         self.embed, self.final_norm = weights["embed"], weights["final_norm"]
         self.lm_head = weights["lm_head"]
+        self.lm_lin = self.linear if isinstance(self.lm_head, W4Packed) else BF16Linear()
         self.layers = [dict(L) for L in weights["layers"]]
         self.has_mtp = bool(mtp and weights.get("mtp"))
         self.mtp = dict(weights["mtp"]) if self.has_mtp else None
-        # long caches: a multiple of 6 selects the tensor-core split kernel (6 splits per CTA);
-        # one CTA per SM and row, i.e. 6 * ceil(SMs / KV heads) splits
-        self.ATTN_SPLITS = attn_splits or (16 if max_len <= 8192 else 6 * -(-_lib_sm_count() // cfg.hkv))
+        # caches beyond 8K positions: a multiple of 6 selects the tensor-core split kernel, sized
+        # to one CTA per SM and row
+        self.ATTN_SPLITS = attn_splits or (16 if max_len <= 8192 else 6 * -(-max(1, int(lib.qe_sm_count())) // cfg.hkv))
         self.draft_head = self.draft_ids = None
         if draft_vocab and self.has_mtp:
-            self._build_draft_head(draft_vocab)
-        self._alloc()
-        self.graphs = {}
-        self.graph_kernels = {}  # kernels of this library per captured graph
-        self.start_pos = 0     # positions [0, start_pos) hold a pre-filled context (set_context)
-        self.force_a = -1      # forced acceptance length for verify passes (< 0: off)
+            self._make_draft_head(draft_vocab)
+        self._make_buffers()
+        self.graphs, self.graph_kernels = {}, {}
+        self.start_pos = 0      # positions [0, start_pos) hold a pre-filled context (set_context)
+        self.force_a = -1       # forced acceptance length of verify passes (< 0: off)
         self.truth = torch.zeros(1, dtype=I32, device=self.dev)
-        _C.set_gdn_early(True)  # safe here: passes start with a fully ordered kernel (see _main)
+        self.l2_win = None      # (base, bytes) of the persisting window around the draft phase
 
-    # ------------------------------------------------------------------------------------------
-    def _build_draft_head(self, nv: int):
-        """Pruned draft head: the first nv rows of the packed lm_head (ids 0..nv-1), no copy of
-        the codes is re-quantised; nv must be a multiple of 16. Under tensor parallelism every rank
-        keeps the first nv / t rows of its own vocabulary slice."""
+    # -- construction -------------------------------------------------------------------------
+    def _make_draft_head(self, nv: int):
+        """The first nv rows of the packed lm_head serve as the draft head (ids 0 .. nv - 1): tiles
+        of 16 rows are independent in the packed format, so this is a slice, not a requantisation.
+        Under tensor parallelism every rank keeps the first nv / t rows of its vocabulary slice."""
         if self.tp is not None:
             nv //= self.tp.size
-        assert nv % 16 == 0 and isinstance(self.lm_head, W4Packed)
+        if nv % 16 or not isinstance(self.lm_head, W4Packed):
+            raise ValueError("draft_vocab must be a multiple of 16 (per rank) on a W4 lm_head")
         p = self.lm_head
         self.draft_head = W4Packed(p.qw[:nv // 16].contiguous(), p.scales[:nv // 16].contiguous(), nv, p.K)
         self.draft_ids = torch.arange(nv, dtype=I32, device=self.dev)
 
-    def _alloc(self):
-        cfg, dev, ml, N = self.cfg, self.dev, self.max_len, NMAX
-        H, I, V = cfg.hidden, cfg.inter, cfg.vocab
-        z = lambda *s, dt=BF16: torch.zeros(*s, dtype=dt, device=dev)
-        self.ctl = z(32, dt=I32)
-        self.in_tok = z(N + 1, dt=I32)
-        self.am, self.next_tok, self.drafts, self.mtp_am = (z(N, dt=I32) for _ in range(4))
-        self.mpos = z(1, dt=I32)
-        self.log = z(ml, dt=I32)
-        self.h, self.xn, self.mo, self.hid = z(N, H), z(N, H), z(N, H), z(N, H)
-        pw = max(cfg.gdn_proj_rows, cfg.attn_proj_rows)
-        self.proj = z(N, (pw + 7) // 8 * 8)
-        self.mix = z(N, max(cfg.value_dim, cfg.hq * cfg.head_dim))
-        self.gu, self.act = z(N, 2 * I), z(N, I)
-        self.logits = z(N, V)
-        self.am_v, self.am_i = z(N * 256, dt=F32), z(N * 256, dt=I32)
-        self.q = z(N, cfg.hq * cfg.head_dim)
-        self.part_o = z(N, cfg.hq, self.ATTN_SPLITS, cfg.head_dim, dt=F32)
-        self.part_ml = z(N, cfg.hq, self.ATTN_SPLITS, 2, dt=F32)
-        rd = cfg.rotary_dim  # built on the CPU in fp32 like the reference, then moved
-        self.inv_freq = (1.0 / (cfg.rope_theta ** (torch.arange(0, rd, 2, dtype=F32) / rd))).to(dev)
-        for L in self.layers:
+    def _make_buffers(self):
+        c, dev, N = self.cfg, self.dev, NMAX
+        H = c.hidden
+
+        def buf(*shape, dt=BF16):
+            return torch.zeros(*shape, dtype=dt, device=dev)
+
+        # control words: ctl[0] pos, [1] pending DeltaNet rows, [2] mode, [3] m, [4] cycles,
+        # [5] accepted drafts, [16 + m] histogram (include/qengine_b200.h)
+        self.ctl, self.in_tok, self.mpos = buf(32, dt=I32), buf(N + 1, dt=I32), buf(1, dt=I32)
+        self.am, self.next_tok, self.drafts, self.mtp_am = (buf(N, dt=I32) for _ in range(4))
+        self.log = buf(self.max_len, dt=I32)
+        # activations of a pass; the residual stream has two homes (see _Residual)
+        self.h, self.h2, self.xn, self.mo, self.hid = (buf(N, H) for _ in range(5))
+        width = max(c.gdn_proj_rows, c.attn_proj_rows)
+        self.proj = buf(N, -(-width // 8) * 8)
+        self.mix = buf(N, max(c.value_dim, c.hq * c.head_dim))
+        self.act = buf(N, c.inter)
+        self.gu = None  # [N, 2 I], only for an unfused gate/up pair (allocated on first use)
+        self.logits = buf(N, c.vocab)
+        self.am_v, self.am_i = buf(N * 256, dt=F32), buf(N * 256, dt=I32)
+        self.q = buf(N, c.hq * c.head_dim)
+        self.part_o = buf(N, c.hq, self.ATTN_SPLITS, c.head_dim, dt=F32)
+        self.part_ml = buf(N, c.hq, self.ATTN_SPLITS, 2, dt=F32)
+        rd = c.rotary_dim  # fp32 on the CPU like the reference (python/qengine/engine.py:403-404)
+        self.inv_freq = (1.0 / (c.rope_theta ** (torch.arange(0, rd, 2, dtype=F32) / rd))).to(dev)
+        for L in self.layers + ([self.mtp] if self.has_mtp else []):
             if L["type"] == "linear_attention":
-                L["ring"] = z(16, cfg.conv_dim)
-                L["S"] = z(cfg.hv, cfg.dk, cfg.dv, dt=F32)
-                L["st_k"], L["st_v"] = z(N, cfg.hv, cfg.dk, dt=F32), z(N, cfg.hv, cfg.dv, dt=F32)
-                L["st_g"] = z(N, cfg.hv, 2, dt=F32)
+                L["ring"] = buf(16, c.conv_dim)
+                L["S"] = buf(c.hv, c.dk, c.dv, dt=F32)
+                L["st_k"], L["st_v"] = buf(N, c.hv, c.dk, dt=F32), buf(N, c.hv, c.dv, dt=F32)
+                L["st_g"] = buf(N, c.hv, 2, dt=F32)
             else:
-                L["kc"], L["vc"] = z(cfg.hkv, ml, cfg.head_dim), z(cfg.hkv, ml, cfg.head_dim)
+                L["kc"], L["vc"] = (buf(c.hkv, self.max_len, c.head_dim) for _ in range(2))
         if self.has_mtp:
-            self.mtp["kc"], self.mtp["vc"] = z(cfg.hkv, ml, cfg.head_dim), z(cfg.hkv, ml, cfg.head_dim)
-            self.cat = z(N, 2 * H)
-            self.mh, self.mout, self.chain_h = z(N, H), z(N, H), z(1, H)
+            self.cat = buf(N, 2 * H)
+            self.mh, self.mh2, self.mout, self.chain_h = buf(N, H), buf(N, H), buf(N, H), buf(1, H)
         if self.tp is not None:
             t = self.tp.size
-            self.part32 = z(N, H, dt=F32)
-            self.parts = {n: z(t, n, H, dt=F32) for n in range(1, N + 1)}
-            self.cand_v, self.cand_i = z(N, dt=F32), z(N, dt=I32)
-            self.all_v = {n: z(t, n, dt=F32) for n in range(1, N + 1)}
-            self.all_i = {n: z(t, n, dt=I32) for n in range(1, N + 1)}
+            self.part32 = buf(N, H, dt=F32)
+            self.parts = {n: buf(t, n, H, dt=F32) for n in range(1, N + 1)}
+            self.cand_v, self.cand_i = buf(N, dt=F32), buf(N, dt=I32)
+            self.all_v = {n: buf(t, n, dt=F32) for n in range(1, N + 1)}
+            self.all_i = {n: buf(t, n, dt=I32) for n in range(1, N + 1)}
+
+    def pin_mtp_l2(self, on: bool, names=("fc", "in_proj", "out"), limit: int | None = None):
+        """Keep the named MTP matrices resident in L2 across the draft passes of a cycle (the
+        reference's experiment, python/qengine/engine.py:360-381, sized for B200: fc + in_proj +
+        o_proj of the 27B draft layer are 81 MB of its ~126 MB L2). The matrices are re-homed into
+        one contiguous buffer so that a single access-policy window covers them; the draft phase
+        of every graph captured afterwards runs under that window. Call before the first
+        `generate_spec`; existing graphs are dropped."""
+        if not self.has_mtp:
+            return
+        if on and getattr(self, "_l2_buf", None) is None:
+            mats = [self.mtp[n] for n in names]
+            chunks = [t for m in mats for t in (m.qw, m.scales)]
+            sizes = [-(-t.numel() * t.element_size() // 256) * 256 for t in chunks]
+            arena = torch.empty(sum(sizes), dtype=torch.uint8, device=self.dev)
+            views, at = [], 0
+            for t, sz in zip(chunks, sizes):
+                v = arena[at:at + t.numel() * t.element_size()].view(t.dtype).view(t.shape)
+                v.copy_(t)
+                views.append(v)
+                at += sz
+            for i, n in enumerate(names):
+                old = self.mtp[n]
+                self.mtp[n] = W4Packed(views[2 * i], views[2 * i + 1], old.M, old.K, old.gate_up)
+            self._l2_buf = arena
+        if on:
+            nbytes = self._l2_buf.numel()
+            _C.l2_persist_limit(int(limit if limit is not None else nbytes))
+            self.l2_win = (self._l2_buf.data_ptr(), nbytes)
+        else:
+            self.l2_win = None
+            _C.l2_persist_limit(0)
+        self.graphs.clear()
+        self.graph_kernels.clear()
 
     def reset(self):
-        """Empty sequence. KV caches need no clearing (only [0, pos] is ever read)."""
+        """Start an empty sequence: DeltaNet state, conv history and control words are cleared;
+        K/V caches are not (rows at or beyond `pos` are never read)."""
         for L in self.layers:
-            if "ring" in L:
+            if "S" in L:
                 L["ring"].zero_()
                 L["S"].zero_()
         self.ctl.zero_()
@@ -203,43 +349,77 @@ class Engine:
 
     @torch.no_grad()
     def set_context(self, length: int, seed: int = 99):
-        """Measurement harness for long caches: pretend `length` positions were already decoded.
-        K and V rows [0, length) of every attention layer (and the draft head's) are filled with
-        seeded N(0, 1) values; sequences then start at position `length` (DeltaNet state empty)."""
-        assert 0 <= length < self.max_len - 2 * NMAX
+        """Measurement harness for long caches: behave as if `length` positions had already been
+        decoded. K and V rows [0, length) of every attention layer (and the draft layer) get seeded
+        N(0, 1) values; sequences then start at position `length` with an empty DeltaNet state."""
+        if not 0 <= length < self.max_len - 2 * NMAX:
+            raise ValueError("context does not fit max_len")
         g = torch.Generator(device=self.dev).manual_seed(seed)
         for L in self.layers + ([self.mtp] if self.has_mtp else []):
-            if "kc" in L:
-                for c in (L["kc"], L["vc"]):
-                    for h in range(c.shape[0]):
-                        c[h, :length].copy_(torch.randn(length, c.shape[2], generator=g, device=self.dev))
+            for name in ("kc", "vc"):
+                if name in L:
+                    for head in L[name]:
+                        head[:length].copy_(torch.randn(length, head.shape[1], generator=g, device=self.dev))
         self.start_pos = int(length)
         self.reset()
 
-    # ------------------------------------------------------------------------------------------
-    # A matrix whose input is split over tensor-parallel ranks (out / o_proj, down, mtp.fc) leaves
-    # its result "pending": single GPU -> bf16 in self.mo; tensor parallel -> every rank's fp32
-    # partial rows gathered into self.parts[n]. The next norm adds the pending rows to the residual.
-    def _ksplit(self, x, p, n, lin):
-        if self.tp is None:
-            lin(x, p, self.mo[:n])
-        else:
-            lin.partial(x, p, self.part32[:n])
-            if self.tp.transport == "nccl":
-                self.tp.all_gather(self.parts[n], self.part32[:n])
+    # -- the pass, as the kernels it launches ----------------------------------------------------
+    @contextmanager
+    def _ordered_first_launch(self):
+        """Programmatic dependent launch lets a kernel's prologue run before its predecessor has
+        finished. Across two passes that is not wanted: the first kernel of a pass is launched in
+        plain stream order, so everything the previous pass wrote (position, pending rows,
+        DeltaNet state and checkpoints) is complete before any early section of this pass runs."""
+        _C.set_pdl_launch(False)
+        try:
+            yield
+        finally:
+            _C.set_pdl_launch(True)
 
-    def _norm(self, h, pending, w, out, eps, n):
-        if not pending:
-            _C.rmsnorm1p(h, None, w, out, eps)
-        elif self.tp is None:
-            _C.rmsnorm1p(h, self.mo[:n], w, out, eps)
-        elif self.tp.transport == "nccl":
-            _C.rmsnorm1p_parts(h, self.parts[n], w, out, eps)
-        else:  # exchange of the partial rows fused into the norm, over peer memory
-            self.tp.exchange_norm(h, self.part32[:n], w, out, eps)
+    def _mixer(self, L, n, pos):
+        """Token mixing on the projected rows in self.proj; result in self.mix."""
+        c = self.cfg
+        if L["type"] == "linear_attention":
+            pr = self.proj[:n, :c.gdn_proj_rows]
+            a0, a1 = c.conv_dim, c.conv_dim + c.value_dim
+            out = self.mix[:n, :c.value_dim]
+            _C.gdn_step_n(pr[:, :a0], pr[:, a0:a1], pr[:, a1:a1 + c.hv], pr[:, a1 + c.hv:], L["ring"],
+                          L["conv_w"], L["A_log"], L["dt_bias"], L["norm_w"], L["S"], L["st_k"], L["st_v"],
+                          L["st_g"], self.ctl, out, c.hk, c.eps, q=self.GDN_Q)
+            return out
+        pr = self.proj[:n, :c.attn_proj_rows]
+        nq = c.hq * 2 * c.head_dim
+        nk = nq + c.hkv * c.head_dim
+        qg, q = pr[:, :nq], self.q[:n]
+        _C.attn_prep(qg, pr[:, nq:nk], pr[:, nk:], L["q_norm"], L["k_norm"], self.inv_freq, pos, q,
+                     L["kc"], L["vc"], c.eps)
+        out = self.mix[:n, :c.hq * c.head_dim]
+        _C.attn_decode(q, L["kc"], L["vc"], pos, qg, self.part_o, self.part_ml, out)
+        return out
 
-    def _argmax(self, logits, n, out, idmap=None):
-        """Greedy token per row (lowest id on ties); vocabulary shards exchange (value, id)."""
+    def _block(self, L, R: _Residual, pos, ordered=False):
+        """One decoder block on the residual stream R: norm -> in_proj -> mixer -> out_proj, then
+        norm -> gate/up + SwiGLU -> down. Both sub-layer outputs stay owed to the stream."""
+        n, lin = R.n, self.linear
+        width = self.cfg.gdn_proj_rows if L["type"] == "linear_attention" else self.cfg.attn_proj_rows
+        R.through(L["in_norm"], L["in_proj"], self.proj[:n, :width], lin, ordered=ordered)
+        mixed = self._mixer(L, n, pos)
+        gu = L["gate_up"]
+        # While the mixer runs the memory system is nearly idle: the out-projection's blocks are
+        # already resident (waiting for the mixer) and ask L2 for the head of the gate/up matrix.
+        hint = gu.qw.view(-1)[:self.prefetch_words] if self.prefetch and isinstance(gu, W4Packed) else None
+        R.owe(mixed, L["out"], lin, prefetch=hint)
+        if isinstance(gu, W4Packed) and gu.gate_up:
+            R.through(L["post_norm"], gu, self.act[:n], lin)
+        else:  # unfused gate / up pair: plain GEMV into [gate | up], SwiGLU as its own kernel
+            if self.gu is None:
+                self.gu = torch.zeros(NMAX, 2 * self.cfg.inter, dtype=BF16, device=self.dev)
+            R.through(L["post_norm"], gu, self.gu[:n], lin)
+            _C.swiglu(self.gu[:n], self.act[:n])
+        R.owe(self.act[:n], L["down"], lin)
+
+    def _greedy(self, logits, n, out, idmap=None):
+        """Greedy token per row, lowest id on ties; vocabulary shards exchange (value, id)."""
         ws_v, ws_i = self.am_v[:n * 256], self.am_i[:n * 256]
         if self.tp is None:
             _C.argmax(logits, ws_v, ws_i, out, idmap)
@@ -252,269 +432,271 @@ class Engine:
         else:
             self.tp.exchange_argmax(self.cand_v, self.cand_i, n, out)
 
-    def _layer(self, L, n, h, eps, first, pos, lin=None):
-        """One decoder layer on rows h[:n]; the previous sub-layer's output in self.mo is added by
-        this layer's first norm unless `first`."""
-        cfg, lin = self.cfg, lin or self.linear
-        xn = self.xn[:n]
-        self._norm(h, not first, L["in_norm"], xn, eps, n)
-        if L["type"] == "linear_attention":
-            pr = self.proj[:n, :cfg.gdn_proj_rows]
-            lin(xn, L["in_proj"], pr)
-            c0, c1 = cfg.conv_dim, cfg.conv_dim + cfg.value_dim
-            out = self.mix[:n, :cfg.value_dim]
-            _C.gdn_step_n(pr[:, :c0], pr[:, c0:c1], pr[:, c1:c1 + cfg.hv], pr[:, c1 + cfg.hv:], L["ring"],
-                          L["conv_w"], L["A_log"], L["dt_bias"], L["norm_w"], L["S"], L["st_k"],
-                          L["st_v"], L["st_g"], self.ctl, out, cfg.hk, eps, q=self.GDN_Q)
-        else:
-            pr = self.proj[:n, :cfg.attn_proj_rows]
-            lin(xn, L["in_proj"], pr)
-            q0 = cfg.hq * 2 * cfg.head_dim
-            k1 = q0 + cfg.hkv * cfg.head_dim
-            qg, q = pr[:, :q0], self.q[:n]
-            _C.attn_prep(qg, pr[:, q0:k1], pr[:, k1:], L["q_norm"], L["k_norm"], self.inv_freq, pos, q,
-                         L["kc"], L["vc"], eps)
-            out = self.mix[:n, :cfg.hq * cfg.head_dim]
-            _C.attn_decode(q, L["kc"], L["vc"], pos, qg, self.part_o, self.part_ml, out)
-        self._ksplit(out, L["out"], n, lin)
-        self._norm(h, True, L["post_norm"], xn, eps, n)
-        if L.get("fused_swiglu", False):
-            lin.gate_up(xn, L["gate_up"], self.act[:n])
-        else:
-            lin(xn, L["gate_up"], self.gu[:n])
-            _C.swiglu(self.gu[:n], self.act[:n])
-        self._ksplit(self.act[:n], L["down"], n, lin)
-
-    def _main(self, n, force=False):
-        eps, k = self.cfg.eps, n - 1
-        h = self.h[:n]
-        # The first kernel of a pass is launched in plain stream order: it starts only after the
-        # previous pass has fully finished, so everything that pass wrote (pos, pending, state,
-        # checkpoints) is safe to read even from the early sections of this pass's kernels.
-        _C.set_pdl_launch(False)
+    def _trunk(self, n, force, then_commit_k=None):
+        """The main model on the n rows of in_tok: logits, greedy tokens, acceptance (and, for a
+        pass without draft rows, the commit in the same kernel)."""
+        R = _Residual(self, n, self.h, self.h2, self.xn)
+        ordered = True
         if force:
-            _C.force_drafts(self.in_tok, self.ctl, self.truth, self.force_a, k, self.vocab_full)
-            _C.set_pdl_launch(True)
-            _C.embed(self.embed, self.in_tok, h)
+            with self._ordered_first_launch():
+                _C.force_drafts(self.in_tok, self.ctl, self.truth, self.force_a, n - 1, self.vocab_full)
+            ordered = False
+        ordered = R.start_from_tokens(self.in_tok, ordered)
+        for L in self.layers:
+            self._block(L, R, self.ctl, ordered=ordered)
+            ordered = False
+        R.through(self.final_norm, self.lm_head, self.logits[:n], self.lm_lin, keep_normed=self.hid[:n])
+        self._greedy(self.logits[:n], n, self.am)
+        if then_commit_k is None:
+            _C.accept(self.in_tok, self.am, n, self.ctl, self.next_tok, self.log)
         else:
-            _C.embed(self.embed, self.in_tok, h)
-            _C.set_pdl_launch(True)
-        for i, L in enumerate(self.layers):
-            self._layer(L, n, h, eps, i == 0, self.ctl)
-        self._norm(h, True, self.final_norm, self.hid[:n], eps, n)
-        self.lm_lin(self.hid[:n], self.lm_head, self.logits[:n])
-        self._argmax(self.logits[:n], n, self.am)
-        _C.accept(self.in_tok, self.am, n, self.ctl, self.next_tok, self.log)
+            _C.accept_commit(self.in_tok, self.am, n, self.ctl, self.next_tok, self.log, self.drafts, then_commit_k)
 
-    def _mtp(self, n, hid, tok):
-        """MTP rows: hid [n, H] (after the final norm), tok int32 next tokens, positions mpos + r.
-        Output: self.mout[:n] (after mtp.norm) and self.mtp_am[:n] (draft tokens)."""
-        M, eps, H = self.mtp, self.cfg.eps, self.cfg.hidden
-        mh, cat = self.mh[:n], self.cat[:n]
-        _C.embed(self.embed, tok, mh)
-        _C.rmsnorm1p(mh, None, M["pre_e"], cat[:, :H], eps)
-        _C.rmsnorm1p(hid, None, M["pre_h"], cat[:, H:], eps)
+    def _draft_rows(self, n, hid, tok):
+        """MTP rows: hid [n, H] (main model, after its final norm) and the tokens that follow
+        them, at positions mpos + r. Leaves the draft layer's normed output in self.mout[:n] and
+        the drafted tokens in self.mtp_am[:n] (reference python/qengine/engine.py:479-496)."""
+        M, c, H = self.mtp, self.cfg, self.cfg.hidden
+        cat = self.cat[:n]
+        R = _Residual(self, n, self.mh, self.mh2, self.xn)
+        _C.embed(self.embed, tok, R.h)
+        _C.rmsnorm1p(R.h, None, M["pre_e"], cat[:, :H], c.eps)
+        _C.rmsnorm1p(hid, None, M["pre_h"], cat[:, H:], c.eps)
+        R.start_from_rows()
         if self.tp is None:
-            self.linear(cat, M["fc"], mh)
-        else:  # this rank's slice of [e | h]; the summed fc rows are added to a zeroed residual
+            self.linear(cat, M["fc"], R.h)
+        else:  # fc is split along K: this rank multiplies its slice of [e | h]
             w = 2 * H // self.tp.size
-            self._ksplit(cat[:, self.tp.rank * w:(self.tp.rank + 1) * w], M["fc"], n, self.linear)
-            mh.zero_()
-        self._layer(M, n, mh, eps, self.tp is None, self.mpos)
-        self._norm(mh, True, M["norm"], self.mout[:n], eps, n)
+            R.zero_then_owe(cat[:, self.tp.rank * w:(self.tp.rank + 1) * w], M["fc"], self.linear)
+        self._block(M, R, self.mpos)
         if self.draft_head is not None:
             lg = self.logits[:n, :self.draft_ids.numel()]
-            self.lm_lin(self.mout[:n], self.draft_head, lg)
-            self._argmax(lg, n, self.mtp_am, self.draft_ids)
+            R.through(M["norm"], self.draft_head, lg, self.lm_lin, keep_normed=self.mout[:n])
+            self._greedy(lg, n, self.mtp_am, self.draft_ids)
         else:
-            self.lm_lin(self.mout[:n], self.lm_head, self.logits[:n])
-            self._argmax(self.logits[:n], n, self.mtp_am)
+            R.through(M["norm"], self.lm_head, self.logits[:n], self.lm_lin, keep_normed=self.mout[:n])
+            self._greedy(self.logits[:n], n, self.mtp_am)
 
     def _pass(self, n, mtp_rows, k, force=False):
-        """Graph body: main pass on n rows; optionally MTP over the n rows (fills the MTP cache and
-        gives draft 1 from the last kept row) and k - 1 chained drafts; then commit."""
-        self._main(n, force)
-        if mtp_rows:
-            _C.mtp_select(self.ctl, self.mpos, -1)
-            self._mtp(n, self.hid[:n], self.next_tok)
-            if k > 0:
-                _C.mtp_select(self.ctl, self.mpos, 0, self.mout[:n], self.chain_h, self.mtp_am, self.drafts[:1])
-            for j in range(1, k):
-                if j > 1:
-                    _C.mtp_select(self.ctl, self.mpos, j - 1)
-                self._mtp(1, self.chain_h, self.drafts[j - 1:j])
-                self.drafts[j:j + 1].copy_(self.mtp_am[:1])
-                self.chain_h.copy_(self.mout[:1])
+        """Everything one graph replay does: the trunk on n rows; with mtp_rows the draft layer on
+        the same n rows (which fills its K/V cache and yields draft 1 from the last kept row) and
+        k - 1 chained single-row drafts; commit."""
+        if not mtp_rows:
+            self._trunk(n, force, then_commit_k=k)
+            return
+        self._trunk(n, force)
+        stream = torch.cuda.current_stream().cuda_stream
+        if self.l2_win:
+            lib.qe_stream_access_window(self.l2_win[0], self.l2_win[1], 1.0, stream)
+        _C.mtp_select(self.ctl, self.mpos, -1)
+        self._draft_rows(n, self.hid[:n], self.next_tok)
+        if k > 0:
+            _C.mtp_select(self.ctl, self.mpos, 0, self.mout[:n], self.chain_h, self.mtp_am, self.drafts[:1])
+        for j in range(1, k):
+            if j > 1:
+                _C.mtp_select(self.ctl, self.mpos, j - 1)
+            self._draft_rows(1, self.chain_h, self.drafts[j - 1:j])
+            _C.chain_draft(self.mtp_am, self.drafts[j:j + 1], self.mout[:1], self.chain_h)
+        if self.l2_win:
+            lib.qe_stream_access_window(0, 0, 0.0, stream)
         _C.commit(self.ctl, self.in_tok, self.am, self.drafts, k)
 
+    # -- graphs ----------------------------------------------------------------------------------
     def graph(self, n, mtp_rows=False, k=0, force=False):
-        """CUDA graph of one pass variant, captured on first use. Capturing runs the body once
-        eagerly (which also sizes the W4 workspace) and changes the sequence state: call reset()."""
+        """The CUDA graph of one pass variant, captured on first use. The body first runs once
+        eagerly (this sizes the W4 scratch, which may not grow during capture) on a side stream;
+        both runs advance the sequence state, so callers reset() afterwards."""
         key = (n, mtp_rows, k, force)
-        assert 1 <= n <= NMAX and (not mtp_rows or self.has_mtp)
-        if key not in self.graphs:
-            s = torch.cuda.Stream()
-            s.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(s):
+        if not (1 <= n <= NMAX) or (mtp_rows and not self.has_mtp):
+            raise ValueError(f"no such pass: {key}")
+        if key in self.graphs:
+            return self.graphs[key]
+        _C.set_gdn_early(True)  # safe inside a pass: see _ordered_first_launch
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
                 self._pass(n, mtp_rows, k, force)
-            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            before = launches[0]
-            # with collectives in the graph, other threads of the process group must stay free to
-            # make CUDA calls during capture
-            mode = "global" if self.tp is None else "thread_local"
-            with torch.cuda.graph(g, capture_error_mode=mode):
+            count0 = launches[0]
+            # a process group's watchdog thread makes CUDA calls of its own during capture
+            with torch.cuda.graph(g, capture_error_mode="global" if self.tp is None else "thread_local"):
                 self._pass(n, mtp_rows, k, force)
             torch.cuda.synchronize()
-            self.graphs[key] = g
-            self.graph_kernels[key] = launches[0] - before
-        return self.graphs[key]
+        finally:
+            _C.set_gdn_early(False)
+        self.graphs[key] = g
+        self.graph_kernels[key] = launches[0] - count0
+        return g
 
-    # ------------------------------------------------------------------------------------------
+    def _need(self, keys):
+        fresh = [key for key in keys if key not in self.graphs]
+        for key in fresh:
+            self.graph(*key)
+        if fresh:
+            self.reset()
+
     @staticmethod
-    def _chunks(seq, size):
+    def _split(seq, size):
         return [seq[i:i + size] for i in range(0, len(seq), size)]
 
     def _prefill_keys(self, P, mtp, k, chunk=NMAX):
-        sizes = [len(c) for c in self._chunks(list(range(P)), chunk)]
-        keys = {(s, mtp, 0, False) for s in sizes[:-1]}
-        keys.add((sizes[-1], mtp, k, False))
-        return keys
+        """Graph keys a prompt of P tokens needs: full chunks, and the last one carrying k."""
+        sizes = [len(c) for c in self._split(range(P), chunk)]
+        return {(s, mtp, 0, False) for s in sizes[:-1]} | {(sizes[-1], mtp, k, False)}
 
-    def _ensure(self, keys):
-        new = [k for k in keys if k not in self.graphs]
-        for key in new:
-            self.graph(*key)
-        if new:
-            self.reset()
+    def _feed(self, tokens, follow):
+        """Host -> device: the rows of the next pass and the token after them (-1: none)."""
+        row = torch.full((NMAX + 1,), -1, dtype=I32)
+        row[:len(tokens)] = torch.tensor(list(tokens), dtype=I32)
+        row[len(tokens)] = follow
+        self.in_tok.copy_(row)
 
+    def _check_device_errors(self):
+        """Bounded waits in the kernels report through sticky error words instead of hanging. Read
+        them where the host synchronises anyway; a set word means the tokens are not to be trusted."""
+        bad = []
+        if _w4.ring_error():
+            bad.append("W4 weight ring: a bulk copy did not complete")
+            _w4.clear_error()
+            _w4.reset_workspaces()
+        if _C.attn_error():
+            bad.append("attention K/V ring: a bulk copy did not complete")
+        if self.tp is not None:
+            err = self.tp.error()
+            if err:
+                bad.append(f"tensor-parallel exchange: rank {err['late_rank']} was late ({err['kind']}, row {err['row']})")
+        if bad:
+            raise RuntimeError("decode aborted: " + "; ".join(bad))
+
+    # -- public loops ---------------------------------------------------------------------------
     def prefill(self, prompt, mtp=False, k=0, chunk=NMAX):
-        """Feed the prompt in passes of `chunk` rows. The last row's argmax is the first generated
-        token (log[len(prompt)]); with mtp/k the drafts for the first verify are ready. Leaves the
-        engine in decode/verify mode. Assumes reset() and existing graphs."""
-        chunks = self._chunks(prompt, chunk)
+        """Feed the prompt `chunk` rows per pass. The last row's greedy token is the first
+        generated token (log[len(prompt)]); with mtp / k the drafts of the first verify pass are
+        ready afterwards. Leaves the engine in decode / verify mode. Expects reset() and captured
+        graphs (`generate*` take care of both)."""
+        pieces = self._split(list(prompt), chunk)
         self.ctl[self.MODE].fill_(0)
-        buf = torch.full((NMAX + 1,), -1, dtype=I32)
-        for ci, c in enumerate(chunks):
-            last = ci == len(chunks) - 1
-            buf.fill_(-1)
-            buf[:len(c)] = torch.tensor(c, dtype=I32)
-            if not last:
-                buf[len(c)] = chunks[ci + 1][0]
-            self.in_tok.copy_(buf)
-            self.graph(len(c), mtp, k if last else 0).replay()
+        for i, piece in enumerate(pieces):
+            last = i == len(pieces) - 1
+            self._feed(piece, -1 if last else pieces[i + 1][0])
+            self.graph(len(piece), mtp, k if last else 0).replay()
         self.ctl[self.MODE].fill_(1)
 
     @torch.no_grad()
     def generate(self, prompt, n_new, timing=False, chunk=NMAX):
-        """Plain greedy: prefill, then n_new - 1 one-row passes. Returns n_new token ids
-        (timing=True adds prefill_s, decode_s)."""
-        P, P0 = len(prompt), self.start_pos + len(prompt)
-        assert P0 + n_new + 1 <= self.max_len
-        self._ensure(self._prefill_keys(P, False, 0, chunk) | {(1, False, 0, False)})
+        """Plain greedy decoding: prefill, then n_new - 1 single-row passes. Returns the n_new token
+        ids; timing=True returns (tokens, prefill seconds, decode seconds)."""
+        P = len(prompt)
+        first = self.start_pos + P
+        if first + n_new + 1 > self.max_len:
+            raise ValueError("sequence does not fit max_len")
+        step_key = (1, False, 0, False)
+        self._need(self._prefill_keys(P, False, 0, chunk) | {step_key})
         self.reset()
-        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        e0.record()
+        t = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        t[0].record()
         self.prefill(prompt, chunk=chunk)
-        e1.record()
-        g = self.graphs[(1, False, 0, False)]
+        t[1].record()
+        step = self.graphs[step_key]
         for _ in range(n_new - 1):
-            g.replay()
-        e2.record()
+            step.replay()
+        t[2].record()
         torch.cuda.synchronize()
-        gen = self.log[P0:P0 + n_new].tolist()
-        if timing:
-            return gen, e0.elapsed_time(e1) / 1e3, e1.elapsed_time(e2) / 1e3
-        return gen
+        self._check_device_errors()
+        out = self.log[first:first + n_new].tolist()
+        return (out, t[0].elapsed_time(t[1]) / 1e3, t[1].elapsed_time(t[2]) / 1e3) if timing else out
 
     @torch.no_grad()
     def generate_spec(self, prompt, n_new, k, timing=False, chunk=NMAX, force_accept=None, truth=None):
-        """Greedy speculative decoding with k MTP drafts per cycle (verify n = k + 1 rows). Output
-        equals `generate` token for token. force_accept = a (0..k) with truth = prompt + known
-        greedy continuation replaces the drafts before every verify so that exactly `a` are
-        accepted (measurement harness). timing=True adds prefill_s, decode_s and a stats dict."""
-        assert self.has_mtp and 1 <= k <= NMAX - 1
-        P, P0 = len(prompt), self.start_pos + len(prompt)
-        assert P0 + n_new + 2 * NMAX + 2 <= self.max_len
-        force = force_accept is not None
-        if force:
-            assert truth is not None and 0 <= force_accept <= k
-            # indexed by absolute position
-            self.truth = torch.tensor([0] * self.start_pos + list(truth), dtype=I32, device=self.dev)
+        """Greedy speculative decoding with k MTP drafts per cycle (verify over k + 1 rows). The
+        output equals `generate` token for token. force_accept = a (0..k) together with truth =
+        prompt + known greedy continuation overwrites the drafts before every verify so that
+        exactly `a` are accepted (measurement harness). timing=True returns (tokens, prefill s,
+        decode s, stats)."""
+        if not self.has_mtp or not 1 <= k <= NMAX - 1:
+            raise ValueError("speculative decoding needs the MTP layer and 1 <= k <= 7")
+        P = len(prompt)
+        first = self.start_pos + P
+        if first + n_new + 2 * NMAX + 2 > self.max_len:
+            raise ValueError("sequence does not fit max_len")
+        forced = force_accept is not None
+        if forced:
+            if truth is None or not 0 <= force_accept <= k:
+                raise ValueError("force_accept needs truth and 0 <= a <= k")
+            self.truth = torch.tensor([0] * self.start_pos + list(truth), dtype=I32, device=self.dev)  # by position
             self.force_a = int(force_accept)
-            self.graphs.pop((k + 1, True, k, True), None)  # truth buffer address changed
-        self._ensure(self._prefill_keys(P, True, k, chunk) | {(k + 1, True, k, force)})
+            self.graphs.pop((k + 1, True, k, True), None)  # the graph holds the old truth buffer
+        cycle_key = (k + 1, True, k, forced)
+        self._need(self._prefill_keys(P, True, k, chunk) | {cycle_key})
         self.reset()
-        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        e0.record()
+        t = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        t[0].record()
         self.prefill(prompt, mtp=True, k=k, chunk=chunk)
         self.ctl[self.CYCLES:self.ACCEPTED + 1].zero_()
         self.ctl[16:].zero_()
-        e1.record()
-        g = self.graphs[(k + 1, True, k, force)]
-        target = P0 + n_new - 1
-        pos = P0
-        while pos < target:
-            for _ in range(max(1, (target - pos) // (k + 1))):
-                g.replay()
-            pos = int(self.ctl[self.POS].item())  # the only host sync: once per batch of cycles
-        e2.record()
+        t[1].record()
+        cycle = self.graphs[cycle_key]
+        goal, pos = first + n_new - 1, first
+        while pos < goal:
+            # every cycle yields at least one token and at most k + 1: replay as many as cannot
+            # overshoot, then look at the position (the only host sync of the loop)
+            for _ in range(max(1, (goal - pos) // (k + 1))):
+                cycle.replay()
+            pos = int(self.ctl[self.POS].item())
+        t[2].record()
         torch.cuda.synchronize()
-        gen = self.log[P0:P0 + n_new].tolist()
+        self._check_device_errors()
+        out = self.log[first:first + n_new].tolist()
         if not timing:
-            return gen
+            return out
         c = self.ctl.tolist()
-        stats = {"cycles": c[self.CYCLES], "accepted": c[self.ACCEPTED],
-                 "accept_rate": c[self.ACCEPTED] / max(1, c[self.CYCLES] * k),
-                 "tokens_per_cycle": 1 + c[self.ACCEPTED] / max(1, c[self.CYCLES]),
-                 "hist": c[16:16 + k + 1]}
-        return gen, e0.elapsed_time(e1) / 1e3, e1.elapsed_time(e2) / 1e3, stats
+        cycles, kept, hist = c[self.CYCLES], c[self.ACCEPTED], c[16:16 + k + 1]
+        reach = [sum(hist[d:]) for d in range(k + 1)]  # cycles that kept at least d drafts
+        stats = {"cycles": cycles, "accepted": kept, "accept_rate": kept / max(1, cycles * k),
+                 "tokens_per_cycle": 1 + kept / max(1, cycles), "hist": hist,
+                 "accept_by_depth": [reach[d] / max(1, reach[d - 1]) for d in range(1, k + 1)]}
+        return out, t[0].elapsed_time(t[1]) / 1e3, t[1].elapsed_time(t[2]) / 1e3, stats
 
     @torch.no_grad()
     def sequence_logits(self, seq, keep="full", chunk=NMAX):
-        """Teacher forcing: feed `seq` in prefill passes; per-position logits [T, V] bf16
-        (keep='full') or argmax ids [T] (keep='argmax')."""
-        T = len(seq)
-        chunks = self._chunks(seq, chunk)
-        self._ensure({(len(c), False, 0, False) for c in chunks})
+        """Teacher forcing: `seq` goes through prefill passes; returns the logits of every position
+        [T, V] bf16 (keep='full') or their argmax [T] (keep='argmax')."""
+        pieces = self._split(list(seq), chunk)
+        self._need({(len(p), False, 0, False) for p in pieces})
         self.reset()
         full = keep == "full"
-        out = torch.empty((T, self.cfg.vocab) if full else (T,), dtype=BF16 if full else I32, device=self.dev)
+        out = torch.empty((len(seq), self.cfg.vocab) if full else (len(seq),), dtype=BF16 if full else I32,
+                          device=self.dev)
         self.ctl[self.MODE].fill_(0)
-        buf = torch.full((NMAX + 1,), -1, dtype=I32)
-        for ci, c in enumerate(chunks):
-            buf.fill_(-1)
-            buf[:len(c)] = torch.tensor(c, dtype=I32)
-            if ci + 1 < len(chunks):
-                buf[len(c)] = chunks[ci + 1][0]
-            self.in_tok.copy_(buf)
-            self.graph(len(c), False, 0).replay()
-            o = ci * chunk
-            out[o:o + len(c)].copy_(self.logits[:len(c)] if full else self.am[:len(c)])
+        at = 0
+        for i, piece in enumerate(pieces):
+            self._feed(piece, pieces[i + 1][0] if i + 1 < len(pieces) else -1)
+            self.graph(len(piece), False, 0).replay()
+            out[at:at + len(piece)].copy_(self.logits[:len(piece)] if full else self.am[:len(piece)])
+            at += len(piece)
         torch.cuda.synchronize()
+        self._check_device_errors()
         return out
 
     @torch.no_grad()
     def mtp_rows_logits(self, seq):
-        """Validation helper: teacher-forced one-row passes with MTP rows on; returns (main hidden
-        after the final norm [T, H], MTP logits [T, V]); MTP row t uses the hidden at t and the
-        next token seq[t + 1] (the model's own argmax at the last position)."""
-        self._ensure({(1, True, 0, False)})
+        """Validation helper: teacher-forced single-row passes with the MTP rows on. Returns the
+        main model's hidden rows after the final norm [T, H] and the MTP logits [T, V]; MTP row t
+        sees the hidden row t and token seq[t + 1] (at the last position: the model's own choice)."""
+        self._need({(1, True, 0, False)})
         self.reset()
-        T, H = len(seq), self.cfg.hidden
-        hid = torch.empty(T, H, dtype=BF16, device=self.dev)
+        T = len(seq)
+        hid = torch.empty(T, self.cfg.hidden, dtype=BF16, device=self.dev)
         lg = torch.empty(T, self.cfg.vocab, dtype=BF16, device=self.dev)
         self.ctl[self.MODE].fill_(0)
-        buf = torch.full((NMAX + 1,), -1, dtype=I32)
         for t in range(T):
-            buf.fill_(-1)
-            buf[0] = seq[t]
-            if t + 1 < T:
-                buf[1] = seq[t + 1]
-            self.in_tok.copy_(buf)
+            self._feed([seq[t]], seq[t + 1] if t + 1 < T else -1)
             self.graph(1, True, 0).replay()
             hid[t].copy_(self.hid[0])
             lg[t].copy_(self.logits[0])
         torch.cuda.synchronize()
+        self._check_device_errors()
         return hid, lg

@@ -49,5 +49,5 @@ def test_struct_layouts_match_header():
 
 def test_abi_version_and_plan_without_gpu():
     from qengine_b200 import _lib
-    assert _lib.lib.qe_abi_version() == 1
+    assert _lib.lib.qe_abi_version() == 2
     assert _lib.lib.qe_w4_auto_ksplit(5120, 17408, 1, 8) == 1

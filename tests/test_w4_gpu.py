@@ -22,13 +22,21 @@ SHAPES_27B = {
     "attn.k/v_proj": (1024, H), "attn.in_proj_fused": (14336, H), "attn.o_proj": (H, 6144),
     "mlp.gate/up_proj": (I, H), "mlp.down_proj": (H, I), "lm_head": (V, H), "mtp.fc": (H, 2 * H),
 }
+# per-rank shapes of the 27B model under tensor parallelism (rows x K): t = 2, 4, 8
+SHAPES_TP = {
+    "t2.gdn_in": (8240, H), "t2.attn_in": (7168, H), "t2.out": (H, 3072), "t2.down": (H, 8704),
+    "t4.gdn_in": (4120, H), "t4.attn_in": (3584, H), "t4.out": (H, 1536), "t4.down": (H, 4352),
+    "t8.gdn_in": (2060, H), "t8.attn_in": (2048, H), "t8.out": (H, 768), "t8.down": (H, 2176),
+    "t8.lm_head": (31040, H), "t8.gate_up_rows": (4352, H),
+}
 ODD_SHAPES = [(1, 1), (1, 128), (7, 127), (16, 129), (127, 1000), (1000, 4097), (33, 32768), (4097, 7),
               (17, 255), (100, 136)]
+# every launch option the boundary accepts (the reference's names); all map onto one kernel family
 CFGS = [dict(), dict(warps=4), dict(warps=16), dict(unroll=1), dict(unroll=4), dict(warps=16, unroll=1),
         dict(mode=0), dict(mode=0, ksplit=2), dict(mode=0, ksplit=7), dict(mode=2), dict(mode=2, min_units=1),
         dict(mode=2, warps=4, unroll=1), dict(variant=1), dict(pdl=False), dict(mode=3),
         dict(mode=3, blocks_per_sm=1, min_units=1), dict(mode=4), dict(mode=4, unroll=2, min_units=1),
-        dict(mode=4, unroll=1, blocks_per_sm=1)]
+        dict(mode=4, unroll=1, blocks_per_sm=1), dict(min_units=6), dict(min_units=64), dict(warps=8, min_units=2)]
 
 
 @pytest.fixture(scope="module")
@@ -92,6 +100,24 @@ def test_27b_shapes_all_row_counts(api, name):
     bnd = bound(x, Wd, ref)
     for N in range(1, 9):
         check(api["gemv"](x[:N].contiguous(), p), ref[:N], bnd[:N], f"{name} N={N}")
+
+
+@pytest.mark.parametrize("name", list(SHAPES_TP))
+def test_tensor_parallel_shard_shapes(api, name):
+    """The matrices a rank of a 2 / 4 / 8-way tensor-parallel engine multiplies with, at the
+    engine's own launch options (default, and min_units = 6)."""
+    M, K = SHAPES_TP[name]
+    p = api["q"](rand_w(M, K, seed=60))
+    Wd = api["deq"](p)
+    x = rand_x(8, K, seed=61)
+    ref = x.float() @ Wd.T
+    bnd = bound(x, Wd, ref)
+    for kw in (dict(), dict(min_units=6)):
+        one = bits(api["gemv"](x[:1].contiguous(), p, **kw))
+        for N in (1, 5, 8):
+            out = api["gemv"](x[:N].contiguous(), p, **kw)
+            check(out, ref[:N], bnd[:N], f"{name} N={N} {kw}")
+            assert torch.equal(bits(out[:1]), one), f"{name} N={N} {kw}: row 0 depends on N"
 
 
 @pytest.mark.parametrize("M,K", ODD_SHAPES)
@@ -273,8 +299,7 @@ def test_swiglu_bitwise_and_row_independent(api):
 
 @pytest.mark.parametrize("name", list(SHAPES_27B))
 def test_ring_mode_all_row_counts(api, name):
-    """Mode 3 (weights through the shared-memory ring) on every 27B shape; its bounded waits must
-    never expire."""
+    """Both ring geometries on every 27B shape; the bounded waits of the rings must never expire."""
     M, K = SHAPES_27B[name]
     p = api["q"](rand_w(M, K, seed=50))
     Wd = api["deq"](p)
@@ -295,3 +320,93 @@ def test_linearity_at_full_size(api):
     a = api["gemv"](x, p).float()
     b = api["gemv"]((x.float() * 2).to(torch.bfloat16), p).float()
     assert torch.equal(a * 2, b)
+
+
+# ---------------------------------------------------------------------------------------------
+# Fused prologue: residual add + RMSNorm1p (+ embedding gather) inside the GEMV launch
+# ---------------------------------------------------------------------------------------------
+def _norm_ref(h, delta, w, eps):
+    """bf16(h + delta) and the normed rows as the torch path computes them (fp32, one rounding)."""
+    hs = (h.float() + delta.float()).to(torch.bfloat16) if delta is not None else h
+    v = hs.float()
+    xn = (v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * (1.0 + w.float())).to(torch.bfloat16)
+    return hs, xn
+
+
+@pytest.mark.parametrize("M,K,gate_up", [(16480, H, False), (I, H, True), (4096, 512, False), (1536, 512, True),
+                                         (V // 8, H, False)])
+def test_fused_norm_prologue(api, M, K, gate_up):
+    from util import bf16_ulp_close
+    w4 = api["w4"]
+    p = api["qgu"](rand_w(M, K, seed=70), rand_w(M, K, seed=71)) if gate_up else api["q"](rand_w(M, K, seed=70))
+    g = torch.Generator(device=DEV).manual_seed(72)
+    h = torch.randn(8, K, generator=g, device=DEV).to(torch.bfloat16)
+    d = (torch.randn(8, K, generator=g, device=DEV) * 0.5).to(torch.bfloat16)
+    nw = (torch.randn(K, generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+    for delta in (d, None):
+        hs_ref, xn_ref = _norm_ref(h, delta, nw, 1e-6)
+        single = None
+        for N in (1, 2, 5, 7, 8):
+            out = torch.empty(N, M, dtype=torch.bfloat16, device=DEV)
+            h_out = torch.full((N, K), 3.0, dtype=torch.bfloat16, device=DEV)
+            xn = torch.empty(N, K, dtype=torch.bfloat16, device=DEV)
+            kw = dict(unroll=2) if N == 8 else {}
+            w4.gemv_fused(h[:N], None if delta is None else delta[:N], nw, 1e-6, p.qw, p.scales, out, M,
+                          h_out=h_out, xn_out=xn, swiglu=gate_up, **kw)
+            assert torch.equal(bits(h_out), bits(hs_ref[:N])), "residual stream rows"
+            ok, err = bf16_ulp_close(xn, xn_ref[:N], ulps=1)
+            assert ok, f"normed rows differ by more than 1 ulp ({err})"
+            # the product itself: exactly the unfused kernel on the kernel's own normed rows
+            want = api["gemv"](xn, p, **kw)
+            assert torch.equal(bits(out), bits(want)), f"N={N}: fused product differs from gemv(xn)"
+            if single is None:
+                single = bits(out[:1])
+            assert torch.equal(bits(out[:1]), single), f"N={N}: row 0 depends on N"
+    assert w4.ring_error() == 0
+
+
+def test_fused_prologue_gathers_embedding_rows(api):
+    w4 = api["w4"]
+    Vt, K, M = 1000, 512, 1552
+    p = api["q"](rand_w(M, K, seed=80))
+    g = torch.Generator(device=DEV).manual_seed(81)
+    table = torch.randn(Vt, K, generator=g, device=DEV).to(torch.bfloat16)
+    nw = (torch.randn(K, generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+    tok = torch.tensor([5, 999, -1, 1000, 0, 17, 3, 3, 42], dtype=torch.int32, device=DEV)  # two out of range
+    for N in (1, 4, 8):
+        rows = table[tok[:N].clamp(0, Vt - 1).long()].clone()
+        rows[(tok[:N] < 0) | (tok[:N] >= Vt)] = 0
+        _, xn_ref = _norm_ref(rows, None, nw, 1e-6)
+        out = torch.empty(N, M, dtype=torch.bfloat16, device=DEV)
+        h_out = torch.empty(N, K, dtype=torch.bfloat16, device=DEV)
+        xn = torch.empty(N, K, dtype=torch.bfloat16, device=DEV)
+        w4.gemv_fused(table, None, nw, 1e-6, p.qw, p.scales, out, M, tok=tok, h_out=h_out, xn_out=xn)
+        assert torch.equal(bits(h_out), bits(rows))
+        from util import bf16_ulp_close
+        assert bf16_ulp_close(xn, xn_ref, ulps=1)[0]
+        assert torch.equal(bits(out), bits(api["gemv"](xn, p)))
+
+
+def test_fused_prologue_rejects_what_it_cannot_serve(api):
+    w4 = api["w4"]
+    q = api["q"](rand_w(64, 1024, seed=83))
+    h = rand_x(1, 1024)
+    with pytest.raises(RuntimeError):  # h_out aliases h_in
+        w4.gemv_fused(h, h.clone(), rand_x(1, 1024)[0], 1e-6, q.qw, q.scales,
+                      torch.empty(1, 64, dtype=torch.bfloat16, device=DEV), 64, h_out=h)
+    big = api["q"](rand_w(64, H, seed=82))
+    with pytest.raises(RuntimeError):  # eight rows of 5120 do not fit beside the default ring geometry
+        w4.gemv_fused(rand_x(8, H), None, rand_x(1, H)[0], 1e-6, big.qw, big.scales,
+                      torch.empty(8, 64, dtype=torch.bfloat16, device=DEV), 64)
+    with pytest.raises(RuntimeError):  # width of h must be the padded K of the matrix
+        w4.gemv_fused(rand_x(1, 512), None, rand_x(1, 512)[0], 1e-6, q.qw, q.scales,
+                      torch.empty(1, 64, dtype=torch.bfloat16, device=DEV), 64)
+
+
+def test_prefetch_hint_changes_nothing(api):
+    p = api["q"](rand_w(5120, 6144, seed=84))
+    nxt = api["q"](rand_w(2048, 5120, seed=85))
+    x = rand_x(3, 6144, seed=86)
+    a = api["gemv"](x, p)
+    b = api["gemv"](x, p, prefetch=nxt.qw)
+    assert torch.equal(bits(a), bits(b))
