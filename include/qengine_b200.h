@@ -229,8 +229,9 @@ typedef struct qe_w4_params {
  * One kernel family serves every shape, so most of them only steer its geometry; every accepted
  * combination is deterministic and independent of N. */
 typedef struct qe_w4_cfg {
-  int warps;         /* warps per block: 0 (auto) / 16 -> 16, 4 / 8 -> 8 */
-  int unroll;        /* weight units (1 KB) per ring stage: 0 / 4 -> 2 stages of 4, 1 / 2 -> 3 stages of 2 */
+  int warps;         /* warps per block: 0 (auto) -> 20, 16 -> 16, 4 / 8 -> 8 */
+  int unroll;        /* ring of 1-KB weight units per warp: 0 / 2 -> 3 stages of 2, 4 -> 2 stages of 4,
+                        1 -> 2 stages of 2 (never changes the result) */
   int ksplit;        /* > 0: at least this many warps share a 16-row tile; 0 = by min_units */
   int pdl;           /* launch with programmatic stream serialization */
   int variant;       /* 1: 24 warps per block; other values: as `warps` says */
@@ -284,6 +285,19 @@ int qe_w4_auto_ksplit(int Mp, int Kp, int N, int warps);
 int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
 /* qe_w4_gemv with the fused prologue / prefetch hint described at qe_w4_norm (nrm may be NULL). */
 int qe_w4_gemv_ex(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg, void* stream);
+/* Up to QE_W4_MAX_CHAIN GEMVs that depend on one another only through device memory (the output
+ * of one is the input or the residual update of the next) as ONE cooperative launch: job j + 1
+ * starts after a grid-wide barrier that follows job j, and every warp requests the head of its
+ * slab of the next matrix before it reaches the barrier, so the memory pipeline does not drain
+ * between the jobs the way it does between two kernel launches. Same results, bit for bit, as the
+ * same calls made one by one with the same cfg. All jobs use `cfg`; p[j]->ws / counters must cover
+ * the largest plan of the chain (they are reused job after job). gridbar: two int32 words in
+ * device memory, zero before the first use, owned by the library afterwards (one pair per stream
+ * of launches). nrm may be NULL, and so may any nrm[j]. njobs == 1 is qe_w4_gemv_ex. No
+ * counterpart in the reference, which launches every GEMV separately. */
+#define QE_W4_MAX_CHAIN 4
+int qe_w4_gemv_chain(const qe_w4_params* const* p, const qe_w4_norm* const* nrm, int njobs,
+                     const qe_w4_cfg* cfg, int* gridbar, void* stream);
 /* Has no counterpart in the reference. The same GEMV as qe_w4_gemv for callers that cannot
  * allocate device memory (a plugin inside another runtime's callback, code running between the
  * capture and the replay of a graph, an embedder that may not call its allocator): p->ws and

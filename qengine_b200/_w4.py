@@ -9,7 +9,8 @@ libqengine_b200.so through ctypes.
 
 Additions without a counterpart in the reference: `gemv_partial` (fp32 partial sums of a matrix
 split along K over tensor-parallel ranks), `gemv_fused` (the GEMV with the residual add + RMSNorm
-that produces its input fused into the launch) and `gemv_static` (no allocation).
+that produces its input fused into the launch), `gemv_chain` (several dependent GEMVs as one
+cooperative launch) and `gemv_static` (no allocation).
 
 Workspace: like the reference binding (gemv_w4_bind.cpp:12-22, 71-79) a per-device, grow-only
 pair of buffers is kept here -- fp32 partial-sum slots (contents irrelevant) and int32 arrival
@@ -31,7 +32,7 @@ _MIN_WS_FLOATS, _MIN_COUNTERS = 1 << 18, 1 << 14
 
 class _Workspace:
     def __init__(self):
-        self.keep, self.ws, self.counters = [], None, None
+        self.keep, self.ws, self.counters, self.gbar = [], None, None, None
 
 
 _per_device: dict[int, _Workspace] = {}
@@ -89,25 +90,48 @@ def _cfg(warps, unroll, ksplit, pdl, variant, mode, bps, min_units):
                  int(min_units))
 
 
-def _launch(p, cfg, nrm, dev, what):
-    plan = W4Plan()
-    check(lib.qe_w4_plan_gemv(C.byref(p), C.byref(cfg), C.byref(plan)), f"{what} plan", kernels=0)
-    W = _workspace(dev, plan.ws_floats, plan.counters)
-    p.ws, p.counters = W.ws.data_ptr(), W.counters.data_ptr()
+class Job:
+    """One GEMV of a chain: the C structs plus the tensors they point into (kept alive)."""
+    __slots__ = ("p", "nrm", "dev", "keep")
+
+    def __init__(self, p, nrm, dev, keep):
+        self.p, self.nrm, self.dev, self.keep = p, nrm, dev, keep
+
+
+def _launch(jobs, cfg, what):
+    """Launch 1..4 jobs as one kernel (qe_w4_gemv_chain); scratch sized for the largest plan."""
+    dev = jobs[0].dev
+    ws_floats = counters = 0
+    for j in jobs:
+        plan = W4Plan()
+        check(lib.qe_w4_plan_gemv(C.byref(j.p), C.byref(cfg), C.byref(plan)), f"{what} plan", kernels=0)
+        ws_floats, counters = max(ws_floats, plan.ws_floats), max(counters, plan.counters)
+    W = _workspace(dev, ws_floats, counters)
+    for j in jobs:
+        j.p.ws, j.p.counters = W.ws.data_ptr(), W.counters.data_ptr()
     stream = torch.cuda.current_stream().cuda_stream
-    if nrm is None:
-        code = lib.qe_w4_gemv(C.byref(p), C.byref(cfg), stream)
+    n = len(jobs)
+    if n == 1 and jobs[0].nrm is None:
+        code = lib.qe_w4_gemv(C.byref(jobs[0].p), C.byref(cfg), stream)
+    elif n == 1:
+        code = lib.qe_w4_gemv_ex(C.byref(jobs[0].p), C.byref(jobs[0].nrm), C.byref(cfg), stream)
     else:
-        code = lib.qe_w4_gemv_ex(C.byref(p), C.byref(nrm), C.byref(cfg), stream)
+        if W.gbar is None:
+            _req(not torch.cuda.is_current_stream_capturing(), "run the chain once eagerly before capturing it")
+            W.gbar = torch.zeros(2, dtype=torch.int32, device=dev)
+        ps = (C.POINTER(W4Params) * n)(*[C.pointer(j.p) for j in jobs])
+        ns = (C.POINTER(W4Norm) * n)(*[C.pointer(j.nrm) if j.nrm is not None else C.POINTER(W4Norm)() for j in jobs])
+        code = lib.qe_w4_gemv_chain(ps, ns, n, C.byref(cfg), W.gbar.data_ptr(), stream)
     _req(code != -22, f"{what}: argument combination not supported by the kernel")
     _req(code == 0, f"{what} launch failed: CUDA error {code}")
     launches[0] += 1
 
 
-def _run(x, qw, scales, out, M, epilogue, warps, unroll, ksplit, pdl, variant, mode, bps, min_units,
-         allow_f32_out=False, prefetch=None):
+def job(x, qw, scales, out, M, swiglu=False, prefetch=None, allow_f32_out=False) -> Job:
+    """Describe out = x @ W~^T (or the SwiGLU of a gate/up pack) without launching it."""
     for t in (x, qw, scales, out):
         _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
+    epilogue = EPI_SWIGLU if swiglu else EPI_NONE
     out_f32 = allow_f32_out and out.dtype == torch.float32 and epilogue == EPI_NONE
     _req(x.dtype == torch.bfloat16, "x must be bf16 (W4A16 kernel)")
     _req(out.dtype == torch.bfloat16 or out_f32, "out must be bf16")
@@ -124,50 +148,19 @@ def _run(x, qw, scales, out, M, epilogue, warps, unroll, ksplit, pdl, variant, m
     else:
         _req(Mp - 16 < M <= Mp, "out width M must match packed rows")
     _req(x.data_ptr() != out.data_ptr(), "in-place not supported")
-    cfg = _cfg(warps, unroll, ksplit, pdl, variant, mode, bps, min_units)
     p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None,
                  M, K, Mp, Kp, N, x.stride(0), out.stride(0), epilogue, int(out_f32))
     nrm = None
     if prefetch is not None:  # L2 hint only: no prologue
         nrm = W4Norm()
         nrm.prefetch, nrm.prefetch_bytes = prefetch.data_ptr(), prefetch.numel() * prefetch.element_size()
-    _launch(p, cfg, nrm, x.device, "gemv_w4")
+    return Job(p, nrm, x.device, (x, qw, scales, out, prefetch))
 
 
-def gemv(x, qw, scales, out, M, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
-         blocks_per_sm=0, min_units=4, prefetch=None):
-    """out[N, M] = x[N, K] @ W~^T (W packed by quant.quantize_w4). prefetch (not in the reference):
-    a tensor whose bytes a later kernel will stream; the launch asks L2 for them before it waits
-    for its own input."""
-    _run(x, qw, scales, out, M, EPI_NONE, warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm,
-         min_units, prefetch=prefetch)
-
-
-def gemv_swiglu(x, qw, scales, out, I, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
-                blocks_per_sm=0, min_units=4):
-    """out[N, I] = silu(x @ Wg^T) * (x @ Wu^T) (packed by quant.quantize_w4_gate_up)."""
-    _run(x, qw, scales, out, I, EPI_SWIGLU, warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm,
-         min_units)
-
-
-def gemv_partial(x, qw, scales, out32, M, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
-                 blocks_per_sm=0, min_units=4):
-    """Not in the reference: `out32` is fp32 [N, M] and receives the unrounded sums -- one rank's
-    partial result of a matrix split along K over tensor-parallel ranks."""
-    _req(out32.dtype == torch.float32, "out32 must be fp32")
-    _run(x, qw, scales, out32, M, EPI_NONE, warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm,
-         min_units, allow_f32_out=True)
-
-
-def gemv_fused(h_in, delta, norm_w, eps, qw, scales, out, M, *, h_out=None, xn_out=None, tok=None,
-               swiglu=False, prefetch=None, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
-               blocks_per_sm=0, min_units=4):
-    """Not in the reference: out = gemv(RMSNorm1p(h_in + delta) * (1 + norm_w)) in one launch.
-
-    h_in bf16 [N, K]; delta bf16 [N, K] or None; h_out (optional, must not alias h_in) receives
-    bf16(h_in + delta) and xn_out (optional) the normed rows. With `tok` (int32 [>= N]) h_in is an
-    embedding table [V, K] and row r is table[tok[r]]. `prefetch` = a tensor whose bytes a later
-    kernel will stream (an L2 hint). Same arithmetic as `_C.rmsnorm1p` followed by `gemv`."""
+def job_fused(h_in, delta, norm_w, eps, qw, scales, out, M, h_out=None, xn_out=None, tok=None,
+              swiglu=False, prefetch=None) -> Job:
+    """Describe out = gemv(RMSNorm1p(h_in + delta) * (1 + norm_w)) without launching it (see
+    `gemv_fused` for the arguments)."""
     for t in (h_in, norm_w, qw, scales, out):
         _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
     Mp, Kp = _packed(qw, scales)
@@ -201,10 +194,60 @@ def gemv_fused(h_in, delta, norm_w, eps, qw, scales, out, M, *, h_out=None, xn_o
         nrm.xn_out, nrm.ldxo = xn_out.data_ptr(), xn_out.stride(0)
     if prefetch is not None:
         nrm.prefetch, nrm.prefetch_bytes = prefetch.data_ptr(), prefetch.numel() * prefetch.element_size()
-    cfg = _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units)
     p = W4Params(qw.data_ptr(), scales.data_ptr(), None, out.data_ptr(), None, None, M, Kp, Mp, Kp, N,
                  0, out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, 0)
-    _launch(p, cfg, nrm, out.device, "gemv_w4 fused")
+    return Job(p, nrm, out.device, (h_in, delta, norm_w, qw, scales, out, h_out, xn_out, tok, prefetch))
+
+
+def gemv_chain(jobs, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1, blocks_per_sm=0, min_units=4):
+    """Not in the reference: run 1..4 jobs (`job`, `job_fused`) that depend on each other only
+    through their tensors as ONE launch, with a grid-wide barrier between consecutive jobs. The
+    results are bit-identical to launching them one by one with the same options; what is saved
+    is the start-up of a kernel per matrix (the weight stream of job j + 1 is requested while job
+    j finishes)."""
+    jobs = list(jobs)
+    _req(1 <= len(jobs) <= 4, "a chain holds 1..4 jobs")
+    _req(all(j.dev == jobs[0].dev for j in jobs), "all jobs of a chain live on one device")
+    _launch(jobs, _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units), "gemv_w4 chain")
+
+
+def gemv(x, qw, scales, out, M, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
+         blocks_per_sm=0, min_units=4, prefetch=None):
+    """out[N, M] = x[N, K] @ W~^T (W packed by quant.quantize_w4). prefetch (not in the reference):
+    a tensor whose bytes a later kernel will stream; the launch asks L2 for them before it waits
+    for its own input."""
+    _launch([job(x, qw, scales, out, M, prefetch=prefetch)],
+            _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units), "gemv_w4")
+
+
+def gemv_swiglu(x, qw, scales, out, I, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
+                blocks_per_sm=0, min_units=4):
+    """out[N, I] = silu(x @ Wg^T) * (x @ Wu^T) (packed by quant.quantize_w4_gate_up)."""
+    _launch([job(x, qw, scales, out, I, swiglu=True)],
+            _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units), "gemv_w4")
+
+
+def gemv_partial(x, qw, scales, out32, M, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
+                 blocks_per_sm=0, min_units=4):
+    """Not in the reference: `out32` is fp32 [N, M] and receives the unrounded sums -- one rank's
+    partial result of a matrix split along K over tensor-parallel ranks."""
+    _req(out32.dtype == torch.float32, "out32 must be fp32")
+    _launch([job(x, qw, scales, out32, M, allow_f32_out=True)],
+            _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units), "gemv_w4")
+
+
+def gemv_fused(h_in, delta, norm_w, eps, qw, scales, out, M, *, h_out=None, xn_out=None, tok=None,
+               swiglu=False, prefetch=None, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
+               blocks_per_sm=0, min_units=4):
+    """Not in the reference: out = gemv(RMSNorm1p(h_in + delta) * (1 + norm_w)) in one launch.
+
+    h_in bf16 [N, K]; delta bf16 [N, K] or None; h_out (optional, must not alias h_in) receives
+    bf16(h_in + delta) and xn_out (optional) the normed rows. With `tok` (int32 [>= N]) h_in is an
+    embedding table [V, K] and row r is table[tok[r]]. `prefetch` = a tensor whose bytes a later
+    kernel will stream (an L2 hint). Same arithmetic as `_C.rmsnorm1p` followed by `gemv`."""
+    _launch([job_fused(h_in, delta, norm_w, eps, qw, scales, out, M, h_out=h_out, xn_out=xn_out, tok=tok,
+                       swiglu=swiglu, prefetch=prefetch)],
+            _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units), "gemv_w4 fused")
 
 
 def auto_ksplit(Mp, Kp, N, warps=8):

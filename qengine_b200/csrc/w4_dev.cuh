@@ -26,14 +26,28 @@ __device__ __forceinline__ uint32_t nib2bf16(uint32_t w) {
   return v;
 }
 
+// A fragment of one packed word: rows (r, r + 8) x the word's four k.
+struct AFrag {
+  uint32_t a0, a1, a2, a3;
+};
+__device__ __forceinline__ AFrag unpack_word(uint32_t word) {
+  return AFrag{nib2bf16(word), nib2bf16(word >> 4), nib2bf16(word >> 8), nib2bf16(word >> 12)};
+}
+// c = A(word) * B(xa, xb): first product of a unit (no accumulator to read).
+__device__ __forceinline__ void mma_first(float (&c)[4], uint32_t word, uint32_t xa, uint32_t xb) {
+  const AFrag f = unpack_word(word);
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+      : "r"(f.a0), "r"(f.a1), "r"(f.a2), "r"(f.a3), "r"(xa), "r"(xb), "f"(0.f));
+}
 // c += A(word) * B(xa, xb): 16 rows x 4 k of weights times 4 k x 8 activation rows.
 __device__ __forceinline__ void mma_word(float (&c)[4], uint32_t word, uint32_t xa, uint32_t xb) {
-  const uint32_t a0 = nib2bf16(word), a1 = nib2bf16(word >> 4), a2 = nib2bf16(word >> 8),
-                 a3 = nib2bf16(word >> 12);
+  const AFrag f = unpack_word(word);
   asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(xa), "r"(xb));
+      : "r"(f.a0), "r"(f.a1), "r"(f.a2), "r"(f.a3), "r"(xa), "r"(xb));
 }
 
 // Operands of one unit for one lane: 2 x 16 B of codes, 2 scales (rows r, r + 8), 32 x values.
@@ -43,28 +57,26 @@ struct UnitOps {
   uint32_t s_lo, s_hi;  // raw fp16 bits
 };
 
-// acc += scale * (codes - 8) . x for one unit. Two independent mma chains (one per 64-k chunk) so
-// that consecutive tensor-core instructions do not wait for each other.
+// acc += scale * (codes - 8) . x for one unit: eight tensor-core products into one fp32 tile, the
+// group scale applied once (exact products, fp32 accumulation: the reference's arithmetic,
+// csrc/gemv_w4.cu:6-9). The unpack of word i + 1 does not depend on product i, so one accumulator
+// chain keeps the pipes busy.
 __device__ __forceinline__ void unit_fma(float (&acc)[4], const UnitOps& o) {
-  float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f};
-  mma_word(ca, o.w0.x, o.x0.x, o.x0.y);
-  mma_word(cb, o.w1.x, o.x2.x, o.x2.y);
-  mma_word(ca, o.w0.y, o.x0.z, o.x0.w);
-  mma_word(cb, o.w1.y, o.x2.z, o.x2.w);
-  mma_word(ca, o.w0.z, o.x1.x, o.x1.y);
-  mma_word(cb, o.w1.z, o.x3.x, o.x3.y);
-  mma_word(ca, o.w0.w, o.x1.z, o.x1.w);
-  mma_word(cb, o.w1.w, o.x3.z, o.x3.w);
+  float c[4];
+  mma_first(c, o.w0.x, o.x0.x, o.x0.y);
+  mma_word(c, o.w0.y, o.x0.z, o.x0.w);
+  mma_word(c, o.w0.z, o.x1.x, o.x1.y);
+  mma_word(c, o.w0.w, o.x1.z, o.x1.w);
+  mma_word(c, o.w1.x, o.x2.x, o.x2.y);
+  mma_word(c, o.w1.y, o.x2.z, o.x2.w);
+  mma_word(c, o.w1.z, o.x3.x, o.x3.y);
+  mma_word(c, o.w1.w, o.x3.z, o.x3.w);
   const float lo = __half2float(__ushort_as_half((unsigned short)o.s_lo));
   const float hi = __half2float(__ushort_as_half((unsigned short)o.s_hi));
-  acc[0] = fmaf(lo, ca[0], acc[0]);
-  acc[1] = fmaf(lo, ca[1], acc[1]);
-  acc[2] = fmaf(hi, ca[2], acc[2]);
-  acc[3] = fmaf(hi, ca[3], acc[3]);
-  acc[0] = fmaf(lo, cb[0], acc[0]);
-  acc[1] = fmaf(lo, cb[1], acc[1]);
-  acc[2] = fmaf(hi, cb[2], acc[2]);
-  acc[3] = fmaf(hi, cb[3], acc[3]);
+  acc[0] = fmaf(lo, c[0], acc[0]);
+  acc[1] = fmaf(lo, c[1], acc[1]);
+  acc[2] = fmaf(hi, c[2], acc[2]);
+  acc[3] = fmaf(hi, c[3], acc[3]);
 }
 
 // ---- mbarrier + bulk copy (TMA engine, untiled form) ---------------------------------------------

@@ -16,9 +16,13 @@
 //     (cp.async.bulk global -> shared, completion on an mbarrier): STAGES x PERW units in flight
 //     per warp, ~130 KB per SM, issued before the programmatic-dependency wait because weights
 //     never depend on the producer of x;
-//   * operands of unit i + 1 (2 LDS.128 of codes, 2 scales, 4 x 16 B of x) are fetched into
-//     registers while unit i is unpacked and multiplied (mma.sync.m16n8k16, two independent
-//     accumulator chains): the loop body is straight-line code without a wait in the common case;
+//   * ranges start at multiples of a ring stage whenever a tile is a whole number of stages long,
+//     so a stage never straddles two tiles and its PERW units run as straight-line code: 2 LDS.128
+//     of codes, 2 scales and 4 x 16 B of x per unit at immediate offsets, then the unpack feeding
+//     mma.sync.m16n8k16. The unpack (shift, lop3, bf16x2 subtract per pair of weights) is the cost
+//     that matters: at HBM rate an SM sub-partition has about 190 issue slots per unit, the
+//     unpack and its eight tensor-core products need 104 of them, so everything else in the
+//     loop has to stay in the low tens;
 //   * a tile (16 output rows) that lies inside one warp's range is stored from registers; the at
 //     most two cut tiles per warp (first / last of its range) are parked in shared memory and
 //     combined after ONE block barrier at the end of the kernel, each by the warp that holds the
@@ -38,8 +42,8 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <map>
 #include <mutex>
-#include <set>
 #include <string>
 #include <utility>
 #include <vector>
@@ -60,8 +64,9 @@ struct GemvArgs {
   float* ws;       // 2 x 128 floats per CTA: partial tiles that cross a CTA boundary
   int* counters;   // one arrival counter per tile, zero on entry, left zero
   int K, G, total, nworkers;
+  int quantum;     // ranges start at multiples of this many units (4 when G % 4 == 0, else 1)
   int xvec;        // x rows are 16-byte aligned with ldx % 8 == 0
-  // fused residual + RMSNorm prologue
+  // fused residual + RMSNorm prologue (h_in != nullptr)
   const bf16* h_in;
   const int* tok;  // optional: row r of h_in is table row tok[r] (h_in = embedding table)
   int vocab;
@@ -80,11 +85,178 @@ __device__ int g_w4_error = 0;
 
 constexpr int kWaitLimit = 1 << 20;
 
-template <int NW, int PERW, int STAGES, bool PRO>
-__global__ void __launch_bounds__(NW * 32, 1) w4_gemv_kernel(const GemvArgs a) {
+// First unit of worker v: the stream is dealt out in quanta of q units.
+__device__ __host__ __forceinline__ int range_begin(int total, int q, int nwk, int v) {
+  return q * share_begin(total / q, nwk, v);
+}
+
+// x fragment of a lane for the ragged cases (misaligned rows, or the last group when K is not a
+// multiple of 128): element loads, zeros beyond K. Kept out of line: it is never on the hot path.
+__device__ __noinline__ void load_x_slow(UnitOps& o, const bf16* row, int gg, int t, int K) {
+  const unsigned short* xs = reinterpret_cast<const unsigned short*>(row);
+  uint32_t v[16];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int k0 = gg * 128 + 64 * h + 16 * t;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int k = k0 + 2 * e;
+      const uint32_t lo = k < K ? xs[k] : 0u, hi = k + 1 < K ? xs[k + 1] : 0u;
+      v[h * 8 + e] = lo | (hi << 16);
+    }
+  }
+  o.x0 = make_uint4(v[0], v[1], v[2], v[3]);   o.x1 = make_uint4(v[4], v[5], v[6], v[7]);
+  o.x2 = make_uint4(v[8], v[9], v[10], v[11]); o.x3 = make_uint4(v[12], v[13], v[14], v[15]);
+}
+
+// The fused prologue: x_s[r] = RMSNorm1p(h_in[r] + delta[r]) * (1 + w) for r < N, computed by the
+// whole CTA. A thread owns packets (8 elements) p = tid, tid + NT, ... of EVERY row: the loads of
+// all rows are issued before the first dependent instruction, so the prologue costs one trip to
+// L2, not one per row. Statistics in fp32, fixed reduction order (warp shuffle tree, then warps in
+// order): a row's result does not depend on how many rows there are.
+template <int NW>
+__device__ __forceinline__ void norm_prologue(const GemvArgs& a, unsigned char* x_s, long pitch,
+                                              float (*s_red)[NW], int tid) {
+  constexpr int NT = NW * 32, RB = 4;  // rows are handled RB at a time (register budget)
+  const int lane = tid & 31, warp = tid >> 5, N = a.o.N, npk = a.K >> 3;
+  const bool writer = blockIdx.x == 0;
+#pragma unroll 1
+  for (int r0 = 0; r0 < N; r0 += RB) {
+    float ss[RB];
+    const bf16* hrow[RB];
+#pragma unroll
+    for (int i = 0; i < RB; ++i) {
+      const int r = r0 + i;
+      ss[i] = 0.f;
+      hrow[i] = nullptr;
+      if (r < N) {
+        if (a.tok) {
+          const int id = a.tok[r];
+          if (id >= 0 && id < a.vocab) hrow[i] = a.h_in + (size_t)id * a.K;  // else: a row of zeros
+        } else {
+          hrow[i] = a.h_in + (long)r * a.ldh;
+        }
+      }
+    }
+    for (int p = tid; p < npk; p += NT) {
+      uint4 hv[RB], dv[RB];
+#pragma unroll
+      for (int i = 0; i < RB; ++i) {
+        if (r0 + i < N) {
+          hv[i] = hrow[i] ? reinterpret_cast<const uint4*>(hrow[i])[p] : make_uint4(0u, 0u, 0u, 0u);
+          if (a.delta) dv[i] = reinterpret_cast<const uint4*>(a.delta + (long)(r0 + i) * a.ldd)[p];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < RB; ++i) {
+        const int r = r0 + i;
+        if (r < N) {
+          float v[8];
+          widen8(hv[i], v);
+          if (a.delta) {
+            float d[8];
+            widen8(dv[i], d);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = rnd(v[e] + d[e]);
+            hv[i] = narrow8(v);
+          }
+          reinterpret_cast<uint4*>(x_s + r * pitch)[p] = hv[i];
+          if (writer && a.h_out) reinterpret_cast<uint4*>(a.h_out + (long)r * a.ldho)[p] = hv[i];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ss[i] = fmaf(v[e], v[e], ss[i]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < RB; ++i) {
+      if (r0 + i < N) {
+        const float w = warp_allsum(ss[i]);
+        if (lane == 0) s_red[r0 + i][warp] = w;
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll 1
+  for (int r0 = 0; r0 < N; r0 += RB) {
+    float inv[RB];
+#pragma unroll
+    for (int i = 0; i < RB; ++i) {
+      inv[i] = 0.f;
+      if (r0 + i < N) {
+        float tot = 0.f;
+#pragma unroll
+        for (int w2 = 0; w2 < NW; ++w2) tot += s_red[r0 + i][w2];
+        inv[i] = rsqrtf(tot / (float)a.K + a.eps);
+      }
+    }
+    for (int p = tid; p < npk; p += NT) {  // same thread -> packet map as above: own data only
+      float g[8];
+      widen8(reinterpret_cast<const uint4*>(a.norm_w)[p], g);
+#pragma unroll
+      for (int i = 0; i < RB; ++i) {
+        const int r = r0 + i;
+        if (r < N) {
+          uint4* xs = reinterpret_cast<uint4*>(x_s + r * pitch);
+          float v[8], y[8];
+          widen8(xs[p], v);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) y[e] = v[e] * inv[i] * (1.0f + g[e]);
+          const uint4 q = narrow8(y);
+          xs[p] = q;
+          if (writer && a.xn_out) reinterpret_cast<uint4*>(a.xn_out + (long)r * a.ldxo)[p] = q;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// A chain is up to kMaxJobs GEMVs that depend on each other only through global memory (the
+// output of one is the input, or the residual update, of the next). They run as ONE cooperative
+// launch: the blocks meet at a grid-wide barrier between two jobs, and every warp asks the copy
+// engine for the head of its slab of the next matrix BEFORE it goes to the barrier, so the
+// memory pipeline never drains at a job boundary the way it does at a kernel boundary (a
+// separate launch costs about 6.6 us here before its first byte is multiplied).
+constexpr int kMaxJobs = 4;
+struct ChainArgs {
+  GemvArgs job[kMaxJobs];
+  int njobs;
+  int* gbar;  // [0] arrivals of the current barrier, [1] generation (never reset)
+};
+
+// Grid-wide barrier for co-resident blocks (cooperative launch). Release: every thread's writes,
+// then a device-scope fence by the arriving thread; acquire: fence after the generation moved
+// (which also drops stale L1 lines, so plain loads afterwards see the other blocks' output).
+// The spin is bounded: on expiry the error word is set and the block goes on (wrong results,
+// reported; never a hang).
+__device__ __forceinline__ void grid_barrier(int* gbar, int nblocks) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    volatile int* vg = gbar;
+    const int gen = vg[1];
+    __threadfence();
+    if (atomicAdd(gbar, 1) == nblocks - 1) {
+      vg[0] = 0;
+      __threadfence();
+      atomicAdd(gbar + 1, 1);
+    } else {
+      int spins = 0;
+      while (vg[1] == gen) {
+        if (++spins > (1 << 24)) {
+          atomicExch(&g_w4_error, 2);
+          break;
+        }
+      }
+    }
+    __threadfence();
+  }
+  __syncthreads();
+}
+
+template <int NW, int PERW, int STAGES>
+__global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_constant__ ChainArgs c) {
   constexpr uint32_t kStageW = PERW * 1024, kStageS = PERW * 32;
   constexpr uint32_t kRing = STAGES * (kStageW + kStageS);
-  constexpr int NT = NW * 32;
   dep_release();
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full[NW][STAGES];
@@ -93,307 +265,317 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_gemv_kernel(const GemvArgs a) {
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = lane >> 2, t = lane & 3;
-  const int G = a.G, total = a.total, nwk = a.nworkers;
   unsigned char* ring_w = smem + (size_t)warp * kRing;
   unsigned char* ring_s = ring_w + (size_t)STAGES * kStageW;
   float* part = reinterpret_cast<float*>(smem + (size_t)NW * kRing);  // [NW][2][128]
   unsigned char* x_s = smem + (size_t)NW * kRing + (size_t)NW * 2 * 128 * sizeof(float);
+  const int worker = blockIdx.x * NW + warp;
 
-  // ---- ranges: worker v of nwk owns units [share_begin(v), share_begin(v + 1)) ----
-  const int w_first = blockIdx.x * NW;
-  const int worker = w_first + warp;
-  const int u0 = share_begin(total, nwk, min(worker, nwk));
-  const int u1 = share_begin(total, nwk, min(worker + 1, nwk));
   if (lane == 0) {
-    s_rb[warp] = u0;
-    if (warp == NW - 1) s_rb[NW] = u1;
     for (int s = 0; s < STAGES; ++s) bar_init(&full[warp][s], 1);
     bar_fence_init();
   }
   __syncwarp();
-  const int n_units = u1 - u0;
-  const int nstage = (n_units + PERW - 1) / PERW;
 
-  auto refill = [&](int st) {  // lane 0 only: stage st of this warp's range into its ring slot
-    const int slot = st % STAGES;
-    const int ub = u0 + st * PERW, cnt = min(PERW, u1 - ub);
-    bar_expect(&full[warp][slot], (uint32_t)cnt * (1024 + 32));
-    bulk_g2s(ring_w + (size_t)slot * kStageW, a.qw + (size_t)ub * 64, (uint32_t)cnt * 1024, &full[warp][slot]);
-    bulk_g2s(ring_s + (size_t)slot * kStageS, a.scales + (size_t)ub * 16, (uint32_t)cnt * 32, &full[warp][slot]);
-  };
-  if (lane == 0) {
-    for (int st = 0; st < min(STAGES, nstage); ++st) refill(st);  // weights never depend on x
-    if (a.pf_bytes) {  // this warp's slice of the hinted range, 16 KB per request
-      const unsigned long long nslices = (unsigned long long)gridDim.x * NW;
-      const unsigned long long per = ((a.pf_bytes + nslices - 1) / nslices + 15) & ~15ull;
-      unsigned long long b = per * (unsigned long long)(blockIdx.x * NW + warp);
-      const unsigned long long e = min(a.pf_bytes & ~15ull, b + per);
-      for (; b < e; b += 16384) l2_prefetch(a.pf + b, (uint32_t)min(16384ull, e - b));
+  // Ring position of the next stage to consume; it runs on across jobs (a slot's barrier
+  // completes one phase per fill, whichever matrix the fill came from).
+  int slot = 0, phase = 0;
+  bool ok = true;
+
+  // lane 0: request stages [st0, st1) of the range [u0, u1) of job `a`, into consecutive ring
+  // slots starting at `at`
+  auto fill = [&](const GemvArgs& a, int u0, int u1, int st0, int st1, int at) {
+    for (int st = st0; st < st1; ++st) {
+      const int ub = u0 + st * PERW, cnt = min(PERW, u1 - ub);
+      bar_expect(&full[warp][at], (uint32_t)cnt * (1024 + 32));
+      bulk_g2s(ring_w + (size_t)at * kStageW, a.qw + (size_t)ub * 64, (uint32_t)cnt * 1024, &full[warp][at]);
+      bulk_g2s(ring_s + (size_t)at * kStageS, a.scales + (size_t)ub * 16, (uint32_t)cnt * 32, &full[warp][at]);
+      if (++at == STAGES) at = 0;
     }
+  };
+  auto range_of = [&](const GemvArgs& a, int& u0, int& u1) {
+    u0 = range_begin(a.total, a.quantum, a.nworkers, min(worker, a.nworkers));
+    u1 = range_begin(a.total, a.quantum, a.nworkers, min(worker + 1, a.nworkers));
+  };
+
+  // weights never depend on the producer of x: the first stages are requested before the
+  // programmatic-dependency wait
+  {
+    int u0, u1;
+    range_of(c.job[0], u0, u1);
+    if (lane == 0) fill(c.job[0], u0, u1, 0, min(STAGES, (u1 - u0 + PERW - 1) / PERW), 0);
   }
-  __syncthreads();  // s_rb visible to everyone
   dep_wait();
 
-  // ---- prologue: x = RMSNorm1p(h_in + delta) into shared memory, one copy per CTA ----
-  const int xrow = min(r, a.o.N - 1);  // rows >= N feed mma columns that are never stored
-  const long pitch = (long)a.K * 2 + 16;  // + 16 B: rows of one quarter-warp hit different banks
-  if constexpr (PRO) {
-    const int npk = a.K >> 3;
-    float ss[QE_MAX_ROWS];
-#pragma unroll
-    for (int rr = 0; rr < QE_MAX_ROWS; ++rr) {
-      ss[rr] = 0.f;
-      if (rr < a.o.N) {
-        const bf16* hrow = a.h_in + (long)rr * a.ldh;
-        bool zero = false;
-        if (a.tok) {
-          const int id = a.tok[rr];
-          zero = id < 0 || id >= a.vocab;
-          hrow = a.h_in + (size_t)(zero ? 0 : id) * a.K;
-        }
-        uint4* xs = reinterpret_cast<uint4*>(x_s + rr * pitch);
-        for (int p = tid; p < npk; p += NT) {
-          float v[8];
-          uint4 raw = zero ? make_uint4(0u, 0u, 0u, 0u) : reinterpret_cast<const uint4*>(hrow)[p];
-          widen8(raw, v);
-          if (a.delta) {
-            float d[8];
-            widen8(reinterpret_cast<const uint4*>(a.delta + (long)rr * a.ldd)[p], d);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = rnd(v[e] + d[e]);
-            raw = narrow8(v);
-          }
-          xs[p] = raw;
-          if (blockIdx.x == 0 && a.h_out) reinterpret_cast<uint4*>(a.h_out + (long)rr * a.ldho)[p] = raw;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) ss[rr] = fmaf(v[e], v[e], ss[rr]);
-        }
-        ss[rr] = warp_allsum(ss[rr]);
-        if (lane == 0) s_red[rr][warp] = ss[rr];
+#pragma unroll 1
+  for (int j = 0; j < c.njobs; ++j) {
+    const GemvArgs& a = c.job[j];
+    const int G = a.G, total = a.total, nwk = a.nworkers;
+    int u0, u1;
+    range_of(a, u0, u1);
+    if (lane == 0) {
+      s_rb[warp] = u0;
+      if (warp == NW - 1) s_rb[NW] = u1;
+      if (a.pf_bytes) {  // this warp's slice of the hinted range, 16 KB per request
+        const unsigned long long nslices = (unsigned long long)gridDim.x * NW;
+        const unsigned long long per = ((a.pf_bytes + nslices - 1) / nslices + 15) & ~15ull;
+        unsigned long long b = per * (unsigned long long)worker;
+        const unsigned long long e = min(a.pf_bytes & ~15ull, b + per);
+        for (; b < e; b += 16384) l2_prefetch(a.pf + b, (uint32_t)min(16384ull, e - b));
       }
     }
-    __syncthreads();
-#pragma unroll
-    for (int rr = 0; rr < QE_MAX_ROWS; ++rr) {
-      if (rr < a.o.N) {
-        float tot = 0.f;
-#pragma unroll
-        for (int w2 = 0; w2 < NW; ++w2) tot += s_red[rr][w2];
-        const float inv = rsqrtf(tot / (float)a.K + a.eps);
-        uint4* xs = reinterpret_cast<uint4*>(x_s + rr * pitch);
-        for (int p = tid; p < npk; p += NT) {  // same thread -> packet map as above
-          float v[8], g[8], y[8];
-          widen8(xs[p], v);
-          widen8(reinterpret_cast<const uint4*>(a.norm_w)[p], g);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) y[e] = v[e] * inv * (1.0f + g[e]);
-          const uint4 q = narrow8(y);
-          xs[p] = q;
-          if (blockIdx.x == 0 && a.xn_out) reinterpret_cast<uint4*>(a.xn_out + (long)rr * a.ldxo)[p] = q;
-        }
-      }
-    }
-    __syncthreads();
-  }
+    const int n_units = u1 - u0;
+    const int nstage = (n_units + PERW - 1) / PERW;
 
-  // ---- x fragment of group gg: 16 consecutive k per 64-k chunk for activation row `xrow` ----
-  const bool tail_k = (a.K & 127) != 0;  // the last group reads past K unless guarded
-  auto load_x = [&](UnitOps& o, int gg) {
-    if constexpr (PRO) {
-      const uint4* xp = reinterpret_cast<const uint4*>(x_s + xrow * pitch + (size_t)gg * 256 + 32 * t);
-      o.x0 = xp[0]; o.x1 = xp[1]; o.x2 = xp[8]; o.x3 = xp[9];
+    // ---- where this lane's x fragments come from ----
+    // Lane (r, t) multiplies activation row r; rows >= N feed mma columns that are never stored
+    // and simply re-read row N - 1. With the prologue x lives in shared memory (pitch + 16 B so
+    // that the rows of a quarter-warp fall into different banks); both cases are read through one
+    // generic pointer so that the stage body below exists once.
+    const int xrow = min(r, a.o.N - 1);
+    const unsigned char* xbase;
+    bool xfast;
+    if (a.h_in) {
+      const long pitch = (long)a.K * 2 + 16;
+      norm_prologue<NW>(a, x_s, pitch, s_red, tid);
+      xbase = x_s + xrow * pitch + 32 * t;
+      xfast = true;
     } else {
-      const bf16* row = a.x + (long)xrow * a.ldx;
-      if (a.xvec && !(tail_k && gg == G - 1)) {
-        const uint4* xp = reinterpret_cast<const uint4*>(row + (size_t)gg * 128 + 16 * t);  // coherent loads
-        o.x0 = xp[0]; o.x1 = xp[1]; o.x2 = xp[8]; o.x3 = xp[9];
-      } else {  // misaligned rows or the ragged end of K: element loads, zeros beyond K
-        const unsigned short* xs = reinterpret_cast<const unsigned short*>(row);
-        uint32_t v[16];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int k0 = gg * 128 + 64 * h + 16 * t;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int k = k0 + 2 * e;
-            const uint32_t lo = k < a.K ? xs[k] : 0u, hi = k + 1 < a.K ? xs[k + 1] : 0u;
-            v[h * 8 + e] = lo | (hi << 16);
-          }
-        }
-        o.x0 = make_uint4(v[0], v[1], v[2], v[3]);   o.x1 = make_uint4(v[4], v[5], v[6], v[7]);
-        o.x2 = make_uint4(v[8], v[9], v[10], v[11]); o.x3 = make_uint4(v[12], v[13], v[14], v[15]);
-      }
+      xbase = reinterpret_cast<const unsigned char*>(a.x + (long)xrow * a.ldx) + 32 * t;
+      xfast = a.xvec != 0;
     }
-  };
+    const bool tail_k = (a.K & 127) != 0;  // the last group reads past K unless guarded
 
-  // ---- the stream: load cursor runs one unit ahead of the compute cursor ----
-  bool ok = true;
-  int l_slot = 0, l_phase = 0, l_j = 0;  // ring slot / phase / index of the next unit to load
-  int tile = u0 / G;
-  int g = u0 - tile * G;                 // group of the unit being computed
-  int l_g = g;                           // group of the next unit to load
-  int seg_gb = g;                        // first group of the segment in `acc`
-  int c_j = 0, c_st = 0;                 // index in stage / stage of the unit being computed
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    // ---- the stream ----
+    int tile = u0 / G;
+    int g = u0 - tile * G;   // group of the next unit
+    int seg_gb = g;          // first group of the segment held in acc
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
 
-  auto load_next = [&](UnitOps& o) {
-    if (l_j == 0 && !bar_wait(&full[warp][l_slot], l_phase, kWaitLimit)) {
-      ok = false;
-      atomicExch(&g_w4_error, 1);
-      return;
-    }
-    const uint4* wp = reinterpret_cast<const uint4*>(ring_w + (size_t)l_slot * kStageW + (size_t)l_j * 1024) + lane;
-    const unsigned short* sp =
-        reinterpret_cast<const unsigned short*>(ring_s + (size_t)l_slot * kStageS + (size_t)l_j * 32) + r;
-    o.w0 = wp[0];
-    o.w1 = wp[32];
-    o.s_lo = sp[0];
-    o.s_hi = sp[8];
-    load_x(o, l_g);
-    if (++l_g == G) l_g = 0;
-    if (++l_j == PERW) {
-      l_j = 0;
-      if (++l_slot == STAGES) { l_slot = 0; l_phase ^= 1; }
-    }
-  };
-
-  auto step = [&](const UnitOps& cur, UnitOps& nxt, int i) {
-    if (i + 1 < n_units) load_next(nxt);
-    unit_fma(acc, cur);
-    ++g;
-    const bool last = i == n_units - 1;
-    if (g == G || last) {
+    // A segment [seg_gb, g) of `tile` is complete: a whole tile is stored, a cut one parked (slot
+    // 0 if this range starts inside the tile, slot 1 if it holds the tile's head).
+    auto close_segment = [&]() {
       if (seg_gb == 0 && g == G) {
         tile_out(a.o, tile, acc, lane);
-      } else {  // cut tile: slot 0 if this range starts inside the tile, slot 1 if it holds its head
+      } else {
         float* p = part + (warp * 2 + (seg_gb != 0 ? 0 : 1)) * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) p[c * 32 + lane] = acc[c];
+        for (int k = 0; k < 4; ++k) p[k * 32 + lane] = acc[k];
       }
       acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
       if (g == G) { g = 0; ++tile; }
       seg_gb = g;
-    }
-    if (++c_j == PERW || last) {  // this stage is consumed: hand its slot back to the copy engine
-      __syncwarp();
-      if (lane == 0 && c_st + STAGES < nstage) {
-        async_proxy_fence();
-        refill(c_st + STAGES);
-      }
-      c_j = 0;
-      ++c_st;
-    }
-  };
+    };
 
-  {
-    UnitOps A, B;
-    if (n_units > 0) load_next(A);
-    for (int i = 0; i < n_units && ok; i += 2) {
-      step(A, B, i);
-      if (i + 1 < n_units && ok) step(B, A, i + 1);
-    }
-    if (!ok) {
-      // Give the copies that are still in flight a bounded chance to land before the CTA exits.
-      __syncwarp();
-      for (int s = 0; s < STAGES; ++s) bar_wait(&full[warp][s], 0, 1 << 10), bar_wait(&full[warp][s], 1, 1 << 10);
-    }
-  }
-  __syncthreads();  // every partial tile of this CTA is in shared memory
-
-  // ---- cut tiles: combined by the warp holding the head, ascending warp order ----
-  const int cta_b = s_rb[0], cta_e = s_rb[NW];
-  const int my_cta = blockIdx.x;
-  auto publish = [&](int T, const float (&f)[4], int units, int slot) {
-    // one partial per CTA through global memory; whoever completes the tile adds them all
-    float* gm = a.ws + ((size_t)my_cta * 2 + slot) * 128;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) __stcg(gm + c * 32 + lane, f[c]);
-    __threadfence();
-    __syncwarp();
-    int done = 0;
-    if (lane == 0) done = atomicAdd(a.counters + T, units) + units == G;
-    done = __shfl_sync(0xffffffffu, done, 0);
-    if (!done) return;
-    __threadfence();
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
-    const int c_lo = share_owner(total, nwk, T * G) / NW, c_hi = share_owner(total, nwk, T * G + G - 1) / NW;
+    // Both loops below walk the ring stage by stage. The fast one serves ranges made of whole
+    // stages that never straddle a tile (every matrix of the model): no per-unit decisions at
+    // all, every operand at an immediate offset from three base pointers.
+    const bool all_fast = xfast && !tail_k && (a.quantum % PERW) == 0;
+    if (all_fast) {
+      const unsigned char* xg = xbase + (size_t)g * 256;
 #pragma unroll 1
-    for (int cc = c_lo; cc <= c_hi; ++cc) {
-      const int cb = share_begin(total, nwk, min(cc * NW, nwk));
-      const float* p = a.ws + ((size_t)cc * 2 + (cb > T * G ? 0 : 1)) * 128;
+      for (int st = 0; st < nstage && ok; ++st) {
+        if (!bar_wait(&full[warp][slot], phase, kWaitLimit)) {
+          ok = false;
+          atomicExch(&g_w4_error, 1);
+          break;
+        }
+        const uint4* wp = reinterpret_cast<const uint4*>(ring_w + (size_t)slot * kStageW) + lane;
+        const unsigned short* sp = reinterpret_cast<const unsigned short*>(ring_s + (size_t)slot * kStageS) + r;
+        const uint4* xp = reinterpret_cast<const uint4*>(xg);
+        UnitOps ops[PERW];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) s[c] += __ldcg(p + c * 32 + lane);
+        for (int i = 0; i < PERW; ++i) {
+          ops[i].w0 = wp[i * 64];
+          ops[i].w1 = wp[i * 64 + 32];
+          ops[i].s_lo = sp[i * 16];
+          ops[i].s_hi = sp[i * 16 + 8];
+          ops[i].x0 = xp[i * 16];
+          ops[i].x1 = xp[i * 16 + 1];
+          ops[i].x2 = xp[i * 16 + 8];
+          ops[i].x3 = xp[i * 16 + 9];
+        }
+#pragma unroll
+        for (int i = 0; i < PERW; ++i) unit_fma(acc, ops[i]);
+        g += PERW;
+        xg += PERW * 256;
+        if (g == G || st == nstage - 1) {
+          close_segment();
+          xg = xbase + (size_t)g * 256;
+        }
+        __syncwarp();  // every lane has read this stage: hand its slot back to the copy engine
+        if (lane == 0 && st + STAGES < nstage) {
+          async_proxy_fence();
+          fill(a, u0, u1, st + STAGES, st + STAGES + 1, slot);
+        }
+        if (++slot == STAGES) { slot = 0; phase ^= 1; }
+      }
+    } else {
+#pragma unroll 1
+      for (int st = 0; st < nstage && ok; ++st) {
+        if (!bar_wait(&full[warp][slot], phase, kWaitLimit)) {
+          ok = false;
+          atomicExch(&g_w4_error, 1);
+          break;
+        }
+        const uint4* wp = reinterpret_cast<const uint4*>(ring_w + (size_t)slot * kStageW) + lane;
+        const unsigned short* sp = reinterpret_cast<const unsigned short*>(ring_s + (size_t)slot * kStageS) + r;
+        const int cnt = min(PERW, n_units - st * PERW);
+#pragma unroll 1
+        for (int i = 0; i < cnt; ++i) {
+          UnitOps o;
+          o.w0 = wp[i * 64];
+          o.w1 = wp[i * 64 + 32];
+          o.s_lo = sp[i * 16];
+          o.s_hi = sp[i * 16 + 8];
+          if (xfast && !(tail_k && g == G - 1)) {
+            const uint4* xp = reinterpret_cast<const uint4*>(xbase + (size_t)g * 256);
+            o.x0 = xp[0]; o.x1 = xp[1]; o.x2 = xp[8]; o.x3 = xp[9];
+          } else {
+            load_x_slow(o, a.x + (long)xrow * a.ldx, g, t, a.K);
+          }
+          unit_fma(acc, o);
+          ++g;
+          if (g == G || (st == nstage - 1 && i == cnt - 1)) close_segment();
+        }
+        __syncwarp();
+        if (lane == 0 && st + STAGES < nstage) {
+          async_proxy_fence();
+          fill(a, u0, u1, st + STAGES, st + STAGES + 1, slot);
+        }
+        if (++slot == STAGES) { slot = 0; phase ^= 1; }
+      }
     }
-    tile_out(a.o, T, s, lane);
-    if (lane == 0) a.counters[T] = 0;
-  };
 
-  if (ok && n_units > 0 && (u1 % G) != 0) {
-    const int T = (u1 - 1) / G;
-    if (T * G >= u0) {  // the head of tile T is in this warp's slot 1
-      const int tend = T * G + G;
+    // This warp's ring is empty: ask for the head of its slab of the next matrix now, so that the
+    // copies run while the blocks finish this job and meet at the barrier.
+    if (ok && j + 1 < c.njobs) {
+      int v0, v1;
+      range_of(c.job[j + 1], v0, v1);
+      __syncwarp();
+      if (lane == 0) {
+        async_proxy_fence();
+        fill(c.job[j + 1], v0, v1, 0, min(STAGES, (v1 - v0 + PERW - 1) / PERW), slot);
+      }
+    }
+    __syncthreads();  // every partial tile of this CTA is in shared memory, s_rb is complete
+
+    // ---- cut tiles: combined by the warp holding the head, ascending warp order ----
+    const int cta_b = s_rb[0], cta_e = s_rb[NW];
+    const int my_cta = blockIdx.x;
+    auto publish = [&](int T, const float (&f)[4], int units, int pslot) {
+      // one partial per CTA through global memory; whoever completes the tile adds them all
+      float* gm = a.ws + ((size_t)my_cta * 2 + pslot) * 128;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) __stcg(gm + k * 32 + lane, f[k]);
+      __threadfence();
+      __syncwarp();
+      int done = 0;
+      if (lane == 0) done = atomicAdd(a.counters + T, units) + units == G;
+      done = __shfl_sync(0xffffffffu, done, 0);
+      if (!done) return;
+      __threadfence();
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      const int q = a.quantum;
+      const int c_lo = share_owner(total / q, nwk, (T * G) / q) / NW;
+      const int c_hi = share_owner(total / q, nwk, (T * G + G - 1) / q) / NW;
+#pragma unroll 1
+      for (int cc = c_lo; cc <= c_hi; ++cc) {
+        const int cb = range_begin(total, q, nwk, min(cc * NW, nwk));
+        const float* p = a.ws + ((size_t)cc * 2 + (cb > T * G ? 0 : 1)) * 128;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) sum[k] += __ldcg(p + k * 32 + lane);
+      }
+      tile_out(a.o, T, sum, lane);
+      if (lane == 0) a.counters[T] = 0;
+    };
+
+    if (ok && n_units > 0 && (u1 % G) != 0) {
+      const int T = (u1 - 1) / G;
+      if (T * G >= u0) {  // the head of tile T is in this warp's slot 1
+        const int tend = T * G + G;
+        float f[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) f[k] = part[(warp * 2 + 1) * 128 + k * 32 + lane];
+        for (int w2 = warp + 1; w2 < NW && s_rb[w2] < tend; ++w2) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) f[k] += part[(w2 * 2) * 128 + k * 32 + lane];
+        }
+        if (tend <= cta_e) tile_out(a.o, T, f, lane);
+        else publish(T, f, cta_e - T * G, 1);
+      }
+    }
+    if (warp == 0 && ok && cta_e > cta_b && (cta_b % G) != 0) {  // tile that began in an earlier CTA
+      const int T = cta_b / G, tend = T * G + G;
       float f[4];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) f[c] = part[(warp * 2 + 1) * 128 + c * 32 + lane];
-      for (int w2 = warp + 1; w2 < NW && s_rb[w2] < tend; ++w2) {
+      for (int k = 0; k < 4; ++k) f[k] = part[k * 32 + lane];
+      for (int w2 = 1; w2 < NW && s_rb[w2] < tend; ++w2) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) f[c] += part[(w2 * 2) * 128 + c * 32 + lane];
+        for (int k = 0; k < 4; ++k) f[k] += part[(w2 * 2) * 128 + k * 32 + lane];
       }
-      if (tend <= cta_e) tile_out(a.o, T, f, lane);
-      else publish(T, f, cta_e - T * G, 1);
+      publish(T, f, min(tend, cta_e) - cta_b, 0);
     }
+    if (j + 1 < c.njobs) grid_barrier(c.gbar, gridDim.x);  // also separates the uses of part / s_rb
   }
-  if (warp == 0 && ok && cta_e > cta_b && (cta_b % G) != 0) {  // tile that began in an earlier CTA
-    const int T = cta_b / G, tend = T * G + G;
-    float f[4];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) f[c] = part[c * 32 + lane];
-    for (int w2 = 1; w2 < NW && s_rb[w2] < tend; ++w2) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) f[c] += part[(w2 * 2) * 128 + c * 32 + lane];
-    }
-    publish(T, f, min(tend, cta_e) - cta_b, 0);
+  if (!ok) {
+    // Give the copies that are still in flight a bounded chance to land before the CTA exits.
+    __syncwarp();
+    for (int s = 0; s < STAGES; ++s) bar_wait(&full[warp][s], 0, 1 << 10), bar_wait(&full[warp][s], 1, 1 << 10);
   }
 }
 
 // ---- host side -----------------------------------------------------------------------------------
-using KernelFn = void (*)(const GemvArgs);
+using KernelFn = void (*)(const ChainArgs);
 
 struct Geometry {
-  KernelFn fn[2];  // [prologue]
+  KernelFn fn;
   int nw, perw, stages;
   size_t ring_bytes() const { return (size_t)nw * stages * perw * (1024 + 32) + (size_t)nw * 2 * 128 * sizeof(float); }
 };
 template <int NW, int PERW, int STAGES>
 constexpr Geometry geometry() {
-  return Geometry{{w4_gemv_kernel<NW, PERW, STAGES, false>, w4_gemv_kernel<NW, PERW, STAGES, true>}, NW, PERW, STAGES};
+  return Geometry{w4_chain_kernel<NW, PERW, STAGES>, NW, PERW, STAGES};
 }
-// Selected by the reference's launch options: `warps` picks the CTA size (4 / 8 -> 8 warps,
-// 0 / 16 -> 16 warps, variant 1 -> 24 warps), `unroll` the ring shape (0 / 4 -> 2 stages of 4
-// units, 1 / 2 -> 3 stages of 2 units).
-const Geometry kGeoms[] = {geometry<16, 4, 2>(), geometry<16, 2, 3>(), geometry<8, 4, 2>(), geometry<8, 2, 3>(),
+// Selected by the reference's launch options. `warps`: 0 (auto) -> 20 warps per CTA, 16 -> 16,
+// 4 / 8 -> 8; variant 1 -> 24 warps. `unroll` picks the ring: 0 / 2 -> 3 stages of 2 units,
+// 4 -> 2 stages of 4 units, 1 -> 2 stages of 2 units (the smallest; leaves room for eight rows of
+// prologue input). Work is split by CTA size only, so every ring shape of one CTA size gives the
+// same bits.
+const Geometry kGeoms[] = {geometry<20, 2, 3>(), geometry<20, 4, 2>(), geometry<20, 2, 2>(),
+                           geometry<16, 2, 3>(), geometry<16, 4, 2>(), geometry<16, 2, 2>(),
+                           geometry<8, 2, 3>(),  geometry<8, 4, 2>(),  geometry<8, 2, 2>(),
                            geometry<24, 2, 3>()};
 
 const Geometry& pick_geometry(const qe_w4_cfg& c) {
-  const bool fine = c.unroll == 1 || c.unroll == 2;
-  if (c.variant == 1) return kGeoms[4];
-  if (c.warps == 4 || c.warps == 8) return kGeoms[fine ? 3 : 2];
-  return kGeoms[fine ? 1 : 0];
+  if (c.variant == 1) return kGeoms[9];
+  const int ring = c.unroll == 4 ? 1 : c.unroll == 1 ? 2 : 0;
+  const int size = (c.warps == 4 || c.warps == 8) ? 2 : c.warps == 16 ? 1 : 0;
+  return kGeoms[3 * size + ring];
 }
 
-// cudaFuncAttributeMaxDynamicSharedMemorySize is per device: remember where it has been set.
-cudaError_t allow_smem(KernelFn fn, size_t bytes) {
+// Largest dynamic shared memory a launch of `fn` may ask for on the current device (the opt-in
+// maximum minus the kernel's static shared memory). Raising the per-function limit is a per-device
+// setting: done once per (function, device). Returns < 0 (minus the CUDA error) on failure.
+long dynamic_smem_limit(KernelFn fn) {
   static std::mutex mu;
-  static std::set<std::pair<const void*, int>> done;
+  static std::map<std::pair<const void*, int>, long> known;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
+  if (e != cudaSuccess) return -(long)e;
   std::lock_guard<std::mutex> lk(mu);
-  if (done.count({(const void*)fn, dev})) return cudaSuccess;
-  e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-  if (e == cudaSuccess) done.insert({(const void*)fn, dev});
-  (void)bytes;
-  return e;
+  auto it = known.find({(const void*)fn, dev});
+  if (it != known.end()) return it->second;
+  int optin = 0;
+  cudaFuncAttributes fa{};
+  if ((e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess ||
+      (e = cudaFuncGetAttributes(&fa, fn)) != cudaSuccess)
+    return -(long)e;
+  const long limit = (long)optin - (long)fa.sharedSizeBytes;
+  if ((e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit)) != cudaSuccess)
+    return -(long)e;
+  known[{(const void*)fn, dev}] = limit;
+  return limit;
 }
 
 // Experiment knob with the reference's syntax (csrc/gemv_w4.cu:427-449):
@@ -425,7 +607,7 @@ const std::vector<ShapeCfg>& env_overrides() {
 struct Resolved {
   qe_w4_plan plan;
   const Geometry* geom;
-  int nworkers;
+  int nworkers, quantum;
 };
 
 // Shape-only launch policy (never N): as many warps as there are units / min_units, at most one
@@ -444,8 +626,12 @@ Resolved resolve(const qe_w4_params& p, const qe_w4_cfg& c_in) {
   if (c.ksplit > 0) min_units = std::max<long>(1, std::min<long>(min_units, G / std::min<long>(c.ksplit, G)));
   const long sms = qe_sm_count();
   const long ctas_max = sms;  // one CTA per SM
+  // ranges are dealt out in quanta of 4 units (a whole number of ring stages in every geometry)
+  // when the tiles are a whole number of quanta long, so that a stage never straddles two tiles
+  const long quantum = (G % 4 == 0) ? 4 : 1;  // the same for every ring geometry: same split, same bits
   const long want = (units + min_units - 1) / min_units;
-  const long workers = std::max<long>(1, std::min<long>({ctas_max * r.geom->nw, want, units}));
+  const long workers = std::max<long>(1, std::min<long>({ctas_max * r.geom->nw, want, units / quantum}));
+  r.quantum = (int)quantum;
   r.nworkers = (int)workers;
   r.plan.mode = 4;
   r.plan.grid_x = (int)((workers + r.geom->nw - 1) / r.geom->nw);
@@ -469,11 +655,13 @@ int check_params(const qe_w4_params* p, const qe_w4_cfg* cfg) {
   return 0;
 }
 
-int launch_gemv(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg, cudaStream_t stream) {
+// Fill the device-side description of one job; *smem_extra = shared memory its prologue needs.
+int make_job(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg, GemvArgs& a, Resolved& r,
+             size_t* smem_extra) {
   int rc = check_params(p, cfg);
   if (rc) return rc;
-  const Resolved r = resolve(*p, *cfg);
-  GemvArgs a{};
+  r = resolve(*p, *cfg);
+  a = GemvArgs{};
   a.qw = reinterpret_cast<const uint4*>(p->qw);
   a.scales = reinterpret_cast<const __half*>(p->scales);
   a.x = reinterpret_cast<const bf16*>(p->x);
@@ -490,9 +678,9 @@ int launch_gemv(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* c
   a.G = p->Kp / 128;
   a.total = (p->Mp / 16) * a.G;
   a.nworkers = r.nworkers;
+  a.quantum = r.quantum;
   a.xvec = ((p->ldx & 7) == 0 && aligned16(p->x)) ? 1 : 0;
-  size_t smem = r.geom->ring_bytes();
-  bool pro = false;
+  *smem_extra = 0;
   if (nrm && nrm->h_in) {
     // the prologue holds N rows of x in shared memory and reads / writes 16-byte packets
     if (p->K != p->Kp || !nrm->norm_w || !aligned16(nrm->h_in) || !aligned16(nrm->norm_w) || (nrm->ldh & 7) ||
@@ -500,9 +688,7 @@ int launch_gemv(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* c
         (nrm->h_out && (!aligned16(nrm->h_out) || (nrm->ldho & 7) || nrm->h_out == nrm->h_in)) ||
         (nrm->xn_out && (!aligned16(nrm->xn_out) || (nrm->ldxo & 7))) || (nrm->tok && nrm->vocab < 1))
       return QE_ERR_ARG;
-    smem += (size_t)p->N * ((size_t)p->K * 2 + 16);
-    if (smem > 227 * 1024) return QE_ERR_ARG;  // caller runs qe_rmsnorm1p + qe_w4_gemv instead
-    pro = true;
+    *smem_extra = (size_t)p->N * ((size_t)p->K * 2 + 16);
     a.h_in = reinterpret_cast<const bf16*>(nrm->h_in);
     a.tok = nrm->tok;
     a.vocab = nrm->vocab;
@@ -519,11 +705,52 @@ int launch_gemv(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* c
     a.pf = reinterpret_cast<const unsigned char*>(nrm->prefetch);
     a.pf_bytes = nrm->prefetch_bytes;
   }
-  KernelFn fn = r.geom->fn[pro ? 1 : 0];
-  cudaError_t e = allow_smem(fn, smem);
-  if (e != cudaSuccess) return (int)e;
+  return 0;
+}
+
+int launch_chain(const qe_w4_params* const* ps, const qe_w4_norm* const* nrms, int njobs, const qe_w4_cfg* cfg,
+                 int* gridbar, cudaStream_t stream) {
+  if (!ps || !cfg || njobs < 1 || njobs > kMaxJobs || (njobs > 1 && !gridbar)) return QE_ERR_ARG;
+  ChainArgs c{};
+  c.njobs = njobs;
+  c.gbar = gridbar;
+  const Geometry* geom = nullptr;
+  size_t extra = 0;
+  int grid = 1;
+  for (int j = 0; j < njobs; ++j) {
+    Resolved r{};
+    size_t e = 0;
+    const int rc = make_job(ps[j], nrms ? nrms[j] : nullptr, cfg, c.job[j], r, &e);
+    if (rc) return rc;
+    geom = r.geom;
+    extra = std::max(extra, e);
+    grid = std::max(grid, r.plan.grid_x);
+  }
+  const size_t smem = geom->ring_bytes() + extra;
+  const long limit = dynamic_smem_limit(geom->fn);
+  if (limit < 0) return (int)-limit;
+  if ((long)smem > limit) return QE_ERR_ARG;  // prologue rows do not fit: run qe_rmsnorm1p + qe_w4_gemv
   const bool pdl = cfg->pdl && pdl_launch_enabled() && pdl_trigger_enabled();
-  return (int)launch(fn, dim3(r.plan.grid_x, 1, 1), dim3(r.plan.threads), smem, stream, pdl, a);
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(grid, 1, 1);
+  lc.blockDim = dim3(geom->nw * 32, 1, 1);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = stream;
+  cudaLaunchAttribute at[2];
+  int na = 0;
+  if (pdl) {
+    at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (njobs > 1) {  // the blocks wait for each other: they must all be resident
+    at[na].id = cudaLaunchAttributeCooperative;
+    at[na].val.cooperative = 1;
+    ++na;
+  }
+  lc.attrs = at;
+  lc.numAttrs = na;
+  return (int)cudaLaunchKernelEx(&lc, geom->fn, c);
 }
 
 }  // namespace
@@ -570,11 +797,16 @@ extern "C" int qe_w4_clear_error(void) {
 }
 
 extern "C" int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream) {
-  return launch_gemv(p, nullptr, cfg, (cudaStream_t)stream);
+  return launch_chain(&p, nullptr, 1, cfg, nullptr, (cudaStream_t)stream);
 }
 
 extern "C" int qe_w4_gemv_ex(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg, void* stream) {
-  return launch_gemv(p, nrm, cfg, (cudaStream_t)stream);
+  return launch_chain(&p, &nrm, 1, cfg, nullptr, (cudaStream_t)stream);
+}
+
+extern "C" int qe_w4_gemv_chain(const qe_w4_params* const* p, const qe_w4_norm* const* nrm, int njobs,
+                                const qe_w4_cfg* cfg, int* gridbar, void* stream) {
+  return launch_chain(p, nrm, njobs, cfg, gridbar, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------

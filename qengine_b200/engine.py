@@ -93,10 +93,40 @@ class W4Linear:
 
     def after_norm(self, h, delta, w, eps, p, out, **kw):
         """out = p(RMSNorm1p(h + delta)) in one launch (see `_w4.gemv_fused`)."""
-        kw = {**self.kw, **kw}
-        if out.shape[0] > 7:  # eight rows of x only fit beside the smaller ring geometry
-            kw.setdefault("unroll", 2)
-        _w4.gemv_fused(h, delta, w, eps, p.qw, p.scales, out, p.M, swiglu=p.gate_up, **kw)
+        _w4.gemv_fused(h, delta, w, eps, p.qw, p.scales, out, p.M, swiglu=p.gate_up, **{**self.kw, **kw})
+
+    # The same four operations as job descriptions, for `launch` below: the engine queues the
+    # GEMVs that follow one another without another kernel in between and runs them as one chain.
+    @staticmethod
+    def job(x, p, out, prefetch=None):
+        return _w4.job(x, p.qw, p.scales, out, p.M, swiglu=p.gate_up, prefetch=prefetch)
+
+    @staticmethod
+    def job_partial(x, p, out32):
+        return _w4.job(x, p.qw, p.scales, out32, p.M, allow_f32_out=True)
+
+    @staticmethod
+    def job_after_norm(h, delta, w, eps, p, out, **kw):
+        return _w4.job_fused(h, delta, w, eps, p.qw, p.scales, out, p.M, swiglu=p.gate_up, **kw)
+
+    def launch(self, jobs, **kw):
+        _w4.gemv_chain(jobs, **{**self.kw, **kw})
+
+
+class _AfterFlush:
+    """`_C` seen through the engine: any kernel other than a W4 GEMV first launches the GEMVs that
+    are still queued, so the stream order is the program order."""
+
+    def __init__(self, ops, flush):
+        self._ops, self._flush = ops, flush
+
+    def __getattr__(self, name):
+        fn = getattr(self._ops, name)
+
+        def call(*a, **kw):
+            self._flush()
+            return fn(*a, **kw)
+        return call
 
 
 # ----------------------------------------------------------------------------------------------
@@ -132,9 +162,9 @@ class _Residual:
             return ordered
         if ordered:
             with e._ordered_first_launch():
-                _C.embed(e.embed, tok, self.h)
+                e.K.embed(e.embed, tok, self.h)
         else:
-            _C.embed(e.embed, tok, self.h)
+            e.K.embed(e.embed, tok, self.h)
         return False
 
     def start_from_rows(self):
@@ -143,31 +173,41 @@ class _Residual:
     def owe(self, x, p, lin, prefetch=None):
         """A matrix split along K on the ranks: its result is added by the next norm."""
         e, n = self.e, self.n
+        w4 = isinstance(lin, W4Linear) and isinstance(p, W4Packed)
         if e.tp is None:
-            if prefetch is not None and isinstance(lin, W4Linear):
-                lin(x, p, e.mo[:n], prefetch=prefetch)
+            if w4:
+                e._gemv(lin.job(x, p, e.mo[:n], prefetch=prefetch))
             else:
+                e._flush()
                 lin(x, p, e.mo[:n])
         else:
-            lin.partial(x, p, e.part32[:n])
+            if w4:
+                e._gemv(lin.job_partial(x, p, e.part32[:n]))
+            else:
+                e._flush()
+                lin.partial(x, p, e.part32[:n])
             if e.tp.transport == "nccl":
+                e._flush()
                 e.tp.all_gather(e.parts[n], e.part32[:n])
         self.owed = True
 
     def zero_then_owe(self, x, p, lin):
         """Tensor parallel only: the stream starts as the sum of the ranks' partial rows."""
+        self.e._flush()
         self.h.zero_()
         self.owe(x, p, lin)
 
     def _norm(self, w, out):
         e, n = self.e, self.n
+        K = e.K  # kernels other than the W4 GEMV: the queue of GEMVs is flushed first
         if not self.owed:
-            _C.rmsnorm1p(self.h, None, w, out, e.cfg.eps)
+            K.rmsnorm1p(self.h, None, w, out, e.cfg.eps)
         elif e.tp is None:
-            _C.rmsnorm1p(self.h, e.mo[:n], w, out, e.cfg.eps)
+            K.rmsnorm1p(self.h, e.mo[:n], w, out, e.cfg.eps)
         elif e.tp.transport == "nccl":
-            _C.rmsnorm1p_parts(self.h, e.parts[n], w, out, e.cfg.eps)
+            K.rmsnorm1p_parts(self.h, e.parts[n], w, out, e.cfg.eps)
         else:
+            e._flush()
             e.tp.exchange_norm(self.h, e.part32[:n], w, out, e.cfg.eps)
         self.owed = False
 
@@ -175,25 +215,26 @@ class _Residual:
         """out = p(norm(h + owed)); keep_normed optionally receives the normed rows. ordered: this
         is the launch that opens a pass (no programmatic overlap with the previous pass)."""
         e, n = self.e, self.n
-        fused = e.fuse and isinstance(p, W4Packed) and isinstance(lin, W4Linear)
-        if fused:
-            kw = {"pdl": False} if ordered else {}
+        w4 = isinstance(p, W4Packed) and isinstance(lin, W4Linear)
+        if e.fuse and w4:
             if self.tok is not None:
-                lin.after_norm(e.embed, None, w, e.cfg.eps, p, out, tok=self.tok, h_out=self.h,
-                               xn_out=keep_normed, **kw)
+                j = lin.job_after_norm(e.embed, None, w, e.cfg.eps, p, out, tok=self.tok, h_out=self.h,
+                                       xn_out=keep_normed)
                 self.tok = None
             elif self.owed:
-                lin.after_norm(self.h, e.mo[:n], w, e.cfg.eps, p, out, h_out=self.spare, xn_out=keep_normed, **kw)
+                j = lin.job_after_norm(self.h, e.mo[:n], w, e.cfg.eps, p, out, h_out=self.spare, xn_out=keep_normed)
                 self.h, self.spare = self.spare, self.h
             else:
-                lin.after_norm(self.h, None, w, e.cfg.eps, p, out, xn_out=keep_normed, **kw)
+                j = lin.job_after_norm(self.h, None, w, e.cfg.eps, p, out, xn_out=keep_normed)
             self.owed = False
+            e._gemv(j, ordered=ordered)
             return
         xn = keep_normed if keep_normed is not None else self.xn
         self._norm(w, xn)
-        if isinstance(p, W4Packed):
-            (lin.gate_up if p.gate_up else lin)(xn, p, out)
+        if w4:
+            e._gemv(lin.job(xn, p, out))
         else:
+            e._flush()
             lin(xn, p, out)
 
 
@@ -204,7 +245,7 @@ class Engine:
 
     def __init__(self, cfg: Config, weights: dict, max_len: int = 4096, linear=None, device="cuda",
                  mtp: bool = True, attn_splits: int | None = None, draft_vocab: int | None = None, tp=None,
-                 fuse: bool | None = None, prefetch: bool | None = None):
+                 fuse: bool | None = None, prefetch: bool | None = None, chain: bool | None = None):
         """weights: dict in the fused layout (qengine_b200.synth.build_model), already on `device`.
         tp: a qengine_b200.tp.TPGroup for tensor parallelism; `cfg` then still describes the whole
         model and `weights` is this rank's shard (qengine_b200.tp.shard_model).
@@ -213,7 +254,9 @@ class Engine:
         token ids (pruned draft head through the argmax id map); verify keeps the full head.
         fuse: run residual add + RMSNorm inside the following W4 GEMV launch (default: on for a
         single GPU; under tensor parallelism the norm is fused with the exchange instead).
-        prefetch: let each GEMV ask L2 for the weights of the next one (default: QE_PREFETCH=1)."""
+        prefetch: let each GEMV ask L2 for the weights of the next one (default: QE_PREFETCH=1).
+        chain: launch runs of consecutive W4 GEMVs as one cooperative kernel (default on;
+        QE_CHAIN=0 turns it off)."""
         self.tp, self.vocab_full, self.vocab_base = tp, cfg.vocab, 0
         if tp is not None:
             from .tp import local_config
@@ -224,6 +267,7 @@ class Engine:
         self.linear = linear or W4Linear()
         self.fuse = (tp is None) if fuse is None else (bool(fuse) and tp is None)
         self.prefetch = (os.environ.get("QE_PREFETCH", "0") == "1") if prefetch is None else bool(prefetch)
+        self.chain = (os.environ.get("QE_CHAIN", "1") == "1") if chain is None else bool(chain)
         self.prefetch_words = int(os.environ.get("QE_PREFETCH_MB", "48")) * (1 << 20) // 4  # int32 words of a hint
         self.embed, self.final_norm = weights["embed"], weights["final_norm"]
         self.lm_head = weights["lm_head"]
@@ -239,6 +283,8 @@ class Engine:
             self._make_draft_head(draft_vocab)
         self._make_buffers()
         self.graphs, self.graph_kernels = {}, {}
+        self._q, self._q_ordered = [], False  # W4 GEMVs waiting to be launched as one chain
+        self.K = _AfterFlush(_C, self._flush)
         self.start_pos = 0      # positions [0, start_pos) hold a pre-filled context (set_context)
         self.force_a = -1       # forced acceptance length of verify passes (< 0: off)
         self.truth = torch.zeros(1, dtype=I32, device=self.dev)
@@ -364,6 +410,30 @@ class Engine:
         self.reset()
 
     # -- the pass, as the kernels it launches ----------------------------------------------------
+    def _gemv(self, job, ordered=False):
+        """Queue one W4 GEMV. GEMVs that follow one another with no other kernel in between (out
+        projection -> gate/up -> down -> next block's in_proj, once the norms ride in the GEMV
+        prologues) are launched together as one chain: see `_w4.gemv_chain`."""
+        if not self.chain:
+            self.linear.launch([job], **({"pdl": False} if ordered else {}), **self._ring_kw(job))
+            return
+        self._q.append(job)
+        self._q_ordered = self._q_ordered or ordered
+        if len(self._q) == 4:
+            self._flush()
+
+    def _ring_kw(self, job):
+        # eight rows of prologue input only fit beside the smallest weight ring (same results)
+        return {"unroll": 1} if job.p.N > 7 and job.nrm is not None and job.nrm.h_in else {}
+
+    def _flush(self):
+        if self._q:
+            kw = {"pdl": False} if self._q_ordered else {}
+            for j in self._q:
+                kw.update(self._ring_kw(j))
+            self.linear.launch(self._q, **kw)
+            self._q, self._q_ordered = [], False
+
     @contextmanager
     def _ordered_first_launch(self):
         """Programmatic dependent launch lets a kernel's prologue run before its predecessor has
@@ -383,7 +453,7 @@ class Engine:
             pr = self.proj[:n, :c.gdn_proj_rows]
             a0, a1 = c.conv_dim, c.conv_dim + c.value_dim
             out = self.mix[:n, :c.value_dim]
-            _C.gdn_step_n(pr[:, :a0], pr[:, a0:a1], pr[:, a1:a1 + c.hv], pr[:, a1 + c.hv:], L["ring"],
+            self.K.gdn_step_n(pr[:, :a0], pr[:, a0:a1], pr[:, a1:a1 + c.hv], pr[:, a1 + c.hv:], L["ring"],
                           L["conv_w"], L["A_log"], L["dt_bias"], L["norm_w"], L["S"], L["st_k"], L["st_v"],
                           L["st_g"], self.ctl, out, c.hk, c.eps, q=self.GDN_Q)
             return out
@@ -391,10 +461,10 @@ class Engine:
         nq = c.hq * 2 * c.head_dim
         nk = nq + c.hkv * c.head_dim
         qg, q = pr[:, :nq], self.q[:n]
-        _C.attn_prep(qg, pr[:, nq:nk], pr[:, nk:], L["q_norm"], L["k_norm"], self.inv_freq, pos, q,
+        self.K.attn_prep(qg, pr[:, nq:nk], pr[:, nk:], L["q_norm"], L["k_norm"], self.inv_freq, pos, q,
                      L["kc"], L["vc"], c.eps)
         out = self.mix[:n, :c.hq * c.head_dim]
-        _C.attn_decode(q, L["kc"], L["vc"], pos, qg, self.part_o, self.part_ml, out)
+        self.K.attn_decode(q, L["kc"], L["vc"], pos, qg, self.part_o, self.part_ml, out)
         return out
 
     def _block(self, L, R: _Residual, pos, ordered=False):
@@ -415,20 +485,20 @@ class Engine:
             if self.gu is None:
                 self.gu = torch.zeros(NMAX, 2 * self.cfg.inter, dtype=BF16, device=self.dev)
             R.through(L["post_norm"], gu, self.gu[:n], lin)
-            _C.swiglu(self.gu[:n], self.act[:n])
+            self.K.swiglu(self.gu[:n], self.act[:n])
         R.owe(self.act[:n], L["down"], lin)
 
     def _greedy(self, logits, n, out, idmap=None):
         """Greedy token per row, lowest id on ties; vocabulary shards exchange (value, id)."""
         ws_v, ws_i = self.am_v[:n * 256], self.am_i[:n * 256]
         if self.tp is None:
-            _C.argmax(logits, ws_v, ws_i, out, idmap)
+            self.K.argmax(logits, ws_v, ws_i, out, idmap)
             return
-        _C.argmax_v(logits, ws_v, ws_i, self.cand_i, self.cand_v, self.vocab_base, idmap)
+        self.K.argmax_v(logits, ws_v, ws_i, self.cand_i, self.cand_v, self.vocab_base, idmap)
         if self.tp.transport == "nccl":
             self.tp.all_gather(self.all_v[n], self.cand_v[:n])
             self.tp.all_gather(self.all_i[n], self.cand_i[:n])
-            _C.argmax_merge(self.all_v[n], self.all_i[n], out)
+            self.K.argmax_merge(self.all_v[n], self.all_i[n], out)
         else:
             self.tp.exchange_argmax(self.cand_v, self.cand_i, n, out)
 
@@ -439,7 +509,7 @@ class Engine:
         ordered = True
         if force:
             with self._ordered_first_launch():
-                _C.force_drafts(self.in_tok, self.ctl, self.truth, self.force_a, n - 1, self.vocab_full)
+                self.K.force_drafts(self.in_tok, self.ctl, self.truth, self.force_a, n - 1, self.vocab_full)
             ordered = False
         ordered = R.start_from_tokens(self.in_tok, ordered)
         for L in self.layers:
@@ -448,9 +518,9 @@ class Engine:
         R.through(self.final_norm, self.lm_head, self.logits[:n], self.lm_lin, keep_normed=self.hid[:n])
         self._greedy(self.logits[:n], n, self.am)
         if then_commit_k is None:
-            _C.accept(self.in_tok, self.am, n, self.ctl, self.next_tok, self.log)
+            self.K.accept(self.in_tok, self.am, n, self.ctl, self.next_tok, self.log)
         else:
-            _C.accept_commit(self.in_tok, self.am, n, self.ctl, self.next_tok, self.log, self.drafts, then_commit_k)
+            self.K.accept_commit(self.in_tok, self.am, n, self.ctl, self.next_tok, self.log, self.drafts, then_commit_k)
 
     def _draft_rows(self, n, hid, tok):
         """MTP rows: hid [n, H] (main model, after its final norm) and the tokens that follow
@@ -459,12 +529,16 @@ class Engine:
         M, c, H = self.mtp, self.cfg, self.cfg.hidden
         cat = self.cat[:n]
         R = _Residual(self, n, self.mh, self.mh2, self.xn)
-        _C.embed(self.embed, tok, R.h)
-        _C.rmsnorm1p(R.h, None, M["pre_e"], cat[:, :H], c.eps)
-        _C.rmsnorm1p(hid, None, M["pre_h"], cat[:, H:], c.eps)
+        self.K.embed(self.embed, tok, R.h)
+        self.K.rmsnorm1p(R.h, None, M["pre_e"], cat[:, :H], c.eps)
+        self.K.rmsnorm1p(hid, None, M["pre_h"], cat[:, H:], c.eps)
         R.start_from_rows()
         if self.tp is None:
-            self.linear(cat, M["fc"], R.h)
+            if isinstance(M["fc"], W4Packed) and isinstance(self.linear, W4Linear):
+                self._gemv(self.linear.job(cat, M["fc"], R.h))
+            else:
+                self._flush()
+                self.linear(cat, M["fc"], R.h)
         else:  # fc is split along K: this rank multiplies its slice of [e | h]
             w = 2 * H // self.tp.size
             R.zero_then_owe(cat[:, self.tp.rank * w:(self.tp.rank + 1) * w], M["fc"], self.linear)
@@ -483,23 +557,27 @@ class Engine:
         k - 1 chained single-row drafts; commit."""
         if not mtp_rows:
             self._trunk(n, force, then_commit_k=k)
+            self._flush()
             return
         self._trunk(n, force)
         stream = torch.cuda.current_stream().cuda_stream
         if self.l2_win:
+            self._flush()
             lib.qe_stream_access_window(self.l2_win[0], self.l2_win[1], 1.0, stream)
-        _C.mtp_select(self.ctl, self.mpos, -1)
+        self.K.mtp_select(self.ctl, self.mpos, -1)
         self._draft_rows(n, self.hid[:n], self.next_tok)
         if k > 0:
-            _C.mtp_select(self.ctl, self.mpos, 0, self.mout[:n], self.chain_h, self.mtp_am, self.drafts[:1])
+            self.K.mtp_select(self.ctl, self.mpos, 0, self.mout[:n], self.chain_h, self.mtp_am, self.drafts[:1])
         for j in range(1, k):
             if j > 1:
-                _C.mtp_select(self.ctl, self.mpos, j - 1)
+                self.K.mtp_select(self.ctl, self.mpos, j - 1)
             self._draft_rows(1, self.chain_h, self.drafts[j - 1:j])
-            _C.chain_draft(self.mtp_am, self.drafts[j:j + 1], self.mout[:1], self.chain_h)
+            self.K.chain_draft(self.mtp_am, self.drafts[j:j + 1], self.mout[:1], self.chain_h)
         if self.l2_win:
+            self._flush()
             lib.qe_stream_access_window(0, 0, 0.0, stream)
-        _C.commit(self.ctl, self.in_tok, self.am, self.drafts, k)
+        self.K.commit(self.ctl, self.in_tok, self.am, self.drafts, k)
+        self._flush()
 
     # -- graphs ----------------------------------------------------------------------------------
     def graph(self, n, mtp_rows=False, k=0, force=False):

@@ -1,7 +1,7 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE's own Python modules
 (`qengine.reference`, `qengine.quant` from a checkout of manaspros/qengine) on CPU.
 
-    python tests/golden/make_golden.py [--reference /path/to/qengine]
+    python tests/golden/make_golden.py --reference /path/to/qengine
 
 The reference checkout is only needed to (re)generate; the tests read the committed files.
 Inputs are the seeded tiny hybrid model of qengine_b200.synth (4 layers, hidden 512, vocab 4096,
@@ -34,53 +34,16 @@ def fq_lin(x, w):
     return torch.nn.functional.linear(x.float(), w.float()).to(BF)
 
 
-def reference_named(D, cfg):
-    """Oracle-layout dense dict -> the reference's HF-style names (python/qengine/reference.py and
-    engine.py:307-331 fuse these; here the fusion is undone)."""
-    W = {"embed_tokens.weight": D["embed"], "norm.weight": D["final_norm"], "lm_head.weight": D["lm_head"]}
-
-    def put(L, p, kind):
-        W[p + "input_layernorm.weight"] = L["in_norm"]
-        W[p + "post_attention_layernorm.weight"] = L["post_norm"]
-        W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"] = L["gate"], L["up"]
-        W[p + "mlp.down_proj.weight"] = L["down"]
-        ip = L["in_proj"]
-        if kind == "linear_attention":
-            q = p + "linear_attn."
-            c0, c1 = cfg.conv_dim, cfg.conv_dim + cfg.value_dim
-            W[q + "in_proj_qkv.weight"], W[q + "in_proj_z.weight"] = ip[:c0], ip[c0:c1]
-            W[q + "in_proj_b.weight"], W[q + "in_proj_a.weight"] = ip[c1:c1 + cfg.hv], ip[c1 + cfg.hv:]
-            W[q + "out_proj.weight"] = L["out"]
-            W[q + "conv1d.weight"], W[q + "A_log"] = L["conv_w"], L["A_log"]
-            W[q + "dt_bias"], W[q + "norm.weight"] = L["dt_bias"], L["norm_w"]
-        else:
-            q = p + "self_attn."
-            q0 = cfg.hq * 2 * cfg.head_dim
-            k1 = q0 + cfg.hkv * cfg.head_dim
-            W[q + "q_proj.weight"], W[q + "k_proj.weight"], W[q + "v_proj.weight"] = ip[:q0], ip[q0:k1], ip[k1:]
-            W[q + "o_proj.weight"] = L["out"]
-            W[q + "q_norm.weight"], W[q + "k_norm.weight"] = L["q_norm"], L["k_norm"]
-
-    for l, L in enumerate(D["layers"]):
-        put(L, f"layers.{l}.", L["type"])
-    if D.get("mtp"):
-        M = D["mtp"]
-        put(M, "mtp.layers.0.", "full_attention")
-        W["mtp.fc.weight"], W["mtp.norm.weight"] = M["fc"], M["norm"]
-        W["mtp.pre_fc_norm_embedding.weight"], W["mtp.pre_fc_norm_hidden.weight"] = M["pre_e"], M["pre_h"]
-    return W
-
-
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of manaspros/qengine")
     a = ap.parse_args()
     sys.path.insert(0, str(Path(a.reference) / "python"))
     from qengine import quant as RQ
     from qengine import reference as R
 
     from qengine_b200 import synth
-    from util import dense_model
+    from oracle.convert import dense_model, reference_named
 
     torch.manual_seed(0)
     torch.set_num_threads(1)

@@ -410,3 +410,78 @@ def test_prefetch_hint_changes_nothing(api):
     a = api["gemv"](x, p)
     b = api["gemv"](x, p, prefetch=nxt.qw)
     assert torch.equal(bits(a), bits(b))
+
+
+# ---------------------------------------------------------------------------------------------
+# Chains: several dependent GEMVs as one cooperative launch
+# ---------------------------------------------------------------------------------------------
+def _block_tensors(api, Hh, Ii, Vd, seed):
+    """out-projection, gate/up, down and the next in_proj of a decoder block of width Hh."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    mk = lambda M, K, s: api["q"](rand_w(M, K, seed=s))
+    W = dict(out=mk(Hh, Vd, seed + 1), gu=api["qgu"](rand_w(Ii, Hh, seed=seed + 2), rand_w(Ii, Hh, seed=seed + 3)),
+             down=mk(Hh, Ii, seed + 4), inp=mk(3 * Hh + 32, Hh, seed + 5))
+    W["n1"] = (torch.randn(Hh, generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+    W["n2"] = (torch.randn(Hh, generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+    return W
+
+
+def _run_block(api, W, mix, h, n, chained, **kw):
+    """The four GEMVs between two mixers, either as one chain or one launch each."""
+    w4 = api["w4"]
+    Hh, Ii = W["down"].M, W["gu"].M
+    z = lambda *sh: torch.zeros(*sh, dtype=torch.bfloat16, device=DEV)
+    mo, h2, h3, act, proj, xn = z(n, Hh), z(n, Hh), z(n, Hh), z(n, Ii), z(n, W["inp"].M), z(n, Hh)
+    jobs = [
+        w4.job(mix[:n], W["out"].qw, W["out"].scales, mo, Hh),
+        w4.job_fused(h[:n], mo, W["n1"], 1e-6, W["gu"].qw, W["gu"].scales, act, Ii, h_out=h2, swiglu=True),
+        w4.job(act, W["down"].qw, W["down"].scales, mo, Hh),
+        w4.job_fused(h2, mo, W["n2"], 1e-6, W["inp"].qw, W["inp"].scales, proj, W["inp"].M, h_out=h3, xn_out=xn),
+    ]
+    if chained:
+        w4.gemv_chain(jobs, **kw)
+    else:
+        for j in jobs:
+            w4.gemv_chain([j], **kw)
+    torch.cuda.synchronize()
+    return [bits(t) for t in (mo, h2, h3, act, proj, xn)]
+
+
+@pytest.mark.parametrize("Hh,Ii,Vd", [(512, 1536, 512), (H, I, 6144)])
+def test_chain_equals_separate_launches(api, Hh, Ii, Vd):
+    W = _block_tensors(api, Hh, Ii, Vd, seed=90)
+    mix, h = rand_x(8, Vd, seed=95), rand_x(8, Hh, seed=96)
+    for n, kw in ((1, {}), (5, {}), (8, dict(unroll=1)), (3, dict(warps=16)), (2, dict(min_units=64))):
+        want = _run_block(api, W, mix, h, n, chained=False, **kw)
+        for rep in range(3):  # the grid barrier's generation counter carries over from launch to launch
+            got = _run_block(api, W, mix, h, n, chained=True, **kw)
+            for a, b, name in zip(got, want, ("mo", "h2", "h3", "act", "proj", "xn")):
+                assert torch.equal(a, b), f"n={n} {kw} rep {rep}: {name} differs between chain and separate launches"
+    assert api["w4"].ring_error() == 0
+
+
+def test_chain_in_a_cuda_graph(api):
+    w4 = api["w4"]
+    W = _block_tensors(api, 512, 1536, 512, seed=97)
+    mix, h = rand_x(4, 512, seed=98), rand_x(4, 512, seed=99)
+    want = _run_block(api, W, mix, h, 4, chained=True)  # eager run: also sizes scratch and barrier words
+    z = lambda *sh: torch.zeros(*sh, dtype=torch.bfloat16, device=DEV)
+    mo, h2, h3, act, proj, xn = z(4, 512), z(4, 512), z(4, 512), z(4, 1536), z(4, W["inp"].M), z(4, 512)
+    jobs = [
+        w4.job(mix, W["out"].qw, W["out"].scales, mo, 512),
+        w4.job_fused(h, mo, W["n1"], 1e-6, W["gu"].qw, W["gu"].scales, act, 1536, h_out=h2, swiglu=True),
+        w4.job(act, W["down"].qw, W["down"].scales, mo, 512),
+        w4.job_fused(h2, mo, W["n2"], 1e-6, W["inp"].qw, W["inp"].scales, proj, W["inp"].M, h_out=h3, xn_out=xn),
+    ]
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        w4.gemv_chain(jobs)
+        w4.gemv_chain(jobs[:2])
+    for _ in range(5):
+        for t in (mo, h2, h3, act, proj, xn):
+            t.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        # the trailing 2-job chain rewrites mo / act / h2 with the same values
+        for a, b in zip([bits(t) for t in (h2, h3, act, proj, xn)], want[1:]):
+            assert torch.equal(a, b)
