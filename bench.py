@@ -10,16 +10,18 @@ Engine.generate() with the prompt coming from host memory and the tokens read ba
 prefill included; `roofline` = the W4 GEMV kernel timed alone on this model's own matrices in
 token order (every matrix distinct, 13 GB, far larger than L2) against the measured HBM copy
 bandwidth; `mtp_k4` = speculative decoding with k = 4 at forced acceptance lengths 0..4 and natural
-acceptance; `cpu_baseline` = the CPU oracle (port of the reference torch path) timed on a bounded
-sample on the host cores.
+acceptance; `cpu_baseline` = whole tokens of the same model shape on the host cores through the
+reference's own torch path (oracle/_ref, else the oracle's restatement of it); at N > 1
+`tp_parity` compares the tensor-parallel engine's logits with the single-GPU engine's.
 
---impl reference times that CPU port as an arm of its own (rank 0 only).
+--impl reference times that CPU path as an arm of its own (rank 0 only).
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -33,11 +35,19 @@ sys.path.insert(0, str(ROOT))
 
 PROMPT_LEN, N_NEW = 128, 1024
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
-# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of w4_warp_ring_kernel, from the
-# ncu capture summarised in profiles/w4_warp_ring_kernel_27b_shapes.md: 16.28 / 16.22, 97.28 / 91.91
-# and 46.06 / 45.96 MB on out_proj, gate_up and down (the excess on gate_up is partial-tile scratch
-# written back from L2). Scaled to an average launch of the 257-launch sequence below.
-NCU_TRAFFIC_RATIO = (16.28 + 97.28 + 46.06) / (16.22 + 91.91 + 45.96)
+WORKLOAD = "27B-shape W4A16 plain greedy decode ({layers} layers, hidden 5120, vocab 248320), " \
+           "{prompt}-token seeded prompt, {tokens} tokens per step"
+
+
+def ncu_traffic_ratio():
+    """DRAM bytes / algorithmic bytes of the W4 kernel from the kept ncu summary (a line
+    `traffic_ratio: <float>` in profiles/w4_chain_kernel_27b_shapes.md); None if there is none."""
+    f = ROOT / "profiles" / "w4_chain_kernel_27b_shapes.md"
+    if f.exists():
+        m = re.search(r"traffic_ratio:\s*([0-9.]+)", f.read_text())
+        if m:
+            return float(m.group(1))
+    return None
 
 
 def measured_peak():
@@ -102,65 +112,109 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------------------------
-# CPU arm: the oracle (port of the reference torch path) on a bounded sample of the workload
+# CPU arm: whole tokens of the model shape on the host cores, through the reference's torch path
 # ----------------------------------------------------------------------------------------------
-def cpu_reference_sample(steps: int, warmup: int, head_frac: int = 8):
-    """One step = one token through one DeltaNet layer, one attention layer and 1/head_frac of the
-    lm_head of the 27B shape, on dense fp32 dequantised weights; per-token time of the whole model
-    = 48 t_gdn + 16 t_attn + head_frac t_head. Returns (tok_s, cores, description)."""
+def _dense_on_grid(rows, K, g, scale_std):
+    """Dense fp32 weights on the int4 grid: what dequantising a packed matrix of uniform codes and
+    |N(0,1)| * scale_std group scales yields, built without the detour through the packer."""
     import torch
-    sys.path.insert(0, str(ROOT / "tests"))
+    codes = torch.randint(0, 16, (rows, K // 128, 128), generator=g, dtype=torch.int8)
+    scales = (torch.randn(rows, K // 128, 1, generator=g).abs() * scale_std).to(torch.float16).float()
+    return ((codes.float() - 8.0) * scales).view(rows, K)
+
+
+def cpu_reference_tokens(steps: int, warmup: int, layers: int = 64, distinct: int = 4, vocab: int | None = None):
+    """Times `steps` whole decode tokens (after `warmup`) of the 27B-shape model on the host cores
+    with all host threads. The dense fp32 model would be 108 GB, so the `layers` layers cycle
+    through `distinct` distinct weight sets (3 DeltaNet + 1 attention: 6 GB, far beyond any CPU
+    cache, so the memory traffic of a token is that of the full model); every layer keeps its own
+    recurrent state and KV cache. Uses the reference's own decode_step with its fake-quant linear
+    when oracle/_ref has been built, else the oracle's restatement.
+    Returns (tok_s, threads, kind, sample description, seconds per token)."""
+    import torch
+    from oracle import build_ref
     from oracle import model as OM
+    from oracle.convert import oracle_config, reference_named
     from qengine_b200 import synth
-    from util import dequant_oracle, oracle_config
 
-    cfg = synth.qwen27b_config(layers=4)  # layers 0..2 DeltaNet, 3 attention: one of each is used
-    ocfg = oracle_config(cfg)
-    S = synth._Seeds(0, "cpu")
+    torch.set_num_threads(os.cpu_count() or 1)  # torchrun exports OMP_NUM_THREADS=1
+    cfg = synth.qwen27b_config(layers=layers)
+    if vocab:
+        cfg.vocab = vocab
+    g = torch.Generator().manual_seed(1)
+    H, I = cfg.hidden, cfg.inter
 
-    def dense(L):
-        D = {k: v for k, v in L.items() if not hasattr(v, "qw")}
-        for k in ("in_proj", "out", "down"):
-            D[k] = dequant_oracle(L[k])
-        D["gate"], D["up"] = dequant_oracle(L["gate_up"])
+    def small(shape, std=1.0, mean=0.0):
+        return (torch.randn(*shape, generator=g) * std + mean).to(torch.bfloat16)
+
+    def dense_layer(kind):
+        D = {"type": kind, "in_norm": small((H,), 0.1), "post_norm": small((H,), 0.1)}
+        if kind == "linear_attention":
+            D["in_proj"] = _dense_on_grid(cfg.gdn_proj_rows, H, g, 0.01)
+            D["out"] = _dense_on_grid(H, cfg.value_dim, g, 0.01)
+            D["conv_w"] = small((cfg.conv_dim, 1, cfg.conv_k), 0.5)
+            D["A_log"] = (torch.rand(cfg.hv, generator=g) * 5.7 - 3.0).to(torch.bfloat16)
+            D["dt_bias"], D["norm_w"] = small((cfg.hv,)), small((cfg.dv,), 0.2, 1.0)
+        else:
+            D["in_proj"] = _dense_on_grid(cfg.attn_proj_rows, H, g, 0.01)
+            D["out"] = _dense_on_grid(H, cfg.hq * cfg.head_dim, g, 0.01)
+            D["q_norm"], D["k_norm"] = small((cfg.head_dim,), 0.3), small((cfg.head_dim,), 0.3)
+        D["gate"], D["up"] = _dense_on_grid(I, H, g, 0.01), _dense_on_grid(I, H, g, 0.01)
+        D["down"] = _dense_on_grid(H, I, g, 0.01)
         return D
 
-    Lg = dense(synth._layer(cfg, "linear_attention", S, 0.01))
-    La = dense(synth._layer(cfg, "full_attention", S, 0.01))
-    head = dequant_oracle(synth.random_w4(cfg.vocab // head_frac, cfg.hidden, S.gen(), "cpu", 0.01))
-    st = OM.State(ocfg, 256, with_mtp=False)
-    g = torch.Generator().manual_seed(3)
-    h = torch.randn(cfg.hidden, generator=g).to(torch.bfloat16)
-    tg, ta, th = [], [], []
-    for i in range(warmup + steps):
-        t0 = time.perf_counter()
-        OM.decoder_layer(h, Lg, st, 0, i, ocfg)
-        t1 = time.perf_counter()
-        OM.decoder_layer(h, La, st, 3, i, ocfg)
-        t2 = time.perf_counter()
-        OM.lin(h, head)
-        t3 = time.perf_counter()
-        if i >= warmup:
-            tg.append(t1 - t0); ta.append(t2 - t1); th.append(t3 - t2)
-    per_tok = 48 * statistics.mean(tg) + 16 * statistics.mean(ta) + head_frac * statistics.mean(th)
-    desc = (f"{steps} tokens through 1 DeltaNet layer + 1 attention layer + 1/{head_frac} of the lm_head at the "
-            f"27B shape (dense fp32 dequantised weights), scaled to 48 + 16 layers + full head")
-    return 1.0 / per_tok, torch.get_num_threads(), desc, per_tok
+    sets = [dense_layer(cfg.layer_types[i]) for i in range(min(distinct, layers))]
+    D = {"embed": small((cfg.vocab, H)), "final_norm": small((H,), 0.1),
+         "lm_head": _dense_on_grid(cfg.vocab, H, g, 0.01),
+         "layers": [sets[l % len(sets)] for l in range(layers)], "mtp": None}
+    ref = build_ref.load()
+    ocfg = oracle_config(cfg)
+    if ref is not None:
+        R, _ = ref
+        rcfg = R.Config(hidden=cfg.hidden, layers=cfg.layers, inter=cfg.inter, vocab=cfg.vocab, eps=cfg.eps,
+                        layer_types=cfg.layer_types, hq=cfg.hq, hkv=cfg.hkv, head_dim=cfg.head_dim,
+                        rope_theta=cfg.rope_theta, rotary_dim=cfg.rotary_dim, hk=cfg.hk, hv=cfg.hv, dk=cfg.dk,
+                        dv=cfg.dv, conv_k=cfg.conv_k, tied=False, mtp_layers=0)
+        Wn = reference_named(D, cfg)
+        st = R.State(rcfg, 64, device="cpu")
+        fq = lambda x, w: torch.nn.functional.linear(x.float(), w.float()).to(torch.bfloat16)
+        step = lambda tok: R.decode_step(Wn, st, tok, rcfg, lin=fq)
+        kind = "reference"
+    else:
+        st = OM.State(ocfg, 64, with_mtp=False)
+        step = lambda tok: OM.decode_step(D, st, tok, ocfg, fused_swiglu=False)[0]
+        kind = "port"
+    tok, times = 17, []
+    with torch.no_grad():
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            lg = step(tok)
+            tok = int(lg.float().argmax())
+            if i >= warmup:
+                times.append(time.perf_counter() - t0)
+    per_tok = statistics.mean(times)
+    desc = (f"{steps} whole tokens ({layers} layers + lm_head of {cfg.vocab} rows) of the 27B-shape model, dense fp32 "
+            f"weights on the int4 grid; the layers cycle through {len(sets)} distinct weight sets "
+            f"({sum(t.numel() for s_ in sets for t in s_.values() if hasattr(t, 'numel')) * 4 / 1e9:.1f} GB) because the "
+            f"whole dense model does not fit host memory; greedy, context <= {warmup + steps}")
+    return 1.0 / per_tok, torch.get_num_threads(), kind, desc, per_tok
 
 
 def run_reference_arm(a):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    tok_s, cores, desc, per_tok = cpu_reference_sample(max(1, a.steps), max(1, a.warmup))
+    tok_s, cores, kind, desc, per_tok = cpu_reference_tokens(max(1, a.steps), max(0, a.warmup), layers=a.layers,
+                                                              vocab=a.ref_vocab or None)
     line = {
         "impl": "reference", "metric": "batch-1 decode tok/s (plain)", "value": tok_s, "unit": "tok/s",
         "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": per_tok * 1e3,
         "higher_is_better": True, "scaling": "weak" if a.gpus == 1 else "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "27B-shape W4A16 plain greedy decode, 128-token prompt, 1,024 tokens",
+        "config": {"workload": WORKLOAD.format(layers=a.layers, prompt=a.prompt, tokens=a.tokens),
+                   "step": "one whole token on the host cores (bounded sample of the workload)",
                    "timing": "host wall clock, CPU only"},
-        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": desc},
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": kind, "sample": desc},
         "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }

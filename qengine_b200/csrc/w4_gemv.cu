@@ -39,6 +39,8 @@
 // alias h_in: other CTAs may still be reading h_in.
 //
 // Every mbarrier wait is bounded; on expiry the warp records g_w4_error, drains and leaves.
+#include <cuda/atomic>
+
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
@@ -118,8 +120,18 @@ template <int NW>
 __device__ __forceinline__ void norm_prologue(const GemvArgs& a, unsigned char* x_s, long pitch,
                                               float (*s_red)[NW], int tid) {
   constexpr int NT = NW * 32, RB = 4;  // rows are handled RB at a time (register budget)
+  constexpr int WP = 3;                 // norm-weight packets a thread keeps (K <= 8 * WP * NT)
   const int lane = tid & 31, warp = tid >> 5, N = a.o.N, npk = a.K >> 3;
   const bool writer = blockIdx.x == 0;
+  // the weight packets this thread needs in the second pass: requested now, so that their trip to
+  // L2 overlaps the one of the rows
+  const bool w_held = npk <= WP * NT;
+  uint4 wv[WP];
+#pragma unroll
+  for (int i = 0; i < WP; ++i) {
+    const int p = tid + i * NT;
+    if (w_held && p < npk) wv[i] = reinterpret_cast<const uint4*>(a.norm_w)[p];
+  }
 #pragma unroll 1
   for (int r0 = 0; r0 < N; r0 += RB) {
     float ss[RB];
@@ -189,9 +201,14 @@ __device__ __forceinline__ void norm_prologue(const GemvArgs& a, unsigned char* 
         inv[i] = rsqrtf(tot / (float)a.K + a.eps);
       }
     }
-    for (int p = tid; p < npk; p += NT) {  // same thread -> packet map as above: own data only
+    int pi = 0;
+    for (int p = tid; p < npk; p += NT, ++pi) {  // same thread -> packet map as above: own data only
       float g[8];
-      widen8(reinterpret_cast<const uint4*>(a.norm_w)[p], g);
+      uint4 wq = wv[0];
+      if (!w_held) wq = reinterpret_cast<const uint4*>(a.norm_w)[p];
+      else if (pi == 1) wq = wv[1];
+      else if (pi == 2) wq = wv[2];
+      widen8(wq, g);
 #pragma unroll
       for (int i = 0; i < RB; ++i) {
         const int r = r0 + i;
@@ -468,13 +485,14 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
       float* gm = a.ws + ((size_t)my_cta * 2 + pslot) * 128;
 #pragma unroll
       for (int k = 0; k < 4; ++k) __stcg(gm + k * 32 + lane, f[k]);
-      __threadfence();
-      __syncwarp();
+      __syncwarp();  // orders the 32 lanes' stores before lane 0's release
       int done = 0;
-      if (lane == 0) done = atomicAdd(a.counters + T, units) + units == G;
-      done = __shfl_sync(0xffffffffu, done, 0);
+      if (lane == 0) {
+        cuda::atomic_ref<int, cuda::thread_scope_device> arrivals(a.counters[T]);
+        done = arrivals.fetch_add(units, cuda::memory_order_acq_rel) + units == G;
+      }
+      done = __shfl_sync(0xffffffffu, done, 0);  // also orders lane 0's acquire before the loads below
       if (!done) return;
-      __threadfence();
       float sum[4] = {0.f, 0.f, 0.f, 0.f};
       const int q = a.quantum;
       const int c_lo = share_owner(total / q, nwk, (T * G) / q) / NW;
@@ -538,18 +556,19 @@ constexpr Geometry geometry() {
   return Geometry{w4_chain_kernel<NW, PERW, STAGES>, NW, PERW, STAGES};
 }
 // Selected by the reference's launch options. `warps`: 0 (auto) -> 20 warps per CTA, 16 -> 16,
-// 4 / 8 -> 8; variant 1 -> 24 warps. `unroll` picks the ring: 0 / 2 -> 3 stages of 2 units,
-// 4 -> 2 stages of 4 units, 1 -> 2 stages of 2 units (the smallest; leaves room for eight rows of
-// prologue input). Work is split by CTA size only, so every ring shape of one CTA size gives the
+// 4 / 8 -> 8; variant 1 -> 24 warps. `unroll` picks the ring: 2 -> 3 stages of 2 units, 4 -> 2
+// stages of 4 units, 1 -> 2 stages of 2 units (the smallest; leaves room for eight rows of
+// prologue input), 0 -> the deepest of the three that fits beside the prologue's rows. Work is split by CTA size only, so every ring shape of one CTA size gives the
 // same bits.
 const Geometry kGeoms[] = {geometry<20, 2, 3>(), geometry<20, 4, 2>(), geometry<20, 2, 2>(),
                            geometry<16, 2, 3>(), geometry<16, 4, 2>(), geometry<16, 2, 2>(),
                            geometry<8, 2, 3>(),  geometry<8, 4, 2>(),  geometry<8, 2, 2>(),
                            geometry<24, 2, 3>()};
 
-const Geometry& pick_geometry(const qe_w4_cfg& c) {
+// `ring` < 0: whatever `unroll` says (0 -> the 3 x 2 ring); 0..2: that ring of the chosen CTA size.
+const Geometry& pick_geometry(const qe_w4_cfg& c, int ring = -1) {
   if (c.variant == 1) return kGeoms[9];
-  const int ring = c.unroll == 4 ? 1 : c.unroll == 1 ? 2 : 0;
+  if (ring < 0) ring = c.unroll == 4 ? 1 : c.unroll == 1 ? 2 : 0;
   const int size = (c.warps == 4 || c.warps == 8) ? 2 : c.warps == 16 ? 1 : 0;
   return kGeoms[3 * size + ring];
 }
@@ -725,6 +744,17 @@ int launch_chain(const qe_w4_params* const* ps, const qe_w4_norm* const* nrms, i
     geom = r.geom;
     extra = std::max(extra, e);
     grid = std::max(grid, r.plan.grid_x);
+  }
+  // unroll = 0 (auto): the deepest ring that still leaves room for the prologue's rows. The split of
+  // the work depends on the CTA size only, so this choice never changes a result.
+  if (cfg->unroll == 0 && cfg->variant != 1) {
+    for (int ring : {1, 0, 2}) {
+      const Geometry& cand = pick_geometry(*cfg, ring);
+      const long lim = dynamic_smem_limit(cand.fn);
+      if (lim < 0) return (int)-lim;
+      geom = &cand;
+      if ((long)(cand.ring_bytes() + extra) <= lim) break;
+    }
   }
   const size_t smem = geom->ring_bytes() + extra;
   const long limit = dynamic_smem_limit(geom->fn);

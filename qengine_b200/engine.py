@@ -170,13 +170,13 @@ class _Residual:
     def start_from_rows(self):
         self.owed, self.tok = False, None
 
-    def owe(self, x, p, lin, prefetch=None):
+    def owe(self, x, p, lin):
         """A matrix split along K on the ranks: its result is added by the next norm."""
         e, n = self.e, self.n
         w4 = isinstance(lin, W4Linear) and isinstance(p, W4Packed)
         if e.tp is None:
             if w4:
-                e._gemv(lin.job(x, p, e.mo[:n], prefetch=prefetch))
+                e._gemv(lin.job(x, p, e.mo[:n]))
             else:
                 e._flush()
                 lin(x, p, e.mo[:n])
@@ -245,7 +245,7 @@ class Engine:
 
     def __init__(self, cfg: Config, weights: dict, max_len: int = 4096, linear=None, device="cuda",
                  mtp: bool = True, attn_splits: int | None = None, draft_vocab: int | None = None, tp=None,
-                 fuse: bool | None = None, prefetch: bool | None = None, chain: bool | None = None):
+                 fuse: bool | None = None, chain: bool | None = None):
         """weights: dict in the fused layout (qengine_b200.synth.build_model), already on `device`.
         tp: a qengine_b200.tp.TPGroup for tensor parallelism; `cfg` then still describes the whole
         model and `weights` is this rank's shard (qengine_b200.tp.shard_model).
@@ -254,9 +254,10 @@ class Engine:
         token ids (pruned draft head through the argmax id map); verify keeps the full head.
         fuse: run residual add + RMSNorm inside the following W4 GEMV launch (default: on for a
         single GPU; under tensor parallelism the norm is fused with the exchange instead).
-        prefetch: let each GEMV ask L2 for the weights of the next one (default: QE_PREFETCH=1).
-        chain: launch runs of consecutive W4 GEMVs as one cooperative kernel (default on;
-        QE_CHAIN=0 turns it off)."""
+        chain: launch runs of consecutive W4 GEMVs as one cooperative kernel with grid barriers
+        (default off, QE_CHAIN=1 turns it on: measured slower than one launch per GEMV under
+        programmatic dependent launch, whose hand-over costs about 1 us against 2.5 us for the
+        barrier)."""
         self.tp, self.vocab_full, self.vocab_base = tp, cfg.vocab, 0
         if tp is not None:
             from .tp import local_config
@@ -266,9 +267,7 @@ class Engine:
         self.cfg, self.max_len, self.dev = cfg, max_len, torch.device(device)
         self.linear = linear or W4Linear()
         self.fuse = (tp is None) if fuse is None else (bool(fuse) and tp is None)
-        self.prefetch = (os.environ.get("QE_PREFETCH", "0") == "1") if prefetch is None else bool(prefetch)
-        self.chain = (os.environ.get("QE_CHAIN", "1") == "1") if chain is None else bool(chain)
-        self.prefetch_words = int(os.environ.get("QE_PREFETCH_MB", "48")) * (1 << 20) // 4  # int32 words of a hint
+        self.chain = (os.environ.get("QE_CHAIN", "0") == "1") if chain is None else bool(chain)
         self.embed, self.final_norm = weights["embed"], weights["final_norm"]
         self.lm_head = weights["lm_head"]
         self.lm_lin = self.linear if isinstance(self.lm_head, W4Packed) else BF16Linear()
@@ -415,23 +414,16 @@ class Engine:
         projection -> gate/up -> down -> next block's in_proj, once the norms ride in the GEMV
         prologues) are launched together as one chain: see `_w4.gemv_chain`."""
         if not self.chain:
-            self.linear.launch([job], **({"pdl": False} if ordered else {}), **self._ring_kw(job))
+            self.linear.launch([job], **({"pdl": False} if ordered else {}))
             return
         self._q.append(job)
         self._q_ordered = self._q_ordered or ordered
         if len(self._q) == 4:
             self._flush()
 
-    def _ring_kw(self, job):
-        # eight rows of prologue input only fit beside the smallest weight ring (same results)
-        return {"unroll": 1} if job.p.N > 7 and job.nrm is not None and job.nrm.h_in else {}
-
     def _flush(self):
         if self._q:
-            kw = {"pdl": False} if self._q_ordered else {}
-            for j in self._q:
-                kw.update(self._ring_kw(j))
-            self.linear.launch(self._q, **kw)
+            self.linear.launch(self._q, **({"pdl": False} if self._q_ordered else {}))
             self._q, self._q_ordered = [], False
 
     @contextmanager
@@ -475,10 +467,7 @@ class Engine:
         R.through(L["in_norm"], L["in_proj"], self.proj[:n, :width], lin, ordered=ordered)
         mixed = self._mixer(L, n, pos)
         gu = L["gate_up"]
-        # While the mixer runs the memory system is nearly idle: the out-projection's blocks are
-        # already resident (waiting for the mixer) and ask L2 for the head of the gate/up matrix.
-        hint = gu.qw.view(-1)[:self.prefetch_words] if self.prefetch and isinstance(gu, W4Packed) else None
-        R.owe(mixed, L["out"], lin, prefetch=hint)
+        R.owe(mixed, L["out"], lin)
         if isinstance(gu, W4Packed) and gu.gate_up:
             R.through(L["post_norm"], gu, self.act[:n], lin)
         else:  # unfused gate / up pair: plain GEMV into [gate | up], SwiGLU as its own kernel

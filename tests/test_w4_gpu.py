@@ -395,9 +395,9 @@ def test_fused_prologue_rejects_what_it_cannot_serve(api):
         w4.gemv_fused(h, h.clone(), rand_x(1, 1024)[0], 1e-6, q.qw, q.scales,
                       torch.empty(1, 64, dtype=torch.bfloat16, device=DEV), 64, h_out=h)
     big = api["q"](rand_w(64, H, seed=82))
-    with pytest.raises(RuntimeError):  # eight rows of 5120 do not fit beside the default ring geometry
+    with pytest.raises(RuntimeError):  # eight rows of 5120 do not fit beside the largest ring geometry
         w4.gemv_fused(rand_x(8, H), None, rand_x(1, H)[0], 1e-6, big.qw, big.scales,
-                      torch.empty(8, 64, dtype=torch.bfloat16, device=DEV), 64)
+                      torch.empty(8, 64, dtype=torch.bfloat16, device=DEV), 64, unroll=4)
     with pytest.raises(RuntimeError):  # width of h must be the padded K of the matrix
         w4.gemv_fused(rand_x(1, 512), None, rand_x(1, 512)[0], 1e-6, q.qw, q.scales,
                       torch.empty(1, 64, dtype=torch.bfloat16, device=DEV), 64)
