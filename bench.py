@@ -342,6 +342,42 @@ def exchange_timing(eng, reps=10, count=128):
     return statistics.median(ms) * 1e3 / count
 
 
+def tp_parity(world, rank, dev, transport, positions=16):
+    """Tensor-parallel logits against the single-GPU engine on the same seeded weights: a 4-layer
+    model of the 27B width (3 DeltaNet + 1 attention layer, full vocabulary), `positions`
+    teacher-forced tokens. Every rank runs its shard; rank 0 also runs the whole model on its own
+    GPU and compares. Returns the comparison on rank 0, None elsewhere."""
+    import torch
+    import torch.distributed as dist
+    from qengine_b200 import synth, tp
+    from qengine_b200.engine import Engine
+    cfg = synth.qwen27b_config(layers=4)
+    seq = synth.prompt_ids(positions, cfg.vocab, seed=77)
+    Wr = tp.build_sharded_model(cfg, world, rank, seed=3, device=dev, scale_std=0.01, mtp=False)
+    eng = Engine(cfg, Wr, max_len=64, device=dev, tp=tp.TPGroup(transport=transport), mtp=False)
+    local = eng.sequence_logits(seq).contiguous()
+    parts = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(parts, local)
+    err = eng.tp.error()
+    eng.graphs.clear()
+    del eng, Wr
+    torch.cuda.empty_cache()
+    out = None
+    if rank == 0:
+        full = torch.cat(parts, dim=-1).float()
+        W1 = synth.build_model(cfg, seed=3, device=dev, scale_std=0.01, mtp=False)
+        ref = Engine(cfg, W1, max_len=64, device=dev, mtp=False).sequence_logits(seq).float()
+        cos = torch.nn.functional.cosine_similarity(full.double(), ref.double(), dim=-1)
+        out = {"model": "4 layers of the 27B width, full vocabulary", "positions": positions,
+               "min_cosine": float(cos.min()), "max_abs": float((full - ref).abs().max()),
+               "top1_agree": int((full.argmax(-1) == ref.argmax(-1)).sum()), "exchange_error": err,
+               "against": "the single-GPU engine of this library on the same seeded weights"}
+        del W1, ref
+        torch.cuda.empty_cache()
+    dist.barrier()
+    return out
+
+
 def bytes_per_token(eng, mean_ctx):
     """Algorithmic HBM bytes of one plain decode step at context length mean_ctx."""
     from qengine_b200 import synth
@@ -376,6 +412,9 @@ def run_ours(a):
             dist.barrier()
         torch.cuda.synchronize()
 
+    parity_early = None
+    if world > 1 and not a.no_tp_parity:
+        parity_early = tp_parity(world, rank, dev, a.transport)
     cfg = synth.qwen27b_config(layers=a.layers)
     n_new, P = a.tokens, a.prompt
     if world == 1:
@@ -446,6 +485,7 @@ def run_ours(a):
         del eng_d
         torch.cuda.empty_cache()
     exchange_us = exchange_timing(eng) if world > 1 else None
+    parity = parity_early
 
     # ---- verify pass alone vs plain step (one graph replay each, same weights) -----------------
     verify = {}
@@ -514,23 +554,26 @@ def run_ours(a):
         pair1_us, pair1_gbs = mlp_pair_timing(eng, 1)
         pair5_us, pair5_gbs = mlp_pair_timing(eng, 5)
         achieved = seq_bytes / (seq_ms * 1e-3) / 1e9
+        ratio = ncu_traffic_ratio()
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": NCU_TRAFFIC_RATIO * seq_bytes / seq_launches, "peak_kind": f"of {peak_kind}",
+                    "traffic": ratio * seq_bytes / seq_launches if ratio else None,
+                    "traffic_note": "dram bytes per launch = algorithmic bytes x the ratio of the kept ncu capture "
+                                    "(profiles/w4_chain_kernel_27b_shapes.md)" if ratio else "no ncu capture kept",
+                    "peak_kind": f"of {peak_kind}",
                     "per_launch": {"algorithmic_bytes": seq_bytes / seq_launches,
                                    "avg_us": seq_ms * 1e3 / seq_launches},
-                    "kernel": "w4_warp_ring_kernel",
+                    "kernel": "w4_chain_kernel",
                     "how": f"{seq_launches} launches (every W4 matrix of one token, in order) as one graph, "
                            f"median of 10 CUDA-event timings; bytes = packed weights + scales + x + out"}
         cpu = None
         if world == 1 and not a.no_cpu:
-            tok_s, cores, desc, _ = cpu_reference_sample(3, 1)
-            cpu = {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": desc}
+            tok_s, cores, kind, desc, _ = cpu_reference_tokens(a.cpu_tokens, 1, layers=a.layers)
+            cpu = {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": kind, "sample": desc}
         line = {
             "metric": "batch-1 decode tok/s (plain)", "value": value, "unit": "tok/s", "n_gpus": world,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": dec_total / a.steps * 1e3,
             "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"27B-shape W4A16 plain greedy decode ({cfg.layers} layers, hidden 5120, vocab "
-                                   f"248320), {P}-token seeded prompt, {n_new} tokens per step",
+            "config": {"workload": WORKLOAD.format(layers=cfg.layers, prompt=P, tokens=n_new),
                        "parallelism": "single GPU" if world == 1 else
                        f"tp{world}: one sequence, every matrix sharded; {2 * cfg.layers + 2} exchanges of fp32 partial "
                        f"rows per token, transport {a.transport}",
@@ -554,6 +597,8 @@ def run_ours(a):
             "clocks": clocks,
             "cpu_baseline": cpu,
         }
+        if parity is not None:
+            line["tp_parity"] = parity
         if exchange_us is not None:
             line["tp_exchange"] = {"us_per_exchange": exchange_us, "per_token": 2 * cfg.layers + 2,
                                    "transport": a.transport, "error": eng.tp.error(),
@@ -588,6 +633,9 @@ def main():
                     help="also time the MTP cycle with the draft head pruned to this many ids (0 = skip)")
     ap.add_argument("--no-mtp", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-tokens", type=int, default=8, help="whole tokens timed for cpu_baseline (N = 1 only)")
+    ap.add_argument("--ref-vocab", type=int, default=0, help="reference arm: cut the vocabulary (tests only)")
+    ap.add_argument("--no-tp-parity", action="store_true")
     a = ap.parse_args()
     if a.impl == "reference":
         run_reference_arm(a)

@@ -285,6 +285,14 @@ int qe_w4_auto_ksplit(int Mp, int Kp, int N, int warps);
 int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
 /* qe_w4_gemv with the fused prologue / prefetch hint described at qe_w4_norm (nrm may be NULL). */
 int qe_w4_gemv_ex(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg, void* stream);
+/* The prologue of qe_w4_gemv_ex as a launch of its own: xn_out[r] = RMSNorm1p(h_in[r] + delta[r]) *
+ * (1 + norm_w) and h_out[r] = bf16(h_in[r] + delta[r]) for r < N, one block per row, with exactly
+ * the arithmetic (thread map, reduction order) the GEMV selected by `cfg` uses in its prologue:
+ * running this and then qe_w4_gemv on xn_out gives the bits of qe_w4_gemv_ex. For passes of
+ * several rows, where N blocks in parallel beat every GEMV block repeating the work for all rows.
+ * h_out may alias h_in here; xn_out is required. K % 8 == 0. Semantics of launch_rmsnorm1p
+ * (csrc/ops.h:8-9). */
+int qe_w4_norm_rows(const qe_w4_norm* nrm, int N, int K, const qe_w4_cfg* cfg, void* stream);
 /* Up to QE_W4_MAX_CHAIN GEMVs that depend on one another only through device memory (the output
  * of one is the input or the residual update of the next) as ONE cooperative launch: job j + 1
  * starts after a grid-wide barrier that follows job j, and every warp requests the head of its

@@ -89,6 +89,7 @@ SIGNATURES = {
     "qe_w4_auto_ksplit": (c_int, [c_int, c_int, c_int, c_int]),
     "qe_w4_gemv": (c_int, [C.POINTER(W4Params), C.POINTER(W4Cfg), P]),
     "qe_w4_gemv_ex": (c_int, [C.POINTER(W4Params), C.POINTER(W4Norm), C.POINTER(W4Cfg), P]),
+    "qe_w4_norm_rows": (c_int, [C.POINTER(W4Norm), c_int, c_int, C.POINTER(W4Cfg), P]),
     "qe_w4_gemv_chain": (c_int, [C.POINTER(C.POINTER(W4Params)), C.POINTER(C.POINTER(W4Norm)), c_int,
                                  C.POINTER(W4Cfg), P, P]),
     "qe_w4_ring_error": (c_int, []),

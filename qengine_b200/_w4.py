@@ -250,6 +250,36 @@ def gemv_fused(h_in, delta, norm_w, eps, qw, scales, out, M, *, h_out=None, xn_o
             _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units), "gemv_w4 fused")
 
 
+def norm_rows(h_in, delta, norm_w, eps, xn_out, h_out=None, tok=None, warps=0, unroll=0, ksplit=0, pdl=True,
+              variant=0, mode=-1, blocks_per_sm=0, min_units=4):
+    """Not in the reference: the prologue of `gemv_fused` as a launch of its own (one block per row),
+    bit-identical to it for the same launch options: xn_out = RMSNorm1p(h_in + delta) * (1 + w),
+    h_out = bf16(h_in + delta) (may alias h_in). `norm_rows` + `gemv` == `gemv_fused`."""
+    bf = torch.bfloat16
+    _req(xn_out.is_cuda and xn_out.dtype == bf and xn_out.dim() == 2 and xn_out.stride(1) == 1, "xn_out bf16 [N, K]")
+    N, K = xn_out.shape
+    _req(1 <= N <= 8 and K % 8 == 0 and norm_w.dtype == bf and norm_w.numel() == K and norm_w.is_contiguous(),
+         "N in 1..8, K % 8 == 0, norm_w [K]")
+    _req(h_in.is_cuda and h_in.dtype == bf and h_in.dim() == 2 and h_in.stride(1) == 1 and h_in.size(1) == K, "h_in [*, K]")
+    nrm = W4Norm()
+    nrm.h_in, nrm.ldh, nrm.norm_w, nrm.eps = h_in.data_ptr(), h_in.stride(0), norm_w.data_ptr(), float(eps)
+    nrm.xn_out, nrm.ldxo = xn_out.data_ptr(), xn_out.stride(0)
+    if tok is not None:
+        _req(tok.dtype == torch.int32 and tok.is_contiguous() and tok.numel() >= N and h_in.is_contiguous(), "tok int32 [>= N]")
+        nrm.tok, nrm.vocab = tok.data_ptr(), h_in.size(0)
+    else:
+        _req(h_in.size(0) == N, "h_in must have N rows")
+    for name, t in (("delta", delta), ("h_out", h_out)):
+        if t is not None:
+            _req(t.is_cuda and t.dtype == bf and t.dim() == 2 and t.stride(1) == 1 and t.shape == (N, K), f"{name} bf16 [N, K]")
+    if delta is not None:
+        nrm.delta, nrm.ldd = delta.data_ptr(), delta.stride(0)
+    if h_out is not None:
+        nrm.h_out, nrm.ldho = h_out.data_ptr(), h_out.stride(0)
+    cfg = _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units)
+    check(lib.qe_w4_norm_rows(C.byref(nrm), N, K, C.byref(cfg), torch.cuda.current_stream().cuda_stream), "norm_rows")
+
+
 def auto_ksplit(Mp, Kp, N, warps=8):
     return int(lib.qe_w4_auto_ksplit(int(Mp), int(Kp), int(N), int(warps)))
 

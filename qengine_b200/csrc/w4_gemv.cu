@@ -118,11 +118,12 @@ __device__ __noinline__ void load_x_slow(UnitOps& o, const bf16* row, int gg, in
 // order): a row's result does not depend on how many rows there are.
 template <int NW>
 __device__ __forceinline__ void norm_prologue(const GemvArgs& a, unsigned char* x_s, long pitch,
-                                              float (*s_red)[NW], int tid) {
+                                              float (*s_red)[NW], int tid, int r_lo, int r_hi, bool writer) {
+  // x_s + r * pitch receives row r (shared memory inside the GEMV, the caller's xn buffer in the
+  // stand-alone kernel below, which runs this same code on one row per block)
   constexpr int NT = NW * 32, RB = 4;  // rows are handled RB at a time (register budget)
   constexpr int WP = 3;                 // norm-weight packets a thread keeps (K <= 8 * WP * NT)
-  const int lane = tid & 31, warp = tid >> 5, N = a.o.N, npk = a.K >> 3;
-  const bool writer = blockIdx.x == 0;
+  const int lane = tid & 31, warp = tid >> 5, N = r_hi, npk = a.K >> 3;
   // the weight packets this thread needs in the second pass: requested now, so that their trip to
   // L2 overlaps the one of the rows
   const bool w_held = npk <= WP * NT;
@@ -133,7 +134,7 @@ __device__ __forceinline__ void norm_prologue(const GemvArgs& a, unsigned char* 
     if (w_held && p < npk) wv[i] = reinterpret_cast<const uint4*>(a.norm_w)[p];
   }
 #pragma unroll 1
-  for (int r0 = 0; r0 < N; r0 += RB) {
+  for (int r0 = r_lo; r0 < N; r0 += RB) {
     float ss[RB];
     const bf16* hrow[RB];
 #pragma unroll
@@ -189,7 +190,7 @@ __device__ __forceinline__ void norm_prologue(const GemvArgs& a, unsigned char* 
   }
   __syncthreads();
 #pragma unroll 1
-  for (int r0 = 0; r0 < N; r0 += RB) {
+  for (int r0 = r_lo; r0 < N; r0 += RB) {
     float inv[RB];
 #pragma unroll
     for (int i = 0; i < RB; ++i) {
@@ -220,12 +221,27 @@ __device__ __forceinline__ void norm_prologue(const GemvArgs& a, unsigned char* 
           for (int e = 0; e < 8; ++e) y[e] = v[e] * inv[i] * (1.0f + g[e]);
           const uint4 q = narrow8(y);
           xs[p] = q;
-          if (writer && a.xn_out) reinterpret_cast<uint4*>(a.xn_out + (long)r * a.ldxo)[p] = q;
+          if (writer && a.xn_out && reinterpret_cast<unsigned char*>(a.xn_out) != x_s)
+            reinterpret_cast<uint4*>(a.xn_out + (long)r * a.ldxo)[p] = q;
         }
       }
     }
   }
   __syncthreads();
+}
+
+// The prologue as a launch of its own: one block per row, the same thread -> packet map and the
+// same reduction order as inside the GEMV, hence the same bits. A pass of several rows runs this
+// (the rows in parallel on as many SMs) in front of a plain GEMV instead of letting every block
+// of the GEMV repeat the work for all rows; h_out may alias h_in here (a thread reads and writes
+// its own packets only).
+template <int NW>
+__global__ void __launch_bounds__(NW * 32) norm_rows_kernel(const GemvArgs a) {
+  dep_release();
+  dep_wait();
+  __shared__ float s_red[QE_MAX_ROWS][NW];
+  const int r = blockIdx.x;
+  norm_prologue<NW>(a, reinterpret_cast<unsigned char*>(a.xn_out), a.ldxo * 2, s_red, threadIdx.x, r, r + 1, true);
 }
 
 // A chain is up to kMaxJobs GEMVs that depend on each other only through global memory (the
@@ -354,7 +370,7 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
     bool xfast;
     if (a.h_in) {
       const long pitch = (long)a.K * 2 + 16;
-      norm_prologue<NW>(a, x_s, pitch, s_red, tid);
+      norm_prologue<NW>(a, x_s, pitch, s_red, tid, 0, a.o.N, blockIdx.x == 0);
       xbase = x_s + xrow * pitch + 32 * t;
       xfast = true;
     } else {
@@ -832,6 +848,36 @@ extern "C" int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* str
 
 extern "C" int qe_w4_gemv_ex(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg, void* stream) {
   return launch_chain(&p, &nrm, 1, cfg, nullptr, (cudaStream_t)stream);
+}
+
+extern "C" int qe_w4_norm_rows(const qe_w4_norm* nrm, int N, int K, const qe_w4_cfg* cfg, void* stream) {
+  if (!nrm || !cfg || N < 1 || N > QE_MAX_ROWS || K < 8 || (K & 7) || !nrm->h_in || !nrm->norm_w || !nrm->xn_out)
+    return QE_ERR_ARG;
+  if (!aligned16(nrm->h_in) || !aligned16(nrm->norm_w) || !aligned16(nrm->xn_out) || (nrm->ldh & 7) || (nrm->ldxo & 7) ||
+      (nrm->delta && (!aligned16(nrm->delta) || (nrm->ldd & 7))) ||
+      (nrm->h_out && (!aligned16(nrm->h_out) || (nrm->ldho & 7))) || (nrm->tok && nrm->vocab < 1))
+    return QE_ERR_ARG;
+  GemvArgs a{};
+  a.K = K;
+  a.o.N = N;
+  a.h_in = reinterpret_cast<const bf16*>(nrm->h_in);
+  a.tok = nrm->tok;
+  a.vocab = nrm->vocab;
+  a.delta = reinterpret_cast<const bf16*>(nrm->delta);
+  a.norm_w = reinterpret_cast<const bf16*>(nrm->norm_w);
+  a.h_out = reinterpret_cast<bf16*>(nrm->h_out);
+  a.xn_out = reinterpret_cast<bf16*>(nrm->xn_out);
+  a.ldh = nrm->ldh; a.ldd = nrm->ldd; a.ldho = nrm->ldho; a.ldxo = nrm->ldxo;
+  a.eps = nrm->eps;
+  const bool pdl = cfg->pdl && pdl_launch_enabled() && pdl_trigger_enabled();
+  const int nw = pick_geometry(*cfg).nw;  // the reduction order follows the CTA size of the GEMV
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (nw) {
+    case 8: return (int)launch(norm_rows_kernel<8>, dim3(N), dim3(256), 0, s, pdl, a);
+    case 16: return (int)launch(norm_rows_kernel<16>, dim3(N), dim3(512), 0, s, pdl, a);
+    case 24: return (int)launch(norm_rows_kernel<24>, dim3(N), dim3(768), 0, s, pdl, a);
+    default: return (int)launch(norm_rows_kernel<20>, dim3(N), dim3(640), 0, s, pdl, a);
+  }
 }
 
 extern "C" int qe_w4_gemv_chain(const qe_w4_params* const* p, const qe_w4_norm* const* nrm, int njobs,

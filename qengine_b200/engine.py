@@ -112,6 +112,10 @@ class W4Linear:
     def launch(self, jobs, **kw):
         _w4.gemv_chain(jobs, **{**self.kw, **kw})
 
+    def norm_rows(self, h, delta, w, eps, xn_out, **kw):
+        """The prologue of `after_norm` as its own launch, one block per row, same bits."""
+        _w4.norm_rows(h, delta, w, eps, xn_out, **{**self.kw, **kw})
+
 
 class _AfterFlush:
     """`_C` seen through the engine: any kernel other than a W4 GEMV first launches the GEMVs that
@@ -216,6 +220,21 @@ class _Residual:
         is the launch that opens a pass (no programmatic overlap with the previous pass)."""
         e, n = self.e, self.n
         w4 = isinstance(p, W4Packed) and isinstance(lin, W4Linear)
+        if e.fuse and w4 and n > e.FUSE_MAX_ROWS:
+            # Several rows: every block of the GEMV would repeat the norm of all rows; one block per
+            # row in front of a plain GEMV is faster, and (same arithmetic) gives the same bits.
+            xn = keep_normed if keep_normed is not None else self.xn
+            e._flush()
+            kw = {"pdl": False} if ordered else {}
+            if self.tok is not None:
+                lin.norm_rows(e.embed, None, w, e.cfg.eps, xn, tok=self.tok, h_out=self.h, **kw)
+                self.tok = None
+            else:
+                lin.norm_rows(self.h, e.mo[:n] if self.owed else None, w, e.cfg.eps, xn,
+                              h_out=self.h if self.owed else None, **kw)
+            self.owed = False
+            e._gemv(lin.job(xn, p, out))
+            return
         if e.fuse and w4:
             if self.tok is not None:
                 j = lin.job_after_norm(e.embed, None, w, e.cfg.eps, p, out, tok=self.tok, h_out=self.h,
@@ -241,6 +260,7 @@ class _Residual:
 # ----------------------------------------------------------------------------------------------
 class Engine:
     GDN_Q = 4
+    FUSE_MAX_ROWS = 1  # passes of more rows run the norm as its own launch (see _Residual.through)
     POS, PENDING, MODE, M, CYCLES, ACCEPTED = range(6)
 
     def __init__(self, cfg: Config, weights: dict, max_len: int = 4096, linear=None, device="cuda",

@@ -76,6 +76,14 @@ def tiny_config() -> Config:
                   hq=8, hkv=2, head_dim=64, rope_theta=1e7, rotary_dim=16, hk=4, hv=8, dk=64, dv=64)
 
 
+def shardable8_config() -> Config:
+    """A small configuration that an 8-way tensor-parallel engine can shard: 16 query / 4 KV heads
+    (KV heads shared by rank pairs at t = 8), 8 key / 16 value DeltaNet heads, every K split a
+    multiple of 128."""
+    return Config(hidden=512, layers=4, inter=2048, vocab=4096, eps=1e-6, layer_types=_pattern(4),
+                  hq=16, hkv=4, head_dim=64, rope_theta=1e7, rotary_dim=16, hk=8, hv=16, dk=64, dv=64)
+
+
 def qwen27b_config(layers: int = 64) -> Config:
     """27B shape: 64 layers (48 DeltaNet + 16 attention), hidden 5120, vocab 248,320."""
     return Config(hidden=5120, layers=layers, inter=17408, vocab=248320, eps=1e-6,

@@ -157,3 +157,93 @@ def test_prefilled_context_spec_equals_plain(setup):
         assert eng.generate_spec(g["prompt"], 40, 4, force_accept=a, truth=g["prompt"] + plain + [0] * 16) == plain
     base = Engine(cfg, synth.model_to(Wp, "cuda"), max_len=512, attn_splits=8).generate(g["prompt"], 40)
     assert base != plain  # the context is really attended to
+
+
+# ---------------------------------------------------------------------------------------------
+# The same checks at the 27B width (hidden 5120, head dim 256, DeltaNet d = 128, 48 value heads,
+# fused projection offsets 16,480 / 14,336, 6 query heads per KV head): 3 DeltaNet layers + 1
+# attention layer + the MTP layer, vocabulary cut to 16,384 rows so that the CPU oracle stays cheap.
+# ---------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def wide():
+    from qengine_b200 import synth
+    from qengine_b200.engine import Engine
+    from qengine_b200.quant import dequantize_w4
+    cfg = synth.qwen27b_config(layers=4)
+    cfg.vocab = 16384
+    W = synth.build_model(cfg, seed=11, device="cuda", scale_std=0.01)
+    eng = Engine(cfg, W, max_len=160)
+
+    # dense fp32 weights for the oracle; dequantised on the GPU by the product dequantiser, which
+    # test_w4_gpu.py::test_product_dequantiser_matches_oracle_dequantiser pins to the oracle's
+    def dense(L):
+        D = {k: v.cpu() for k, v in L.items() if isinstance(v, torch.Tensor)}
+        D["type"] = L["type"]
+        for k in ("in_proj", "out", "down", "fc"):
+            if k in L:
+                D[k] = dequantize_w4(L[k]).cpu()
+        g, u = dequantize_w4(L["gate_up"])
+        D["gate"], D["up"] = g.cpu(), u.cpu()
+        return D
+
+    D = {"embed": W["embed"].cpu(), "final_norm": W["final_norm"].cpu(), "lm_head": dequantize_w4(W["lm_head"]).cpu(),
+         "layers": [dense(L) for L in W["layers"]], "mtp": dense(W["mtp"])}
+    return cfg, D, eng
+
+
+def test_wide_teacher_forced_logits_vs_oracle(wide):
+    from qengine_b200 import synth
+    cfg, D, eng = wide
+    ocfg = oracle_config(cfg)
+    seq = synth.prompt_ids(12, cfg.vocab, seed=21)
+    e_logits = eng.sequence_logits(seq, chunk=5).float().cpu()   # passes of 5, 5 and 2 rows
+    hid, m_logits = eng.mtp_rows_logits(seq[:6])
+    st = OM.State(ocfg, 32)
+    worst, worst_abs, agree, worst_m = 1.0, 0.0, 0, 1.0
+    for t, tok in enumerate(seq):
+        lg, hf = OM.decode_step(D, st, tok, ocfg, fused_swiglu=True)
+        worst = min(worst, cosine(e_logits[t], lg))
+        worst_abs = max(worst_abs, float((e_logits[t] - lg.float()).abs().max()))
+        agree += int(e_logits[t].argmax()) == int(lg.float().argmax())
+        if t < 5:
+            ml, _ = OM.mtp_step(D, st, hid[t].cpu(), seq[t + 1], t, ocfg, fused_swiglu=True)
+            worst_m = min(worst_m, cosine(m_logits[t].float().cpu(), ml))
+    print(f"\n27B width, 4 layers: min cosine {worst:.6f} (MTP rows {worst_m:.6f}), max|d| {worst_abs:.4f}, "
+          f"top-1 {agree}/{len(seq)}")
+    assert worst >= 0.9999 and worst_m >= 0.9999 and agree >= len(seq) - 1
+
+
+def test_wide_spec_equals_plain_and_chunking(wide):
+    from qengine_b200 import synth
+    cfg, _, eng = wide
+    prompt = synth.prompt_ids(19, cfg.vocab, seed=22)
+    plain = eng.generate(prompt, 40)
+    for k in (1, 4):
+        assert eng.generate_spec(prompt, 40, k) == plain, k
+    for a in (0, 3, 4):
+        assert eng.generate_spec(prompt, 40, 4, force_accept=a, truth=prompt + plain + [0] * 16) == plain, a
+    a8 = eng.sequence_logits(prompt, chunk=8)
+    a1 = eng.sequence_logits(prompt, chunk=1)
+    assert torch.equal(a8.view(torch.int16), a1.view(torch.int16))
+
+
+def test_engine_without_fused_norms_and_with_chains_agree(setup):
+    """The three ways to run the same pass: norm fused into the GEMV launch (default), every norm
+    as its own kernel, and consecutive GEMVs as one cooperative chain. Chains are bit-identical to
+    the default; the unfused engine differs only by the order of the norm's sum of squares."""
+    cfg, Wp, eng = setup
+    from qengine_b200 import synth
+    from qengine_b200.engine import Engine
+    g = torch.load(G / "greedy.pt")
+    seq = (g["prompt"] + g["tokens"])[:24]
+    base = eng.sequence_logits(seq)
+    W = synth.model_to(Wp, "cuda")
+    chained = Engine(cfg, W, max_len=256, chain=True)
+    assert torch.equal(chained.sequence_logits(seq).view(torch.int16), base.view(torch.int16))
+    plain = eng.generate(g["prompt"], 60)
+    assert chained.generate(g["prompt"], 60) == plain
+    assert chained.generate_spec(g["prompt"], 60, 4) == plain
+    unfused = Engine(cfg, W, max_len=256, fuse=False)
+    lg = unfused.sequence_logits(seq)
+    assert min(cosine(lg[t], base[t]) for t in range(len(seq))) >= 0.99999
+    assert unfused.generate_spec(g["prompt"], 60, 3) == unfused.generate(g["prompt"], 60)

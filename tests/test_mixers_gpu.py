@@ -210,6 +210,39 @@ def test_attention_vs_oracle_and_row_independence(C, hq, hkv, hd, rd, steps, sta
     assert C.attn_error() == 0
 
 
+def test_attention_at_the_long_context_operating_point(C):
+    """The split kernel as the engine runs it on a 32K-position cache of the 27B shape: 24 query /
+    4 KV heads of dim 256, 5 rows (verify), 222 splits (6 per CTA, one CTA per SM and row), against
+    the oracle's attention over the same cache; rows bit-identical to 1-row passes."""
+    g = torch.Generator().manual_seed(5)
+    hq, hkv, hd, NS, n, start = 24, 4, 256, 222, 5, 32003
+    cfg = attn_cfg(hq, hkv, hd, 64)
+    max_len = start + n + 3
+    kc = torch.randn(hkv, max_len, hd, generator=g).to(BF)
+    vc = torch.randn(hkv, max_len, hd, generator=g).to(BF)
+    q = torch.randn(n, hq, hd, generator=g).to(BF)
+    gate = (torch.randn(n, hq, hd, generator=g) * 2).to(BF)
+    qg = torch.cat([q, gate], dim=-1).reshape(n, hq * 2 * hd)  # per head [q | gate]
+    refs = [OM.attention_core(q[t], gate[t].reshape(-1), kc, vc, start + t + 1, cfg) for t in range(n)]
+    kcd, vcd, qd, qgd = kc.to(dev), vc.to(dev), q.reshape(n, hq * hd).to(dev).contiguous(), qg.to(dev)
+    pos_t = torch.tensor([start], dtype=torch.int32, device=dev)
+    po = torch.empty(8, hq, NS, hd, device=dev)
+    pml = torch.empty(8, hq, NS, 2, device=dev)
+    out = torch.empty(n, hq * hd, dtype=BF, device=dev)
+    C.attn_decode(qd, kcd, vcd, pos_t, qgd, po, pml, out)
+    worst = 0.0
+    for t in range(n):
+        ref = refs[t].float()
+        diff = (out[t].cpu().float() - ref).abs()
+        worst = max(worst, float((diff / (2.0 ** -6 * ref.abs() + 2e-3)).max()))
+        o1 = torch.empty(1, hq * hd, dtype=BF, device=dev)
+        C.attn_decode(qd[t:t + 1], kcd, vcd, pos_t + t, qgd[t:t + 1], po, pml, o1)
+        assert torch.equal(o1[0], out[t]), "row differs from the 1-row pass"
+    print(f"\n32K positions, 222 splits: worst error / bound = {worst:.3f}")
+    assert worst <= 1.0
+    assert C.attn_error() == 0
+
+
 def test_attention_never_writes_past_the_cache(C):
     hq, hkv, hd = 8, 2, 256
     cfg = attn_cfg(hq, hkv, hd, 64)

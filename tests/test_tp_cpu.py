@@ -74,11 +74,12 @@ def test_select_rows_slice_k_slice_tiles_roundtrip():
     assert torch.equal(torch.cat([G0, G1]), G) and torch.equal(torch.cat([U0, U1]), U)
 
 
-@pytest.mark.parametrize("t", [2, 4])
-def test_shards_reassemble_to_the_full_layer(t):
+@pytest.mark.parametrize("t,small8", [(2, False), (4, False), (2, True), (8, True)])
+def test_shards_reassemble_to_the_full_layer(t, small8):
     """Row shards of in_proj are the head slices, K shards of out / down concatenate to the full
-    matrix, and attention KV heads are shared once t exceeds their number."""
-    cfg = synth.tiny_config()
+    matrix, and attention KV heads are shared once t exceeds their number (t = 4 on the tiny
+    configuration, t = 8 on the 8-way shardable one)."""
+    cfg = synth.shardable8_config() if small8 else synth.tiny_config()
     W = synth.build_model(cfg, SEED, "cpu", STD)
     lc = tp.local_config(cfg, t)
     for li in (0, 3):

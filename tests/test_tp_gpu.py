@@ -302,17 +302,21 @@ def _gather_cols(local):
     return torch.cat(parts, dim=-1)
 
 
-def _engine_worker(rank, world, transport):
+def _engine_worker(rank, world, transport, small8=False):
     from oracle import model as OM
     from qengine_b200 import synth, tp
     from qengine_b200.engine import Engine
     from util import cosine, dense_model, oracle_config
-    cfg = synth.tiny_config()
+    cfg = synth.shardable8_config() if small8 else synth.tiny_config()
     Wp = synth.build_model(cfg, seed=7, device="cpu", scale_std=0.01)
     W = synth.model_to(Wp, "cuda")
     eng = Engine(cfg, tp.shard_model(W, cfg, world, rank), max_len=256, tp=tp.TPGroup(transport=transport))
-    g = torch.load(G / "greedy.pt")
-    prompt, seq = g["prompt"], (g["prompt"] + g["tokens"])[:40]
+    if small8:  # no stored continuation for this configuration: a seeded prompt, teacher-forced
+        prompt = synth.prompt_ids(32, cfg.vocab, seed=1234)
+        seq = prompt + synth.prompt_ids(8, cfg.vocab, seed=4321)
+    else:
+        g = torch.load(G / "greedy.pt")
+        prompt, seq = g["prompt"], (g["prompt"] + g["tokens"])[:40]
 
     lg = _gather_cols(eng.sequence_logits(seq))
     hid, mlg_l = eng.mtp_rows_logits(seq[:12])
@@ -376,3 +380,14 @@ def test_tp_engine_two_gpus(transport):
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_tp_engine_four_gpus_shared_kv_heads():
     _spawn(_engine_worker, 4, "peer")  # tiny model: 2 KV heads over 4 ranks
+
+
+def test_tp_engine_shardable8_config_group_of_one():
+    """The 8-way shardable configuration through the same checks on one GPU (logits vs the single-GPU
+    engine and the oracle, speculative == plain), so that the 8-GPU test below differs only in t."""
+    _spawn(_engine_worker, 1, "peer", True)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+def test_tp_engine_eight_gpus():
+    _spawn(_engine_worker, 8, "peer", True)  # 4 KV heads over 8 ranks: each shared by a pair

@@ -365,6 +365,32 @@ def test_fused_norm_prologue(api, M, K, gate_up):
     assert w4.ring_error() == 0
 
 
+def test_norm_rows_equals_the_fused_prologue(api):
+    """`norm_rows` + `gemv` must give the bits of `gemv_fused` (the engine mixes the two: fused for
+    one-row passes, separate launches for verify passes, and the outputs have to agree)."""
+    w4 = api["w4"]
+    K, M = H, 2048
+    p = api["q"](rand_w(M, K, seed=73))
+    g = torch.Generator(device=DEV).manual_seed(74)
+    h = torch.randn(8, K, generator=g, device=DEV).to(torch.bfloat16)
+    d = (torch.randn(8, K, generator=g, device=DEV) * 0.5).to(torch.bfloat16)
+    nw = (torch.randn(K, generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+    for kw in (dict(), dict(warps=16), dict(warps=8)):
+        for N in (1, 5, 8):
+            for delta in (d[:N], None):
+                out_f = torch.empty(N, M, dtype=torch.bfloat16, device=DEV)
+                ho_f = torch.zeros(N, K, dtype=torch.bfloat16, device=DEV)
+                xn_f = torch.empty(N, K, dtype=torch.bfloat16, device=DEV)
+                w4.gemv_fused(h[:N], delta, nw, 1e-6, p.qw, p.scales, out_f, M, h_out=ho_f, xn_out=xn_f, **kw)
+                hh = h[:N].clone()
+                xn = torch.empty(N, K, dtype=torch.bfloat16, device=DEV)
+                w4.norm_rows(hh, delta, nw, 1e-6, xn, h_out=hh if delta is not None else None, **kw)  # in place
+                assert torch.equal(bits(xn), bits(xn_f)), f"{kw} N={N}: normed rows differ"
+                if delta is not None:
+                    assert torch.equal(bits(hh), bits(ho_f)), "residual rows differ"
+                assert torch.equal(bits(api["gemv"](xn, p, **kw)), bits(out_f))
+
+
 def test_fused_prologue_gathers_embedding_rows(api):
     w4 = api["w4"]
     Vt, K, M = 1000, 512, 1552
