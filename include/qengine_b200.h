@@ -229,12 +229,12 @@ typedef struct qe_w4_params {
  * One kernel family serves every shape, so most of them only steer its geometry; every accepted
  * combination is deterministic and independent of N. */
 typedef struct qe_w4_cfg {
-  int warps;         /* warps per block: 0 (auto) -> 20, 16 -> 16, 4 / 8 -> 8 */
+  int warps;         /* warps per block: 0 (auto) / 16 -> 16, 4 / 8 -> 8 */
   int unroll;        /* ring of 1-KB weight units per warp: 4 -> 2 stages of 4, 2 -> 3 stages of 2,
                         1 -> 2 stages of 2, 0 -> the deepest that fits (never changes the result) */
   int ksplit;        /* > 0: at least this many warps share a 16-row tile; 0 = by min_units */
   int pdl;           /* launch with programmatic stream serialization */
-  int variant;       /* 1: 24 warps per block; other values: as `warps` says */
+  int variant;       /* 1: 24 warps per block, 2: 20 warps; other values: as `warps` says */
   int mode;          /* accepted for compatibility (-1, 0, 2, 3, 4); the plan always reports 4 */
   int blocks_per_sm; /* accepted for compatibility; the kernel runs one block per SM */
   int min_units;     /* minimum 1-KB units per warp (fewer warps for small matrices) */

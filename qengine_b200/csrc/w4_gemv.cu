@@ -10,8 +10,9 @@
 // Design. The matrix is a stream of 1 KB units (16 rows x 128 k); 97 % of the bytes of a decode
 // step are such units, so the kernel is organised around streaming them at HBM rate with as few
 // issued instructions per unit as the unpack allows:
-//   * one CTA per SM, NW warps; the unit stream is cut into one contiguous range per warp (all
-//     warps of all CTAs, equal shares), so every warp reads one contiguous slab of HBM;
+//   * one CTA per SM, NW warps; the unit stream is cut into one contiguous range per CTA (equal
+//     shares, to within four units) and that range into one contiguous range per warp, so every
+//     warp reads one contiguous slab of HBM and every SM has the same amount of work;
 //   * each warp owns a private ring in shared memory that its lane 0 keeps full with bulk copies
 //     (cp.async.bulk global -> shared, completion on an mbarrier): STAGES x PERW units in flight
 //     per warp, ~130 KB per SM, issued before the programmatic-dependency wait because weights
@@ -65,7 +66,8 @@ struct GemvArgs {
   OutDesc o;
   float* ws;       // 2 x 128 floats per CTA: partial tiles that cross a CTA boundary
   int* counters;   // one arrival counter per tile, zero on entry, left zero
-  int K, G, total, nworkers;
+  int K, G, total;
+  int nctas;       // CTAs that own work (<= gridDim.x)
   int quantum;     // ranges start at multiples of this many units (4 when G % 4 == 0, else 1)
   int xvec;        // x rows are 16-byte aligned with ldx % 8 == 0
   // fused residual + RMSNorm prologue (h_in != nullptr)
@@ -87,9 +89,18 @@ __device__ int g_w4_error = 0;
 
 constexpr int kWaitLimit = 1 << 20;
 
-// First unit of worker v: the stream is dealt out in quanta of q units.
-__device__ __host__ __forceinline__ int range_begin(int total, int q, int nwk, int v) {
-  return q * share_begin(total / q, nwk, v);
+// The stream is dealt out in quanta of q units, in two levels: equal shares of quanta per CTA
+// (so every SM has the same amount of work to within one quantum), and inside a CTA equal shares
+// of its quanta per warp.
+__device__ __host__ __forceinline__ int cta_begin(int total, int q, int nctas, int c) {
+  return q * share_begin(total / q, nctas, c);
+}
+template <int NW>
+__device__ __forceinline__ void warp_range(int total, int q, int nctas, int cta, int warp, int& u0, int& u1) {
+  if (cta >= nctas) { u0 = u1 = total; return; }
+  const int b = share_begin(total / q, nctas, cta), e = share_begin(total / q, nctas, cta + 1);
+  u0 = q * (b + share_begin(e - b, NW, warp));
+  u1 = q * (b + share_begin(e - b, NW, warp + 1));
 }
 
 // x fragment of a lane for the ragged cases (misaligned rows, or the last group when K is not a
@@ -327,8 +338,7 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
     }
   };
   auto range_of = [&](const GemvArgs& a, int& u0, int& u1) {
-    u0 = range_begin(a.total, a.quantum, a.nworkers, min(worker, a.nworkers));
-    u1 = range_begin(a.total, a.quantum, a.nworkers, min(worker + 1, a.nworkers));
+    warp_range<NW>(a.total, a.quantum, a.nctas, blockIdx.x, warp, u0, u1);
   };
 
   // weights never depend on the producer of x: the first stages are requested before the
@@ -343,7 +353,7 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
 #pragma unroll 1
   for (int j = 0; j < c.njobs; ++j) {
     const GemvArgs& a = c.job[j];
-    const int G = a.G, total = a.total, nwk = a.nworkers;
+    const int G = a.G, total = a.total;
     int u0, u1;
     range_of(a, u0, u1);
     if (lane == 0) {
@@ -511,11 +521,11 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
       if (!done) return;
       float sum[4] = {0.f, 0.f, 0.f, 0.f};
       const int q = a.quantum;
-      const int c_lo = share_owner(total / q, nwk, (T * G) / q) / NW;
-      const int c_hi = share_owner(total / q, nwk, (T * G + G - 1) / q) / NW;
+      const int c_lo = share_owner(total / q, a.nctas, (T * G) / q);
+      const int c_hi = share_owner(total / q, a.nctas, (T * G + G - 1) / q);
 #pragma unroll 1
       for (int cc = c_lo; cc <= c_hi; ++cc) {
-        const int cb = range_begin(total, q, nwk, min(cc * NW, nwk));
+        const int cb = cta_begin(total, q, a.nctas, cc);
         const float* p = a.ws + ((size_t)cc * 2 + (cb > T * G ? 0 : 1)) * 128;
 #pragma unroll
         for (int k = 0; k < 4; ++k) sum[k] += __ldcg(p + k * 32 + lane);
@@ -531,7 +541,7 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
         float f[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) f[k] = part[(warp * 2 + 1) * 128 + k * 32 + lane];
-        for (int w2 = warp + 1; w2 < NW && s_rb[w2] < tend; ++w2) {
+        for (int w2 = warp + 1; w2 < NW && s_rb[w2] < min(tend, cta_e); ++w2) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) f[k] += part[(w2 * 2) * 128 + k * 32 + lane];
         }
@@ -544,7 +554,7 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
       float f[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) f[k] = part[k * 32 + lane];
-      for (int w2 = 1; w2 < NW && s_rb[w2] < tend; ++w2) {
+      for (int w2 = 1; w2 < NW && s_rb[w2] < min(tend, cta_e); ++w2) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) f[k] += part[(w2 * 2) * 128 + k * 32 + lane];
       }
@@ -571,13 +581,13 @@ template <int NW, int PERW, int STAGES>
 constexpr Geometry geometry() {
   return Geometry{w4_chain_kernel<NW, PERW, STAGES>, NW, PERW, STAGES};
 }
-// Selected by the reference's launch options. `warps`: 0 (auto) -> 20 warps per CTA, 16 -> 16,
-// 4 / 8 -> 8; variant 1 -> 24 warps. `unroll` picks the ring: 2 -> 3 stages of 2 units, 4 -> 2
+// Selected by the reference's launch options. `warps`: 0 (auto) / 16 -> 16 warps per CTA, 4 / 8 -> 8;
+// variant 1 -> 24 warps, variant 2 -> 20 warps. `unroll` picks the ring: 2 -> 3 stages of 2 units, 4 -> 2
 // stages of 4 units, 1 -> 2 stages of 2 units (the smallest; leaves room for eight rows of
 // prologue input), 0 -> the deepest of the three that fits beside the prologue's rows. Work is split by CTA size only, so every ring shape of one CTA size gives the
 // same bits.
-const Geometry kGeoms[] = {geometry<20, 2, 3>(), geometry<20, 4, 2>(), geometry<20, 2, 2>(),
-                           geometry<16, 2, 3>(), geometry<16, 4, 2>(), geometry<16, 2, 2>(),
+const Geometry kGeoms[] = {geometry<16, 2, 3>(), geometry<16, 4, 2>(), geometry<16, 2, 2>(),
+                           geometry<20, 2, 3>(), geometry<20, 4, 2>(), geometry<20, 2, 2>(),
                            geometry<8, 2, 3>(),  geometry<8, 4, 2>(),  geometry<8, 2, 2>(),
                            geometry<24, 2, 3>()};
 
@@ -585,7 +595,7 @@ const Geometry kGeoms[] = {geometry<20, 2, 3>(), geometry<20, 4, 2>(), geometry<
 const Geometry& pick_geometry(const qe_w4_cfg& c, int ring = -1) {
   if (c.variant == 1) return kGeoms[9];
   if (ring < 0) ring = c.unroll == 4 ? 1 : c.unroll == 1 ? 2 : 0;
-  const int size = (c.warps == 4 || c.warps == 8) ? 2 : c.warps == 16 ? 1 : 0;
+  const int size = (c.warps == 4 || c.warps == 8) ? 2 : c.variant == 2 ? 1 : 0;
   return kGeoms[3 * size + ring];
 }
 
@@ -642,7 +652,7 @@ const std::vector<ShapeCfg>& env_overrides() {
 struct Resolved {
   qe_w4_plan plan;
   const Geometry* geom;
-  int nworkers, quantum;
+  int nctas, quantum;
 };
 
 // Shape-only launch policy (never N): as many warps as there are units / min_units, at most one
@@ -664,12 +674,12 @@ Resolved resolve(const qe_w4_params& p, const qe_w4_cfg& c_in) {
   // ranges are dealt out in quanta of 4 units (a whole number of ring stages in every geometry)
   // when the tiles are a whole number of quanta long, so that a stage never straddles two tiles
   const long quantum = (G % 4 == 0) ? 4 : 1;  // the same for every ring geometry: same split, same bits
-  const long want = (units + min_units - 1) / min_units;
-  const long workers = std::max<long>(1, std::min<long>({ctas_max * r.geom->nw, want, units / quantum}));
+  const long want = (units + min_units - 1) / min_units;  // warps that would each get min_units
+  const long ctas = std::max<long>(1, std::min<long>({ctas_max, (want + r.geom->nw - 1) / r.geom->nw, units / quantum}));
   r.quantum = (int)quantum;
-  r.nworkers = (int)workers;
+  r.nctas = (int)ctas;
   r.plan.mode = 4;
-  r.plan.grid_x = (int)((workers + r.geom->nw - 1) / r.geom->nw);
+  r.plan.grid_x = (int)ctas;
   r.plan.grid_y = 1;
   r.plan.threads = r.geom->nw * 32;
   r.plan.ws_floats = (long)r.plan.grid_x * 2 * 128;
@@ -712,7 +722,7 @@ int make_job(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg,
   a.K = p->K;
   a.G = p->Kp / 128;
   a.total = (p->Mp / 16) * a.G;
-  a.nworkers = r.nworkers;
+  a.nctas = r.nctas;
   a.quantum = r.quantum;
   a.xvec = ((p->ldx & 7) == 0 && aligned16(p->x)) ? 1 : 0;
   *smem_extra = 0;
