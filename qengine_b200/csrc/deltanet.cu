@@ -88,10 +88,22 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
   const int n = a.n;
   float* Sj = a.S + (size_t)j * D * D + c0 + lane;
 
-  // ---- independent of this pass's producer: state slice, per-head constants ----
+  // ---- independent of this pass's producer: state slice, per-head constants, checkpoints ----
+  // Every load below is issued before anything waits: the state (3 MB per layer, from HBM), all
+  // eight checkpoint slots (whether or not they are pending: that is only known once ctl arrives,
+  // and waiting for it would put a second memory round trip in front of the replay) and ctl.
   float s[RP];
 #pragma unroll
   for (int i = 0; i < RP; ++i) s[i] = Sj[(size_t)(warp * RP + i) * D];
+  for (int idx = tid; idx < kMaxRows * D; idx += NT) {
+    const int t = idx / D, i = idx - t * D;
+    k_s[t][i] = a.st_k[((size_t)t * a.Hv + j) * D + i];
+  }
+  {
+    const int t = tid >> 5;  // 8 warps = 8 slots, lane = column
+    v_s[t][lane] = a.st_v[((size_t)t * a.Hv + j) * D + c0 + lane];
+    if (lane < 2) gate_s[t][lane] = a.st_g[(t * a.Hv + j) * 2 + lane];
+  }
   const float A_log = tofloat(a.A_log[j]), dt_bias = tofloat(a.dt_bias[j]);
   const float nw = tofloat(a.norm_w[c0 + lane]);
   // ctl and the checkpoints were written by the previous pass, which has completed (the first
@@ -127,15 +139,9 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
 
   // ---- 1. replay the kept rows of the previous pass, write the committed state once ----
   int buf = 0;
-  for (int t = 0; t < pend; ++t) {
-    // checkpoints into shared memory (k for all D rows, v for this CTA's columns)
-    for (int i = tid; i < D; i += NT) k_s[t][i] = a.st_k[((size_t)t * a.Hv + j) * D + i];
-    if (tid < kCols) v_s[t][tid] = a.st_v[((size_t)t * a.Hv + j) * D + c0 + tid];
-  }
   __syncthreads();
   for (int t = 0; t < pend; ++t) {
-    row_update(k_s[t], nullptr, v_s[t][lane], a.st_g[(t * a.Hv + j) * 2], a.st_g[(t * a.Hv + j) * 2 + 1],
-               0.f, buf, false);
+    row_update(k_s[t], nullptr, v_s[t][lane], gate_s[t][0], gate_s[t][1], 0.f, buf, false);
     buf ^= 1;
   }
   // This CTA is done reading the checkpoints of the previous pass. The CTA with cs == 0 overwrites
@@ -146,37 +152,52 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
 #pragma unroll
     for (int i = 0; i < RP; ++i) Sj[(size_t)(warp * RP + i) * D] = s[i];
   }
+  // conv taps and history of the channels this thread convolves below: constants and state of
+  // earlier passes, fetched before the dependency wait as well
+  constexpr int CPT = (2 * D + kCols + NT - 1) / NT;  // conv channels per thread (2 for D = 128)
+  float cw[CPT][4], hx[CPT][3];
+  int chn[CPT];
+#pragma unroll
+  for (int u = 0; u < CPT; ++u) {
+    const int idx = tid + u * NT;
+    chn[u] = -1;
+    if (idx < 2 * D + kCols) {
+      const int part_id = idx < D ? 0 : idx < 2 * D ? 1 : 2;
+      const int c = part_id == 0 ? idx : part_id == 1 ? idx - D : idx - 2 * D;
+      const int ch = part_id == 0 ? i_qk * D + c : part_id == 1 ? a.Hk * D + i_qk * D + c : 2 * a.Hk * D + j * D + c0 + c;
+      chn[u] = ch;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) cw[u][w] = tofloat(a.conv_w[ch * 4 + w]);
+#pragma unroll
+      for (int b = 0; b < 3; ++b) {
+        const int p = P - 3 + b;
+        hx[u][b] = p >= 0 ? tofloat(a.ring[(size_t)(p & (kRing - 1)) * C + ch]) : 0.f;
+      }
+    }
+  }
   if (a.early) dep_wait();  // from here on: this pass's projections
   // the gate input of this warp's row is only needed at the very end: fetch it now
   const float z_pre = warp < n ? tofloat(a.z[(long)warp * a.ldp + j * D + c0 + lane]) : 0.f;
   __syncthreads();  // k_s / v_s are about to be overwritten by the new rows
 
   // ---- 2a. causal conv + SiLU of every new row (q, k: all D channels; v: own columns) ----
-  for (int idx = tid; idx < 2 * D + kCols; idx += NT) {
+#pragma unroll
+  for (int u = 0; u < CPT; ++u) {
+    const int idx = tid + u * NT;
+    if (chn[u] < 0) continue;
     const int part_id = idx < D ? 0 : idx < 2 * D ? 1 : 2;
     const int c = part_id == 0 ? idx : part_id == 1 ? idx - D : idx - 2 * D;
-    const int ch = part_id == 0 ? i_qk * D + c
-                 : part_id == 1 ? a.Hk * D + i_qk * D + c
-                                : 2 * a.Hk * D + j * D + c0 + c;
-    float cw[4];
-#pragma unroll
-    for (int w = 0; w < 4; ++w) cw[w] = tofloat(a.conv_w[ch * 4 + w]);
-    float x0, x1, x2;
-    {
-      const int p0 = P - 3, p1 = P - 2, p2 = P - 1;
-      x0 = p0 >= 0 ? tofloat(a.ring[(size_t)(p0 & (kRing - 1)) * C + ch]) : 0.f;
-      x1 = p1 >= 0 ? tofloat(a.ring[(size_t)(p1 & (kRing - 1)) * C + ch]) : 0.f;
-      x2 = p2 >= 0 ? tofloat(a.ring[(size_t)(p2 & (kRing - 1)) * C + ch]) : 0.f;
-    }
+    const int ch = chn[u];
+    float x0 = hx[u][0], x1 = hx[u][1], x2 = hx[u][2];
     // q/k channels are shared by `rep` heads and by the CTAs of a head: one CTA writes them
     const bool owner = part_id == 2 || ((j % rep) == 0 && cs == 0);
     for (int t = 0; t < n; ++t) {
       const bf16 xb = a.qkv[(long)t * a.ldp + ch];
       const float x3 = tofloat(xb);
-      float acc = cw[0] * x0;
-      acc = fmaf(cw[1], x1, acc);
-      acc = fmaf(cw[2], x2, acc);
-      acc = fmaf(cw[3], x3, acc);
+      float acc = cw[u][0] * x0;
+      acc = fmaf(cw[u][1], x1, acc);
+      acc = fmaf(cw[u][2], x2, acc);
+      acc = fmaf(cw[u][3], x3, acc);
       const float y = rnd(silu_acc(rnd(acc)));
       if (part_id == 0) q_s[t][c] = y;
       else if (part_id == 1) k_s[t][c] = y;

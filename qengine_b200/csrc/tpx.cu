@@ -3,7 +3,7 @@
 //
 // A matrix split along K over t ranks leaves every rank with fp32 partial rows [n, H]. The
 // consumer is always "residual += sum of the partial rows; RMSNorm1p". tp_xnorm_kernel does the
-// exchange and the norm in ONE kernel over peer memory: every rank stores its partial row straight
+// exchange and the norm in ONE kernel (a cluster of 8 CTAs per row) over peer memory: every rank stores its partial row straight
 // into a slot of every peer's exchange block (NVLink peer stores), and reads the other ranks'
 // rows from its own block as they land. Transport is a flag-in-data protocol: each 8-byte store
 // carries 4 bytes of payload and the 4-byte sequence number of the exchange, 8-byte stores are
@@ -26,14 +26,18 @@
 // Every wait is bounded (wall-clock limit per wait, default 10 s; sticky: after the first timeout
 // no later wait spins at all). A timed-out exchange produces garbage and sets the error word that
 // qe_tp_error reads; it never hangs the GPU. The sum over ranks is taken in ascending rank order
-// on every rank, so all ranks hold bit-identical activations, and a group of one rank reproduces
-// the single-GPU arithmetic exactly. The same norm without the exchange (parts already gathered by
-// a library collective) is qe_rmsnorm1p_parts.
+// on every rank, so all ranks hold bit-identical activations. The same norm without the exchange
+// (parts already gathered by a library collective) is qe_rmsnorm1p_parts; its sum of squares is
+// taken in another order, so the two transports agree to rounding, not bit for bit.
+#include <cooperative_groups.h>
+
 #include <algorithm>
 #include <cstring>
 
 #include "../../include/qengine_b200.h"
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace qb {
 namespace {
@@ -144,141 +148,122 @@ tp_norm_kernel(bf16* x, const float* part, int nparts, const bf16* w, bf16* out,
   }
 }
 
-// The exchange + norm kernel. Two phases with different thread layouts:
-//  gather  all threads (up to 640), one 8-element packet each: push our partial to every peer,
-//          issue the loads of up to four peers' slots at once (a blocking wait per 16 bytes would
-//          serialise ~0.6 us L2 round trips: 30 of them at 4 ranks), re-poll only what has not
-//          landed, add the ranks in ascending order, round once to bf16 -> shared memory;
-//  norm    the first VT threads in the exact layout of rmsnorm1p_vec_kernel (packets tid + p * VT,
-//          same block reduction; idle threads add zeros), so a group of one rank reproduces the
-//          single-GPU bits.
-constexpr int kXThreads = 640;
-template <int PKT>
-__global__ void __launch_bounds__(kXThreads)
-tp_xnorm_kernel(TpView tv, bf16* x, const float* part, const bf16* w, bf16* out, int H, int VT, long ldx,
+// The exchange + norm kernel. A row is handled by a thread-block cluster of kCX CTAs, each owning
+// a slice of PK packets (8 elements each) of the row; inside a CTA the threads form a [peer][packet]
+// grid, so every (peer, packet) pair has a thread of its own: it pushes this rank's packet into
+// that peer's block (4 x 16-byte flag-in-data stores) and polls this rank's block for the packet
+// the peer pushes (4 x 16-byte loads per try). With 8 ranks and hidden 5120 that is 4,480 threads
+// on 8 SMs per row, each with 64 bytes out and 64 bytes in -- the exchange is one NVLink store
+// latency plus one poll, not a loop over peers and packets in one CTA. The packets land in shared
+// memory; the first PK threads of the CTA add the ranks in ascending order (every rank the same
+// order: bit-identical activations everywhere), round once to bf16, add the residual, and the sum
+// of squares of the row is combined across the cluster through distributed shared memory in CTA
+// order. Rows of a pass run in parallel (grid.y).
+constexpr int kCX = 8;  // CTAs per row = cluster size (portable maximum)
+
+__global__ void __launch_bounds__(1024)
+tp_xnorm_kernel(TpView tv, bf16* x, const float* part, const bf16* w, bf16* out, int H, int PK, long ldx,
                 long ldp, long ldo, float eps) {
   dep_release();
   dep_wait();
-  extern __shared__ float delta_s[];  // [H] bf16-rounded sum of the ranks' partial rows
+  cg::cluster_group cluster = cg::this_cluster();
+  extern __shared__ float recv_s[];  // [world][PK][8]: the peers' packets of this CTA's slice
   __shared__ float scratch[32];
-  const int row = blockIdx.x, npk = H >> 3, tid = threadIdx.x;
+  __shared__ float ss_all[kCX];      // sum of squares of every CTA's slice (pushed by its owner)
+  const int cs = blockIdx.x, row = blockIdx.y, tid = threadIdx.x;
+  const int npk = H >> 3, npeers = tv.world - 1;
+  const int pk = tid % PK, pj = tid / PK;  // packet inside the slice, peer slot
+  const int i = cs * PK + pk;              // packet of the row
   int* hdr = reinterpret_cast<int*>(tv.base[tv.rank]);
   const uint32_t e = (uint32_t)(*(volatile int*)(hdr + row)) + 1u;
   bool dead = *(volatile int*)(hdr + kErrWord) != 0;
 
-  for (int i = tid; i < npk; i += blockDim.x) {
-    float mine[8];
-    {
-      const float4* pr = reinterpret_cast<const float4*>(part + (long)row * ldp) + 2 * i;
-      const float4 a = pr[0], b = pr[1];
-      mine[0] = a.x; mine[1] = a.y; mine[2] = a.z; mine[3] = a.w;
-      mine[4] = b.x; mine[5] = b.y; mine[6] = b.z; mine[7] = b.w;
-    }
-    for (int r = 0; r < tv.world; ++r) {
-      if (r == tv.rank) continue;
-      char* d = norm_slot(tv.base[r], tv, e, tv.rank, row) + (long)i * 64;
+  float mine[8];
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
-        st_v4(d + 16 * q, __float_as_uint(mine[2 * q]), e, __float_as_uint(mine[2 * q + 1]), e);
-    }
-    float d[8];
+  for (int k = 0; k < 8; ++k) mine[k] = 0.f;
+  const bool has_packet = i < npk && pj < max(npeers, 1);
+  if (has_packet) {
+    const float4* pr = reinterpret_cast<const float4*>(part + (long)row * ldp) + 2 * i;
+    const float4 a = pr[0], b = pr[1];
+    mine[0] = a.x; mine[1] = a.y; mine[2] = a.z; mine[3] = a.w;
+    mine[4] = b.x; mine[5] = b.y; mine[6] = b.z; mine[7] = b.w;
+  }
+  if (has_packet && pj < npeers) {
+    const int peer = pj < tv.rank ? pj : pj + 1;  // the other ranks in ascending order
+    char* d = norm_slot(tv.base[peer], tv, e, tv.rank, row) + (long)i * 64;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) d[k] = 0.f;
-    for (int b0 = 0; b0 < tv.world; b0 += 4) {
-      // up to four peers at a time: all 16 loads of the batch are issued together and the whole
-      // batch is re-read until every flag matches (one L2 round trip per try, never one per word)
-      uint4 rv[4][4];
-      const unsigned long long t0 = now_ns();
-      for (unsigned tries = 1;; ++tries) {
+    for (int q = 0; q < 4; ++q)
+      st_v4(d + 16 * q, __float_as_uint(mine[2 * q]), e, __float_as_uint(mine[2 * q + 1]), e);
+    const char* sp = norm_slot(tv.base[tv.rank], tv, e, peer, row) + (long)i * 64;
+    uint4 rv[4];
+    const unsigned long long t0 = now_ns();
+    for (unsigned tries = 1;; ++tries) {
+      // all four loads of a try are issued together: one round trip per try, never one per word
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int src = b0 + u;
-          if (src < tv.world && src != tv.rank) {
-            const char* sp = norm_slot(tv.base[tv.rank], tv, e, src, row) + (long)i * 64;
+      for (int q = 0; q < 4; ++q) rv[q] = ld_v4(sp + 16 * q);
+      bool all = true;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) rv[u][q] = ld_v4(sp + 16 * q);
-          }
-        }
-        bool all = true;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int src = b0 + u;
-          if (src < tv.world && src != tv.rank) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) all = all && rv[u][q].y == e && rv[u][q].w == e;
-          }
-        }
-        if (all || dead) break;
-        if ((tries & 63u) == 0) {
-          volatile int* err = hdr + kErrWord;
-          if (err[0] != 0 || now_ns() - t0 > tv.timeout_ns) {
-            if (atomicCAS(hdr + kErrWord, 0, 1) == 0) {
-              int late = b0;  // first source of the batch whose data has not landed
-#pragma unroll
-              for (int u = 3; u >= 0; --u)
-                if (b0 + u < tv.world && b0 + u != tv.rank && (rv[u][0].y != e || rv[u][3].w != e)) late = b0 + u;
-              err[1] = late; err[2] = row; err[3] = 0;
-            }
-            dead = true;
-            break;
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int src = b0 + u;
-        if (src >= tv.world) continue;
-        if (src == tv.rank) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) d[k] += mine[k];
-          continue;
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          d[2 * q] += __uint_as_float(rv[u][q].x);
-          d[2 * q + 1] += __uint_as_float(rv[u][q].z);
+      for (int q = 0; q < 4; ++q) all = all && rv[q].y == e && rv[q].w == e;
+      if (all || dead) break;
+      if ((tries & 63u) == 0) {
+        volatile int* err = hdr + kErrWord;
+        if (err[0] != 0 || now_ns() - t0 > tv.timeout_ns) {
+          if (atomicCAS(hdr + kErrWord, 0, 1) == 0) { err[1] = peer; err[2] = row; err[3] = 0; }
+          dead = true;
+          break;
         }
       }
     }
+    float* dst = recv_s + ((size_t)peer * PK + pk) * 8;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) delta_s[i * 8 + k] = rnd(d[k]);
+    for (int q = 0; q < 4; ++q) {
+      dst[2 * q] = __uint_as_float(rv[q].x);
+      dst[2 * q + 1] = __uint_as_float(rv[q].z);
+    }
   }
   __syncthreads();
 
-  uint4* xr = reinterpret_cast<uint4*>(x + (long)row * ldx);
-  float v[PKT][8];
+  float v[8];
   float ss = 0.f;
-  if (tid < VT) {
+  const bool owner = pj == 0 && i < npk;
+  if (owner) {
+    float dsum[8];
 #pragma unroll
-    for (int p = 0; p < PKT; ++p) {
-      const int i = tid + p * VT;
-      if (i < npk) {
-        widen8(xr[i], v[p]);
+    for (int k = 0; k < 8; ++k) dsum[k] = 0.f;
+    for (int src = 0; src < tv.world; ++src) {
+      if (src == tv.rank) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) v[p][k] = rnd(v[p][k] + delta_s[i * 8 + k]);
-        xr[i] = narrow8(v[p]);
+        for (int k = 0; k < 8; ++k) dsum[k] += mine[k];
+      } else {
+        const float* rp = recv_s + ((size_t)src * PK + pk) * 8;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) ss = fmaf(v[p][k], v[p][k], ss);
+        for (int k = 0; k < 8; ++k) dsum[k] += rp[k];
       }
     }
-  }
-  const float inv = rsqrtf(block_allsum(ss, scratch) / (float)H + eps);
-  if (tid < VT) {
-    uint4* orow = reinterpret_cast<uint4*>(out + (long)row * ldo);
+    uint4* xr = reinterpret_cast<uint4*>(x + (long)row * ldx);
+    widen8(xr[i], v);
 #pragma unroll
-    for (int p = 0; p < PKT; ++p) {
-      const int i = tid + p * VT;
-      if (i < npk) {
-        float g[8], y[8];
-        widen8(__ldg(reinterpret_cast<const uint4*>(w) + i), g);
+    for (int k = 0; k < 8; ++k) v[k] = rnd(v[k] + rnd(dsum[k]));
+    xr[i] = narrow8(v);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) y[k] = v[p][k] * inv * (1.0f + g[k]);
-        orow[i] = narrow8(y);
-      }
-    }
+    for (int k = 0; k < 8; ++k) ss = fmaf(v[k], v[k], ss);
   }
-  // every thread read the sequence number before the barriers above
-  if (tid == 0) *(volatile int*)(hdr + row) = (int)e;
+  const float mine_ss = block_allsum(ss, scratch);
+  if (tid < kCX) *cluster.map_shared_rank(&ss_all[cs], tid) = mine_ss;
+  cluster.sync();
+  float total = 0.f;
+#pragma unroll
+  for (int c = 0; c < kCX; ++c) total += ss_all[c];
+  const float inv = rsqrtf(total / (float)H + eps);
+  if (owner) {
+    float g[8], y[8];
+    widen8(__ldg(reinterpret_cast<const uint4*>(w) + i), g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) y[k] = v[k] * inv * (1.0f + g[k]);
+    reinterpret_cast<uint4*>(out + (long)row * ldo)[i] = narrow8(y);
+  }
+  // every CTA of the cluster read the sequence number before the cluster barrier above
+  if (cs == 0 && tid == 0) *(volatile int*)(hdr + row) = (int)e;
 }
 
 __device__ __forceinline__ bool beats(float a, int ia, float b, int ib) {
@@ -432,25 +417,29 @@ extern "C" int qe_tp_exchange_norm(void* comm, void* x, const float* part, const
   if (!comm) return QE_ERR_ARG;
   const Comm* c = static_cast<Comm*>(comm);
   const int H = c->v.H, npk = H / 8;
-  if (rows < 1 || rows > kRows || H > 8 * 256 * 4 || ldx % 8 || ldo % 8 || ldp % 4 || !aligned16(x) ||
-      !aligned16(out) || !aligned16(w) || !aligned16(part))
+  if (rows < 1 || rows > kRows || ldx % 8 || ldo % 8 || ldp % 4 || !aligned16(x) || !aligned16(out) ||
+      !aligned16(w) || !aligned16(part))
     return QE_ERR_ARG;
-  // norm layout of qe_rmsnorm1p: VT threads x PKT packets
-  const int VT = npk <= 256 ? std::max(32, (npk + 31) / 32 * 32) : 256;
-  const int threads = std::max(VT, std::min(kXThreads, (npk + 31) / 32 * 32));
-  const size_t smem = (size_t)H * sizeof(float);
-  cudaStream_t s = (cudaStream_t)stream;
-  bf16* X = (bf16*)x;
-  const bf16* W = (const bf16*)w;
-  bf16* O = (bf16*)out;
-  if (npk <= 256)
-    return (int)launch(tp_xnorm_kernel<1>, dim3(rows), dim3(threads), smem, s, pdl_on(), c->v, X, part, W, O, H, VT,
-                       ldx, ldp, ldo, eps);
-  if (npk <= 512)
-    return (int)launch(tp_xnorm_kernel<2>, dim3(rows), dim3(threads), smem, s, pdl_on(), c->v, X, part, W, O, H, VT,
-                       ldx, ldp, ldo, eps);
-  return (int)launch(tp_xnorm_kernel<4>, dim3(rows), dim3(threads), smem, s, pdl_on(), c->v, X, part, W, O, H, VT,
-                     ldx, ldp, ldo, eps);
+  const int PK = (npk + kCX - 1) / kCX;                      // packets per CTA
+  const int lanes = PK * std::max(1, c->v.world - 1);        // one thread per (peer, packet)
+  const int threads = std::max(32, (lanes + 31) / 32 * 32);
+  if (threads > 1024) return QE_ERR_ARG;                     // hidden sizes beyond 8 * 8 * 146 per rank pair
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(kCX, rows, 1);
+  lc.blockDim = dim3(threads, 1, 1);
+  lc.dynamicSmemBytes = (size_t)c->v.world * PK * 8 * sizeof(float);
+  lc.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = kCX;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = pdl_on() ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&lc, tp_xnorm_kernel, c->v, (bf16*)x, part, (const bf16*)w, (bf16*)out, H, PK, ldx,
+                                 ldp, ldo, eps);
 }
 
 extern "C" int qe_tp_exchange_argmax(void* comm, const float* cand_v, const int* cand_i, int rows, int* out,

@@ -68,6 +68,7 @@ struct GemvArgs {
   int* counters;   // one arrival counter per tile, zero on entry, left zero
   int K, G, total;
   int nctas;       // CTAs that own work (<= gridDim.x)
+  int nwarps;      // warps of a CTA that own work (small matrices keep min_units per warp)
   int quantum;     // ranges start at multiples of this many units (4 when G % 4 == 0, else 1)
   int xvec;        // x rows are 16-byte aligned with ldx % 8 == 0
   // fused residual + RMSNorm prologue (h_in != nullptr)
@@ -95,12 +96,12 @@ constexpr int kWaitLimit = 1 << 20;
 __device__ __host__ __forceinline__ int cta_begin(int total, int q, int nctas, int c) {
   return q * share_begin(total / q, nctas, c);
 }
-template <int NW>
-__device__ __forceinline__ void warp_range(int total, int q, int nctas, int cta, int warp, int& u0, int& u1) {
+__device__ __forceinline__ void warp_range(int total, int q, int nctas, int nwarps, int cta, int warp, int& u0,
+                                           int& u1) {
   if (cta >= nctas) { u0 = u1 = total; return; }
   const int b = share_begin(total / q, nctas, cta), e = share_begin(total / q, nctas, cta + 1);
-  u0 = q * (b + share_begin(e - b, NW, warp));
-  u1 = q * (b + share_begin(e - b, NW, warp + 1));
+  u0 = q * (b + share_begin(e - b, nwarps, min(warp, nwarps)));
+  u1 = q * (b + share_begin(e - b, nwarps, min(warp + 1, nwarps)));
 }
 
 // x fragment of a lane for the ragged cases (misaligned rows, or the last group when K is not a
@@ -338,7 +339,7 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
     }
   };
   auto range_of = [&](const GemvArgs& a, int& u0, int& u1) {
-    warp_range<NW>(a.total, a.quantum, a.nctas, blockIdx.x, warp, u0, u1);
+    warp_range(a.total, a.quantum, a.nctas, a.nwarps, blockIdx.x, warp, u0, u1);
   };
 
   // weights never depend on the producer of x: the first stages are requested before the
@@ -416,15 +417,23 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
     const bool all_fast = xfast && !tail_k && (a.quantum % PERW) == 0;
     if (all_fast) {
       const unsigned char* xg = xbase + (size_t)g * 256;
+      // the next stage to request from HBM: whole stages only in this loop, so the copy sizes are
+      // constants and the global addresses advance by constants
+      const unsigned char* gw = reinterpret_cast<const unsigned char*>(a.qw) + (size_t)(u0 + STAGES * PERW) * 1024;
+      const unsigned char* gs = reinterpret_cast<const unsigned char*>(a.scales) + (size_t)(u0 + STAGES * PERW) * 32;
+      int to_request = nstage - STAGES;  // stages not yet requested
 #pragma unroll 1
       for (int st = 0; st < nstage && ok; ++st) {
-        if (!bar_wait(&full[warp][slot], phase, kWaitLimit)) {
+        uint64_t* bar = &full[warp][slot];
+        if (!bar_wait(bar, phase, kWaitLimit)) {
           ok = false;
           atomicExch(&g_w4_error, 1);
           break;
         }
-        const uint4* wp = reinterpret_cast<const uint4*>(ring_w + (size_t)slot * kStageW) + lane;
-        const unsigned short* sp = reinterpret_cast<const unsigned short*>(ring_s + (size_t)slot * kStageS) + r;
+        unsigned char* stage_w = ring_w + (size_t)slot * kStageW;
+        unsigned char* stage_s = ring_s + (size_t)slot * kStageS;
+        const uint4* wp = reinterpret_cast<const uint4*>(stage_w) + lane;
+        const unsigned short* sp = reinterpret_cast<const unsigned short*>(stage_s) + r;
         const uint4* xp = reinterpret_cast<const uint4*>(xg);
         UnitOps ops[PERW];
 #pragma unroll
@@ -447,9 +456,16 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
           xg = xbase + (size_t)g * 256;
         }
         __syncwarp();  // every lane has read this stage: hand its slot back to the copy engine
-        if (lane == 0 && st + STAGES < nstage) {
-          async_proxy_fence();
-          fill(a, u0, u1, st + STAGES, st + STAGES + 1, slot);
+        if (to_request > 0) {
+          if (lane == 0) {
+            async_proxy_fence();
+            bar_expect(bar, kStageW + kStageS);
+            bulk_g2s(stage_w, gw, kStageW, bar);
+            bulk_g2s(stage_s, gs, kStageS, bar);
+          }
+          gw += kStageW;
+          gs += kStageS;
+          --to_request;
         }
         if (++slot == STAGES) { slot = 0; phase ^= 1; }
       }
@@ -652,7 +668,7 @@ const std::vector<ShapeCfg>& env_overrides() {
 struct Resolved {
   qe_w4_plan plan;
   const Geometry* geom;
-  int nctas, quantum;
+  int nctas, nwarps, quantum;
 };
 
 // Shape-only launch policy (never N): as many warps as there are units / min_units, at most one
@@ -675,7 +691,10 @@ Resolved resolve(const qe_w4_params& p, const qe_w4_cfg& c_in) {
   // when the tiles are a whole number of quanta long, so that a stage never straddles two tiles
   const long quantum = (G % 4 == 0) ? 4 : 1;  // the same for every ring geometry: same split, same bits
   const long want = (units + min_units - 1) / min_units;  // warps that would each get min_units
-  const long ctas = std::max<long>(1, std::min<long>({ctas_max, (want + r.geom->nw - 1) / r.geom->nw, units / quantum}));
+  // small matrices: as many CTAs as possible (every SM pulls from HBM), fewer warps in each
+  const long ctas = std::max<long>(1, std::min<long>({ctas_max, want, units / quantum}));
+  const long per_cta = (units + ctas - 1) / ctas;
+  r.nwarps = (int)std::max<long>(1, std::min<long>(r.geom->nw, (per_cta + min_units - 1) / min_units));
   r.quantum = (int)quantum;
   r.nctas = (int)ctas;
   r.plan.mode = 4;
@@ -723,6 +742,7 @@ int make_job(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg,
   a.G = p->Kp / 128;
   a.total = (p->Mp / 16) * a.G;
   a.nctas = r.nctas;
+  a.nwarps = r.nwarps;
   a.quantum = r.quantum;
   a.xvec = ((p->ldx & 7) == 0 && aligned16(p->x)) ? 1 : 0;
   *smem_extra = 0;

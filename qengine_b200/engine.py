@@ -215,9 +215,10 @@ class _Residual:
             e.tp.exchange_norm(self.h, e.part32[:n], w, out, e.cfg.eps)
         self.owed = False
 
-    def through(self, w, p, out, lin, keep_normed=None, ordered=False):
+    def through(self, w, p, out, lin, keep_normed=None, ordered=False, prefetch=None):
         """out = p(norm(h + owed)); keep_normed optionally receives the normed rows. ordered: this
-        is the launch that opens a pass (no programmatic overlap with the previous pass)."""
+        is the launch that opens a pass (no programmatic overlap with the previous pass).
+        prefetch: a tensor the kernel after this GEMV reads from HBM (an L2 hint)."""
         e, n = self.e, self.n
         w4 = isinstance(p, W4Packed) and isinstance(lin, W4Linear)
         if e.fuse and w4 and n > e.FUSE_MAX_ROWS:
@@ -233,25 +234,26 @@ class _Residual:
                 lin.norm_rows(self.h, e.mo[:n] if self.owed else None, w, e.cfg.eps, xn,
                               h_out=self.h if self.owed else None, **kw)
             self.owed = False
-            e._gemv(lin.job(xn, p, out))
+            e._gemv(lin.job(xn, p, out, prefetch=prefetch))
             return
         if e.fuse and w4:
             if self.tok is not None:
                 j = lin.job_after_norm(e.embed, None, w, e.cfg.eps, p, out, tok=self.tok, h_out=self.h,
-                                       xn_out=keep_normed)
+                                       xn_out=keep_normed, prefetch=prefetch)
                 self.tok = None
             elif self.owed:
-                j = lin.job_after_norm(self.h, e.mo[:n], w, e.cfg.eps, p, out, h_out=self.spare, xn_out=keep_normed)
+                j = lin.job_after_norm(self.h, e.mo[:n], w, e.cfg.eps, p, out, h_out=self.spare, xn_out=keep_normed,
+                                       prefetch=prefetch)
                 self.h, self.spare = self.spare, self.h
             else:
-                j = lin.job_after_norm(self.h, None, w, e.cfg.eps, p, out, xn_out=keep_normed)
+                j = lin.job_after_norm(self.h, None, w, e.cfg.eps, p, out, xn_out=keep_normed, prefetch=prefetch)
             self.owed = False
             e._gemv(j, ordered=ordered)
             return
         xn = keep_normed if keep_normed is not None else self.xn
         self._norm(w, xn)
         if w4:
-            e._gemv(lin.job(xn, p, out))
+            e._gemv(lin.job(xn, p, out, prefetch=prefetch))
         else:
             e._flush()
             lin(xn, p, out)

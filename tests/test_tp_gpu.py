@@ -180,10 +180,12 @@ def test_exchange_norm_against_prefilled_peers(H, world, rank):
             assert fw.error()[0] == 0
             xr, ref = _norm_ref(x0, parts, w)
             assert torch.equal(x, xr)
-            # the same bits as the norm over gathered parts, and what every peer received is our row
+            # the norm over gathered parts (library-collective transport) sums the squares in another
+            # order: same residual rows, normed rows within one ulp; every peer received our row
+            from util import bf16_ulp_close
             x2, out2 = x0.clone(), torch.empty_like(x)
             _C.rmsnorm1p_parts(x2, torch.stack(parts), w, out2, 1e-6)
-            assert torch.equal(out, out2) and torch.equal(x, x2)
+            assert torch.equal(x, x2) and bf16_ulp_close(out, out2, ulps=1)[0]
             assert float(((out.float() - ref.float()).abs() / ref.float().abs().clamp_min(1e-2)).max()) < 2 ** -6
             for peer in range(world):
                 if peer == rank:
@@ -347,7 +349,7 @@ def _engine_worker(rank, world, transport, small8=False):
         ref_lg = one.sequence_logits(seq)
         _, ref_mlg = one.mtp_rows_logits(seq[:12])
         ref_plain = one.generate(prompt, 40)
-        if world == 1:  # a group of one rank adds the exchange but no arithmetic
+        if world == 1 and transport == "nccl":  # same kernels, no exchange: the same bits
             assert torch.equal(lg, ref_lg) and torch.equal(mlg, ref_mlg) and plain == ref_plain
         cs = min(cosine(lg[t], ref_lg[t]) for t in range(len(seq)))
         cm = min(cosine(mlg[t], ref_mlg[t]) for t in range(12))
@@ -367,7 +369,10 @@ def _engine_worker(rank, world, transport, small8=False):
 
 
 @pytest.mark.parametrize("transport", ["peer", "nccl"])
-def test_tp_engine_group_of_one_is_bit_identical(transport):
+def test_tp_engine_group_of_one(transport):
+    """One rank: with the library-collective transport the kernels are those of the unfused single-GPU
+    engine (bit-identical); the peer transport's exchange kernel sums the squares of the norm in its
+    own order (cosine, token checks)."""
     _spawn(_engine_worker, 1, transport)
 
 
