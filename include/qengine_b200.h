@@ -257,10 +257,7 @@ typedef struct qe_w4_plan {
  *   NULL, h_in is an embedding table [vocab, K] and row r is table[tok[r]] (zeros when out of
  *   range). Needs K == Kp, 16-byte aligned rows, row strides that are multiples of 8, and
  *   N * (2 K + 16) bytes of shared memory beside the weight rings (QE_ERR_ARG otherwise: run
- *   qe_rmsnorm1p and qe_w4_gemv instead).
- *   Prefetch (prefetch_bytes > 0): every block asks L2 for its slice of [prefetch,
- *   prefetch + prefetch_bytes) before it waits for its input -- the weights of a later GEMV, so
- *   that HBM keeps working while short dependent kernels run. A hint; no effect on results. */
+ *   qe_rmsnorm1p and qe_w4_gemv instead). */
 typedef struct qe_w4_norm {
   const void* h_in;    /* bf16 [N, K] rows (stride ldh), or the embedding table when tok != NULL */
   const int* tok;      /* optional token ids [N] */
@@ -271,8 +268,6 @@ typedef struct qe_w4_norm {
   void* xn_out;        /* optional bf16 [N, K], stride ldxo */
   long ldh, ldd, ldho, ldxo;
   float eps;
-  const void* prefetch;
-  size_t prefetch_bytes;
 } qe_w4_norm;
 
 /* Default-initialise a cfg (all auto, pdl on, min_units 4). */
@@ -283,7 +278,7 @@ int qe_w4_plan_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, qe_w4_plan* pla
 int qe_w4_auto_ksplit(int Mp, int Kp, int N, int warps);
 /* Replaces launch_gemv_w4 (gemv_w4.h:56). */
 int qe_w4_gemv(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
-/* qe_w4_gemv with the fused prologue / prefetch hint described at qe_w4_norm (nrm may be NULL). */
+/* qe_w4_gemv with the fused prologue described at qe_w4_norm (nrm may be NULL). */
 int qe_w4_gemv_ex(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg, void* stream);
 /* The prologue of qe_w4_gemv_ex as a launch of its own: xn_out[r] = RMSNorm1p(h_in[r] + delta[r]) *
  * (1 + norm_w) and h_out[r] = bf16(h_in[r] + delta[r]) for r < N, one block per row, with exactly

@@ -31,7 +31,7 @@ class W4Norm(C.Structure):
     """struct qe_w4_norm"""
     _fields_ = [("h_in", P), ("tok", P), ("vocab", c_int), ("delta", P), ("norm_w", P), ("h_out", P),
                 ("xn_out", P), ("ldh", c_long), ("ldd", c_long), ("ldho", c_long), ("ldxo", c_long),
-                ("eps", c_float), ("prefetch", P), ("prefetch_bytes", c_size_t)]
+                ("eps", c_float)]
 
 
 class W4Plan(C.Structure):

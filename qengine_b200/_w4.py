@@ -127,7 +127,7 @@ def _launch(jobs, cfg, what):
     launches[0] += 1
 
 
-def job(x, qw, scales, out, M, swiglu=False, prefetch=None, allow_f32_out=False) -> Job:
+def job(x, qw, scales, out, M, swiglu=False, allow_f32_out=False) -> Job:
     """Describe out = x @ W~^T (or the SwiGLU of a gate/up pack) without launching it."""
     for t in (x, qw, scales, out):
         _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
@@ -150,15 +150,11 @@ def job(x, qw, scales, out, M, swiglu=False, prefetch=None, allow_f32_out=False)
     _req(x.data_ptr() != out.data_ptr(), "in-place not supported")
     p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None,
                  M, K, Mp, Kp, N, x.stride(0), out.stride(0), epilogue, int(out_f32))
-    nrm = None
-    if prefetch is not None:  # L2 hint only: no prologue
-        nrm = W4Norm()
-        nrm.prefetch, nrm.prefetch_bytes = prefetch.data_ptr(), prefetch.numel() * prefetch.element_size()
-    return Job(p, nrm, x.device, (x, qw, scales, out, prefetch))
+    return Job(p, None, x.device, (x, qw, scales, out))
 
 
 def job_fused(h_in, delta, norm_w, eps, qw, scales, out, M, h_out=None, xn_out=None, tok=None,
-              swiglu=False, prefetch=None) -> Job:
+              swiglu=False) -> Job:
     """Describe out = gemv(RMSNorm1p(h_in + delta) * (1 + norm_w)) without launching it (see
     `gemv_fused` for the arguments)."""
     for t in (h_in, norm_w, qw, scales, out):
@@ -192,11 +188,9 @@ def job_fused(h_in, delta, norm_w, eps, qw, scales, out, M, h_out=None, xn_out=N
         nrm.h_out, nrm.ldho = h_out.data_ptr(), h_out.stride(0)
     if xn_out is not None:
         nrm.xn_out, nrm.ldxo = xn_out.data_ptr(), xn_out.stride(0)
-    if prefetch is not None:
-        nrm.prefetch, nrm.prefetch_bytes = prefetch.data_ptr(), prefetch.numel() * prefetch.element_size()
     p = W4Params(qw.data_ptr(), scales.data_ptr(), None, out.data_ptr(), None, None, M, Kp, Mp, Kp, N,
                  0, out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, 0)
-    return Job(p, nrm, out.device, (h_in, delta, norm_w, qw, scales, out, h_out, xn_out, tok, prefetch))
+    return Job(p, nrm, out.device, (h_in, delta, norm_w, qw, scales, out, h_out, xn_out, tok))
 
 
 def gemv_chain(jobs, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1, blocks_per_sm=0, min_units=4):
@@ -212,11 +206,9 @@ def gemv_chain(jobs, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1, 
 
 
 def gemv(x, qw, scales, out, M, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
-         blocks_per_sm=0, min_units=4, prefetch=None):
-    """out[N, M] = x[N, K] @ W~^T (W packed by quant.quantize_w4). prefetch (not in the reference):
-    a tensor whose bytes a later kernel will stream; the launch asks L2 for them before it waits
-    for its own input."""
-    _launch([job(x, qw, scales, out, M, prefetch=prefetch)],
+         blocks_per_sm=0, min_units=4):
+    """out[N, M] = x[N, K] @ W~^T (W packed by quant.quantize_w4)."""
+    _launch([job(x, qw, scales, out, M)],
             _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units), "gemv_w4")
 
 
@@ -237,16 +229,16 @@ def gemv_partial(x, qw, scales, out32, M, warps=0, unroll=0, ksplit=0, pdl=True,
 
 
 def gemv_fused(h_in, delta, norm_w, eps, qw, scales, out, M, *, h_out=None, xn_out=None, tok=None,
-               swiglu=False, prefetch=None, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
+               swiglu=False, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
                blocks_per_sm=0, min_units=4):
     """Not in the reference: out = gemv(RMSNorm1p(h_in + delta) * (1 + norm_w)) in one launch.
 
     h_in bf16 [N, K]; delta bf16 [N, K] or None; h_out (optional, must not alias h_in) receives
     bf16(h_in + delta) and xn_out (optional) the normed rows. With `tok` (int32 [>= N]) h_in is an
-    embedding table [V, K] and row r is table[tok[r]]. `prefetch` = a tensor whose bytes a later
-    kernel will stream (an L2 hint). Same arithmetic as `_C.rmsnorm1p` followed by `gemv`."""
+    embedding table [V, K] and row r is table[tok[r]]. Same arithmetic as `_C.rmsnorm1p` followed
+    by `gemv`."""
     _launch([job_fused(h_in, delta, norm_w, eps, qw, scales, out, M, h_out=h_out, xn_out=xn_out, tok=tok,
-                       swiglu=swiglu, prefetch=prefetch)],
+                       swiglu=swiglu)],
             _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units), "gemv_w4 fused")
 
 

@@ -113,10 +113,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                    sa(dst)), "l"(src), "r"(bytes), "r"(sa(bar))
                : "memory");
 }
-// Hint: bring [p, p + bytes) into L2 (no destination, no completion); bytes a multiple of 16.
-__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void async_proxy_fence() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

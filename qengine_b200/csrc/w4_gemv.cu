@@ -81,9 +81,6 @@ struct GemvArgs {
   bf16* xn_out;
   long ldh, ldd, ldho, ldxo;
   float eps;
-  // optional L2 prefetch of memory a later kernel will stream
-  const unsigned char* pf;
-  unsigned long long pf_bytes;
 };
 
 __device__ int g_w4_error = 0;
@@ -314,7 +311,6 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
   unsigned char* ring_s = ring_w + (size_t)STAGES * kStageW;
   float* part = reinterpret_cast<float*>(smem + (size_t)NW * kRing);  // [NW][2][128]
   unsigned char* x_s = smem + (size_t)NW * kRing + (size_t)NW * 2 * 128 * sizeof(float);
-  const int worker = blockIdx.x * NW + warp;
 
   if (lane == 0) {
     for (int s = 0; s < STAGES; ++s) bar_init(&full[warp][s], 1);
@@ -360,13 +356,6 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
     if (lane == 0) {
       s_rb[warp] = u0;
       if (warp == NW - 1) s_rb[NW] = u1;
-      if (a.pf_bytes) {  // this warp's slice of the hinted range, 16 KB per request
-        const unsigned long long nslices = (unsigned long long)gridDim.x * NW;
-        const unsigned long long per = ((a.pf_bytes + nslices - 1) / nslices + 15) & ~15ull;
-        unsigned long long b = per * (unsigned long long)worker;
-        const unsigned long long e = min(a.pf_bytes & ~15ull, b + per);
-        for (; b < e; b += 16384) l2_prefetch(a.pf + b, (uint32_t)min(16384ull, e - b));
-      }
     }
     const int n_units = u1 - u0;
     const int nstage = (n_units + PERW - 1) / PERW;
@@ -765,10 +754,6 @@ int make_job(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg,
     a.eps = nrm->eps;
   } else if (!p->x) {
     return QE_ERR_ARG;
-  }
-  if (nrm && nrm->prefetch && nrm->prefetch_bytes) {
-    a.pf = reinterpret_cast<const unsigned char*>(nrm->prefetch);
-    a.pf_bytes = nrm->prefetch_bytes;
   }
   return 0;
 }

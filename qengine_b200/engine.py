@@ -98,8 +98,8 @@ class W4Linear:
     # The same four operations as job descriptions, for `launch` below: the engine queues the
     # GEMVs that follow one another without another kernel in between and runs them as one chain.
     @staticmethod
-    def job(x, p, out, prefetch=None):
-        return _w4.job(x, p.qw, p.scales, out, p.M, swiglu=p.gate_up, prefetch=prefetch)
+    def job(x, p, out):
+        return _w4.job(x, p.qw, p.scales, out, p.M, swiglu=p.gate_up)
 
     @staticmethod
     def job_partial(x, p, out32):
@@ -215,10 +215,9 @@ class _Residual:
             e.tp.exchange_norm(self.h, e.part32[:n], w, out, e.cfg.eps)
         self.owed = False
 
-    def through(self, w, p, out, lin, keep_normed=None, ordered=False, prefetch=None):
+    def through(self, w, p, out, lin, keep_normed=None, ordered=False):
         """out = p(norm(h + owed)); keep_normed optionally receives the normed rows. ordered: this
-        is the launch that opens a pass (no programmatic overlap with the previous pass).
-        prefetch: a tensor the kernel after this GEMV reads from HBM (an L2 hint)."""
+        is the launch that opens a pass (no programmatic overlap with the previous pass)."""
         e, n = self.e, self.n
         w4 = isinstance(p, W4Packed) and isinstance(lin, W4Linear)
         if e.fuse and w4 and n > e.FUSE_MAX_ROWS:
@@ -234,26 +233,25 @@ class _Residual:
                 lin.norm_rows(self.h, e.mo[:n] if self.owed else None, w, e.cfg.eps, xn,
                               h_out=self.h if self.owed else None, **kw)
             self.owed = False
-            e._gemv(lin.job(xn, p, out, prefetch=prefetch))
+            e._gemv(lin.job(xn, p, out))
             return
         if e.fuse and w4:
             if self.tok is not None:
                 j = lin.job_after_norm(e.embed, None, w, e.cfg.eps, p, out, tok=self.tok, h_out=self.h,
-                                       xn_out=keep_normed, prefetch=prefetch)
+                                       xn_out=keep_normed)
                 self.tok = None
             elif self.owed:
-                j = lin.job_after_norm(self.h, e.mo[:n], w, e.cfg.eps, p, out, h_out=self.spare, xn_out=keep_normed,
-                                       prefetch=prefetch)
+                j = lin.job_after_norm(self.h, e.mo[:n], w, e.cfg.eps, p, out, h_out=self.spare, xn_out=keep_normed)
                 self.h, self.spare = self.spare, self.h
             else:
-                j = lin.job_after_norm(self.h, None, w, e.cfg.eps, p, out, xn_out=keep_normed, prefetch=prefetch)
+                j = lin.job_after_norm(self.h, None, w, e.cfg.eps, p, out, xn_out=keep_normed)
             self.owed = False
             e._gemv(j, ordered=ordered)
             return
         xn = keep_normed if keep_normed is not None else self.xn
         self._norm(w, xn)
         if w4:
-            e._gemv(lin.job(xn, p, out, prefetch=prefetch))
+            e._gemv(lin.job(xn, p, out))
         else:
             e._flush()
             lin(xn, p, out)

@@ -429,18 +429,6 @@ def test_fused_prologue_rejects_what_it_cannot_serve(api):
                       torch.empty(1, 64, dtype=torch.bfloat16, device=DEV), 64)
 
 
-def test_prefetch_hint_changes_nothing(api):
-    p = api["q"](rand_w(5120, 6144, seed=84))
-    nxt = api["q"](rand_w(2048, 5120, seed=85))
-    x = rand_x(3, 6144, seed=86)
-    a = api["gemv"](x, p)
-    b = api["gemv"](x, p, prefetch=nxt.qw)
-    assert torch.equal(bits(a), bits(b))
-
-
-# ---------------------------------------------------------------------------------------------
-# Chains: several dependent GEMVs as one cooperative launch
-# ---------------------------------------------------------------------------------------------
 def _block_tensors(api, Hh, Ii, Vd, seed):
     """out-projection, gate/up, down and the next in_proj of a decoder block of width Hh."""
     g = torch.Generator(device=DEV).manual_seed(seed)
