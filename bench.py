@@ -15,6 +15,8 @@ reference's own torch path (oracle/_ref, else the oracle's restatement of it); a
 `tp_parity` compares the tensor-parallel engine's logits with the single-GPU engine's.
 
 --impl reference times that CPU path as an arm of its own (rank 0 only).
+--impl reference-gpu (one GPU) runs the unmodified reference engine on its own kernels, built for
+sm_100a by baseline/build_ref.py, on the same synthetic model, and this library beside it.
 """
 from __future__ import annotations
 
@@ -224,6 +226,96 @@ def run_reference_arm(a):
 # ----------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------
+def run_reference_gpu(a):
+    """Same-box comparator: the unmodified reference engine on its own kernels, compiled for
+    sm_100a by baseline/build_ref.py, decoding the same synthetic 27B-shape model. The model is
+    handed over through the reference's public route for prepared weights: a cache directory in
+    its layout (qengine_b200.cache.save_cache) plus a config.json. The same directory is then
+    loaded into this repository's engine, so both engines multiply with the same bytes."""
+    import shutil
+    import tempfile
+    import torch
+    from qengine_b200 import cache, synth
+    from qengine_b200.engine import Engine as Ours
+
+    native = str(ROOT / "baseline" / "_ref" / "native" / "python")
+    if not os.path.exists(os.path.join(native, "qengine", "engine.py")):
+        print(json.dumps({"impl": "reference-gpu", "unavailable": "baseline/_ref/native is not built "
+                          "(python baseline/build_ref.py needs the reference checkout)"}), flush=True)
+        return
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = synth.qwen27b_config(layers=a.layers)
+    n_new, P = a.tokens, a.prompt
+    tmp = tempfile.mkdtemp(prefix="qe_cache_")
+    try:
+        model_dir = os.path.join(tmp, "synthetic-27b")
+        cache.write_config(model_dir, cfg)
+        W = synth.build_model(cfg, seed=1, device=dev, scale_std=0.01)
+        t0 = time.perf_counter()
+        cdir = cache.save_cache(cache.cache_path(os.path.join(tmp, "cache"), "synthetic-27b"), W)
+        save_s = time.perf_counter() - t0
+        del W
+        torch.cuda.empty_cache()
+        prompt = synth.prompt_ids(P, cfg.vocab, seed=1234)
+
+        sys.path.insert(0, native)
+        from qengine.engine import Engine as Ref, W4Linear as RefW4  # the reference's own classes
+        t0 = time.perf_counter()
+        ref = Ref(model_dir, max_len=P + n_new + 32, linear=RefW4(), device="cuda",
+                  cache_dir=os.path.join(tmp, "cache"))
+        load_s = time.perf_counter() - t0
+        for _ in range(max(1, a.warmup)):
+            ref.generate(prompt, n_new)
+        sampler = ClockSampler(0)
+        sampler.start()
+        dec, e2e = [], []
+        for _ in range(a.steps):
+            t0 = time.perf_counter()
+            gen_ref, _, d = ref.generate(prompt, n_new, timing=True)
+            e2e.append(time.perf_counter() - t0)
+            dec.append(d)
+        clocks = sampler.stop()
+        ref_tok_s = a.steps * (n_new - 1) / sum(dec)
+        spec = {}
+        if not a.no_mtp:
+            ref.generate_spec(prompt, n_new, 4)
+            out, _, d, st = ref.generate_spec(prompt, n_new, 4, timing=True)
+            spec = {"tok_s": (n_new - 1) / d, "tokens_per_cycle": st["tokens_per_cycle"],
+                    "ms_per_cycle": d * 1e3 / max(1, st["cycles"]), "identical_to_plain": out == gen_ref}
+        del ref
+        torch.cuda.empty_cache()
+
+        ours = Ours.from_cache(model_dir, os.path.join(tmp, "cache"), device=dev, max_len=P + n_new + 32)
+        for _ in range(max(1, a.warmup)):
+            ours.generate(prompt, n_new)
+        dec2 = []
+        for _ in range(a.steps):
+            gen_ours, _, d = ours.generate(prompt, n_new, timing=True)
+            dec2.append(d)
+        ours_tok_s = a.steps * (n_new - 1) / sum(dec2)
+        same = 0
+        for x, y in zip(gen_ref, gen_ours):
+            if x != y:
+                break
+            same += 1
+        print(json.dumps({
+            "impl": "reference-gpu", "metric": "batch-1 decode tok/s (plain)", "value": ref_tok_s,
+            "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": 1e3 * sum(dec) / a.steps, "higher_is_better": True, "dtype": "bf16 x int4 (W4A16)",
+            "data": "synthetic", "config": {"workload": WORKLOAD.format(layers=a.layers, prompt=P, tokens=n_new),
+                                            "route": "cache directory in the reference's layout"},
+            "e2e": {"value": a.steps * n_new / sum(e2e), "unit": "tok/s", "h2d_bytes_per_step": 4 * P,
+                    "d2h_bytes_per_step": 4 * n_new},
+            "reference_mtp_k4": spec, "clocks": clocks,
+            "this_library_same_cache": {"tok_s": ours_tok_s, "ratio_to_reference": ours_tok_s / ref_tok_s,
+                                        "leading_tokens_equal": same, "of": len(gen_ref)},
+            "cache": {"bytes": sum(os.path.getsize(os.path.join(cdir, f)) for f in os.listdir(cdir)),
+                      "save_s": save_s, "reference_load_s": load_s}}), flush=True)
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+
 def w4_sequence_timing(eng, n_rows, reps=10):
     """Every W4 GEMV of one token (all layers in order, then the lm_head) as one CUDA graph on the
     model's own weights: the dominant kernel timed alone, in situ shapes, nothing reused in L2.
@@ -621,7 +713,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--layers", type=int, default=64, help="model depth (64 = the 27B shape)")
     ap.add_argument("--tokens", type=int, default=N_NEW, help="generated tokens per step")
     ap.add_argument("--prompt", type=int, default=PROMPT_LEN, help="prompt length (profiling runs use a short one)")
@@ -639,6 +731,8 @@ def main():
     a = ap.parse_args()
     if a.impl == "reference":
         run_reference_arm(a)
+    elif a.impl == "reference-gpu":
+        run_reference_gpu(a)
     else:
         run_ours(a)
 

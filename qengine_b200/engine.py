@@ -64,6 +64,7 @@ class W4Linear:
     (python/qengine/engine.py:74-115) it is the only place that touches that API. Keyword
     arguments given at construction are forwarded to every launch."""
     name = "w4"
+    cache_tag = "w4-rtn-g128-v1"  # names the prepared-weights directory (qengine_b200.cache)
 
     def __init__(self, **launch_kw):
         self.kw = dict(launch_kw)
@@ -71,6 +72,12 @@ class W4Linear:
     def prepare(self, w):
         from .quant import quantize_w4
         return quantize_w4(w)
+
+    def prepare_from_grid(self, Wq, rows_per_step: int = 2048):
+        """Pack a matrix that is already on the W4 grid (a GPTQ lm_head) without quantising it
+        again; returns (packed, stats). See qengine_b200.cache.pack_from_grid."""
+        from .cache import pack_from_grid
+        return pack_from_grid(Wq, rows_per_step)
 
     def prepare_gate_up(self, wg, wu):
         from .quant import quantize_w4_gate_up
@@ -308,6 +315,19 @@ class Engine:
         self.force_a = -1       # forced acceptance length of verify passes (< 0: off)
         self.truth = torch.zeros(1, dtype=I32, device=self.dev)
         self.l2_win = None      # (base, bytes) of the persisting window around the draft phase
+
+    @classmethod
+    def from_cache(cls, path, cache_dir, device="cuda", linear=None, **kw):
+        """Engine over a checkpoint directory whose prepared weights were cached (by this package
+        or by the reference, python/qengine/engine.py:215-236): `path` supplies config.json, the
+        weights come from `<cache_dir>/<path name>-<linear.cache_tag>/`."""
+        from pathlib import Path
+        from . import cache
+        linear = linear or W4Linear()
+        cfg = cache.config_from_dir(path)
+        d = cache.cache_path(cache_dir, Path(path).name, linear.cache_tag)
+        weights = cache.load_cache(d, cfg, device=device, mtp=kw.get("mtp", True))
+        return cls(cfg, weights, linear=linear, device=device, **kw)
 
     # -- construction -------------------------------------------------------------------------
     def _make_draft_head(self, nv: int):

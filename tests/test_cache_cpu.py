@@ -1,0 +1,89 @@
+"""The prepared-weights cache directory (reference layout) and the GPTQ-grid repack, on CPU."""
+import pickle
+import pickletools
+
+import pytest
+import torch
+
+from qengine_b200 import cache, quant
+from qengine_b200.synth import build_model, tiny_config
+
+
+def _same(a, b):
+    if isinstance(a, quant.W4Packed):
+        return (isinstance(b, quant.W4Packed) and torch.equal(a.qw, b.qw) and torch.equal(a.scales, b.scales)
+                and (a.M, a.K, a.gate_up) == (b.M, b.K, b.gate_up))
+    if isinstance(a, torch.Tensor):
+        return a.dtype == b.dtype and torch.equal(a, b)
+    if isinstance(a, dict):
+        return a.keys() == b.keys() and all(_same(a[k], b[k]) for k in a)
+    if isinstance(a, list):
+        return len(a) == len(b) and all(_same(x, y) for x, y in zip(a, b))
+    return a == b
+
+
+def test_round_trip_in_the_reference_layout(tmp_path):
+    cfg = tiny_config()
+    W = build_model(cfg, seed=3)
+    d = cache.save_cache(cache.cache_path(tmp_path, "tiny"), W)
+    assert d.name == "tiny-w4-rtn-g128-v1"
+    names = sorted(p.name for p in d.iterdir())
+    assert names == sorted(["COMPLETE", "top.pt", "lm_head.pt", "mtp.pt"]
+                           + [f"layer{i:02d}.pt" for i in range(cfg.layers)])
+    back = cache.load_cache(d, cfg)
+    for k in ("embed", "final_norm", "lm_head", "layers", "mtp"):
+        assert _same(W[k], back[k]), k
+    # the files name the reference's class, so its engine can unpickle them
+    import zipfile
+    with zipfile.ZipFile(d / "lm_head.pt") as z:
+        pkl = z.read([n for n in z.namelist() if n.endswith("data.pkl")][0])
+    ops = [(op.name, arg) for op, arg, _ in pickletools.genops(pkl)]
+    text = " ".join(str(a) for _, a in ops if isinstance(a, str))
+    assert "qengine.quant" in text and "W4Packed" in text and "qengine_b200" not in text
+    # and the alias used for writing is gone again
+    import sys
+    assert "qengine.quant" not in sys.modules
+    assert quant.W4Packed.__module__ == "qengine_b200.quant"
+    assert pickle.loads(pickle.dumps(quant.W4Packed(torch.zeros(1), torch.zeros(1), 1, 1))).M == 1
+
+
+def test_partial_directories_are_refused(tmp_path):
+    cfg = tiny_config()
+    W = build_model(cfg, seed=4)
+    d = cache.save_cache(tmp_path / "m", W)
+    (d / "COMPLETE").unlink()
+    with pytest.raises(FileNotFoundError):
+        cache.load_cache(d, cfg)
+    (d / "COMPLETE").write_text("x\n")
+    (d / "layer01.pt").unlink()
+    with pytest.raises(FileNotFoundError):
+        cache.load_cache(d, cfg)
+
+
+def test_config_json_round_trip(tmp_path):
+    cfg = tiny_config()
+    cache.write_config(tmp_path, cfg)
+    assert cache.config_from_dir(tmp_path) == cfg
+
+
+def test_grid_repack_is_exact_on_grid_matrices():
+    g = torch.Generator().manual_seed(11)
+    M, K = 40, 384
+    W = torch.randn(M, K, generator=g) * 0.02
+    W[3, 128:256] = 0          # an all-zero group
+    p0 = quant.quantize_w4(W)
+    on_grid = quant.dequantize_w4(p0)                    # fp32 values code * scale
+    stored = on_grid.to(torch.bfloat16)                  # how a checkpoint holds them
+    p1, stats = cache.pack_from_grid(stored)
+    # the packed matrix multiplies with values that round to the stored ones
+    again = quant.dequantize_w4(p1)
+    assert torch.equal(again.to(torch.bfloat16), stored)
+    assert stats["exact_frac"] == 1.0
+    # a group that never uses code -8 or 7 still comes back exactly (no re-quantisation drift)
+    codes = torch.randint(5, 12, (16, 128), generator=g)
+    s = torch.full((16, 1), 0.0123).to(torch.float16)
+    Wg = ((codes - 8).float() * s.float()).to(torch.bfloat16)
+    p2, st2 = cache.pack_from_grid(Wg)
+    assert torch.equal(quant.dequantize_w4(p2).to(torch.bfloat16), Wg) and st2["exact_frac"] == 1.0
+    with pytest.raises(ValueError):
+        cache.pack_from_grid(torch.zeros(16, 100))

@@ -247,3 +247,69 @@ def test_engine_without_fused_norms_and_with_chains_agree(setup):
     lg = unfused.sequence_logits(seq)
     assert min(cosine(lg[t], base[t]) for t in range(len(seq))) >= 0.99999
     assert unfused.generate_spec(g["prompt"], 60, 3) == unfused.generate(g["prompt"], 60)
+
+
+def _new_engine(cfg, Wp, **kw):
+    from qengine_b200 import synth
+    from qengine_b200.engine import Engine
+    return Engine(cfg, synth.model_to(Wp, "cuda"), max_len=256, **kw)
+
+
+def test_l2_window_around_the_draft_phase_changes_no_token(setup):
+    """pin_mtp_l2 re-homes the draft layer's matrices into one arena and runs the draft phase of
+    every graph under a persisting access-policy window (reference: python/qengine/engine.py:
+    360-381, 502-519). It is a cache policy: tokens must not change, on or off."""
+    from qengine_b200 import _C, _w4
+    cfg, Wp, base = setup
+    prompt = torch.load(G / "greedy.pt")["prompt"]
+    plain = base.generate(prompt, 60)
+    eng = _new_engine(cfg, Wp)
+    names = ("fc", "in_proj", "out")
+    before = {n: eng.mtp[n].qw.data_ptr() for n in names}
+    eng.pin_mtp_l2(True)
+    assert eng.l2_win is not None and eng.l2_win[1] >= sum(eng.mtp[n].nbytes for n in names)
+    lo, hi = eng.l2_win[0], eng.l2_win[0] + eng.l2_win[1]
+    assert all(lo <= eng.mtp[n].qw.data_ptr() < hi and eng.mtp[n].qw.data_ptr() != before[n] for n in names)
+    for k in (1, 4):
+        assert eng.generate_spec(prompt, 60, k) == plain, f"window on, k={k}"
+    eng.pin_mtp_l2(False)
+    assert eng.l2_win is None and not eng.graphs
+    assert eng.generate_spec(prompt, 60, 4) == plain
+    assert eng.generate(prompt, 60) == plain
+    assert _C.attn_error() == 0 and _w4.ring_error() == 0
+
+
+def test_engine_from_a_cache_directory(setup, tmp_path):
+    """Weights written in the reference's cache layout load back into an engine that decodes the
+    same tokens (qengine_b200.cache; reference python/qengine/engine.py:215-236)."""
+    from qengine_b200 import cache
+    from qengine_b200.engine import Engine
+    cfg, Wp, base = setup
+    prompt = torch.load(G / "greedy.pt")["prompt"]
+    model_dir = tmp_path / "tiny-model"
+    cache.write_config(model_dir, cfg)
+    cache.save_cache(cache.cache_path(tmp_path / "c", "tiny-model"), Wp)
+    eng = Engine.from_cache(model_dir, tmp_path / "c", device="cuda", max_len=256)
+    assert eng.cfg == cfg
+    want = base.generate(prompt, 48)
+    assert eng.generate(prompt, 48) == want
+    assert eng.generate_spec(prompt, 48, 3) == want
+
+
+def test_bf16_lm_head_backend(setup):
+    """lm_head kept in BF16 while the layers stay W4 (the reference's lm_head="bf16" choice,
+    python/qengine/engine.py:195-208): the engine picks the BF16 GEMV for a dense head. With the
+    dense head set to the packed head's own dequantised values, logits agree up to the summation
+    order and speculative output still equals plain output."""
+    from qengine_b200 import quant
+    cfg, Wp, base = setup
+    prompt = torch.load(G / "greedy.pt")["prompt"]
+    Wd = dict(Wp)
+    Wd["lm_head"] = quant.dequantize_w4(Wp["lm_head"]).to(torch.bfloat16).contiguous()
+    eng = _new_engine(cfg, Wd)
+    a = eng.sequence_logits(prompt[:12]).float()
+    b = base.sequence_logits(prompt[:12]).float()
+    cos = torch.nn.functional.cosine_similarity(a, b, dim=-1)
+    assert cos.min() > 0.9999, cos.min()
+    plain = eng.generate(prompt, 48)
+    assert eng.generate_spec(prompt, 48, 4) == plain
