@@ -14,6 +14,8 @@
 //           and applies bf16(sigmoid(gate)).
 // Row independence: the slice boundaries of row t depend only on its own prefix length, so row t
 // of an n-row call is bit-identical to a 1-row call at position pos + t.
+#include <algorithm>
+
 #include "common.cuh"
 #include "../../include/qengine_b200.h"
 
@@ -332,26 +334,58 @@ attn_stream_kernel(const bf16* q, const bf16* kc, const bf16* vc, const int* pos
   }
 }
 
-// Tensor-core split for head dim 256 and long caches. The query heads of a KV group are the M rows
-// of mma.m16n8k16 (GQ <= 8 of 16 rows used): S = Q K^T and O += P V run on the tensor cores, which
-// removes the per-(position, head) widening, FMAs and butterfly reductions that make the CUDA-core
-// kernels issue-bound (72 warp-instructions per position and head there, about 2 here), so that the
-// layer becomes what it should be: a stream of the KV cache.
-//   CTA (row, KV head, 6 consecutive splits) = 6 warps, each a pipeline of its own on its own split
-//   (sub-slice of the row's causal prefix): it streams 16 positions per stage (K rows, V rows,
-//   512 B each, one bulk copy per row issued by lane = row, into a 528-byte pitch so that LDS.128 and ldmatrix are
-//   conflict-free) into a warp-private ring of 2 stages (33 KB per warp, 198 KB per SM in flight).
+// Tensor-core split for head dim 256 and long caches. The (pass row, query head) pairs that share a
+// KV head are the M rows of mma.m16n8k16, packed densely: pair e = row * GQ + head sits in tile
+// e / 16 at tile row e % 16, so the 30 pairs of a 5-row verify pass over 6 heads fill two tiles and
+// S = Q K^T and O += P V of all five rows cost the tensor-core work of two. The per-(position,
+// head) widening, FMAs and butterfly reductions that make the CUDA-core kernels issue-bound (72
+// warp-instructions per position and head there, about 2 here) are gone and the layer becomes
+// what it should be: a stream of the KV cache.
+//
+// One K/V stream serves all rows of a pass. The cache positions are cut into splits of C
+// consecutive positions, C = 16 * ceil(len / (16 NS)) with len the row's own prefix length: split
+// s of a row is [s C, (s + 1) C) clipped to the prefix, whatever else is in the pass. The rows of
+// one pass have prefix lengths pos + 1 .. pos + n and therefore the same C, except when a multiple
+// of 16 NS lies between them; then the rows on either side are served one after the other (two
+// phases over the same code, rows of the other phase masked out). Within a phase a GROUP of
+// WPG = ceil(n GQ / 16) warps (one per tile) works on a split: the group streams the split's K and V rows, 16
+// positions per stage (1 KB per position; nine bulk copies per stage, see v_row) through a ring that all
+// warps of the group read, warp w applying them to the pairs of tile w. full[] barriers count the
+// bytes of a stage, empty[] barriers the warps that are done with it; the warp whose turn it is
+// refills a stage once it is empty. 198 KB of stages per SM: 6 groups x 2 stages (one tile),
+// 4 x 3 (two), 2 x 6 (three or four). A CTA is (KV head, z); its groups take the splits
+// z GPC + group, + Z GPC, ... one after the other, the ring running across split boundaries.
+//
 //   Q K^T: the k index of the mma is permuted so that thread (g, t) feeds dims (4c + t) * 8 .. + 7
 //   of its position / head from ONE 16-byte load per two k-steps -- a dot product does not care
-//   about the order as long as A and B agree. P (bf16, as a flash-attention kernel keeps it) goes
-//   from the score accumulators straight into A fragments; V^T fragments come from
-//   ldmatrix.x4.trans. Online softmax state (m, l) is per head row; l is kept as per-thread partial
-//   sums and reduced once at the end.
+//   about the order as long as A and B agree; four accumulators (two position blocks x even / odd
+//   k-steps) keep dependent mma instructions apart. P goes from the score accumulators straight
+//   into A fragments. For rows with at most kExactLen cached positions it goes as TWO bf16 numbers
+//   per probability, its bf16 rounding and the bf16 rounding of what that left over: one bf16
+//   alone costs 2^-9 relative per term, which shows in the last bits of the output when few terms
+//   carry the sum; over thousands of positions the errors average out and the second product per
+//   V fragment is not spent. V^T fragments come from ldmatrix.x4.trans. Online softmax state (m, l) is per head row; l is kept as per-thread partial
+//   sums and reduced once at the end of a split.
+//
+// Positions of a stage that lie beyond a row's prefix get probability 0; their V rows are read
+// all the same (times 0), so cache rows up to 15 positions past the longest prefix must hold
+// finite numbers -- they do: the cache starts zeroed and is only written by attn_prep_kernel.
 // The partial of a split is written like the other split kernels' (unnormalised O, m, l) and merged
-// by attn_merge_kernel. Split boundaries depend on the row's prefix length and NS only: row t of an
+// by attn_merge_kernel. Nothing a row computes depends on n or on the other rows: row t of an
 // n-row call is bit-identical to a 1-row call. Waits are bounded (g_attn_error = 3).
-constexpr int kMmaWarps = 6, kMmaPos = 16, kMmaStages = 2, kRowPitch = 528;
-constexpr int kMmaStageBytes = 2 * kMmaPos * kRowPitch;  // K rows, then V rows
+constexpr int kMmaPos = 16, kMmaRingStages = 12, kExactLen = 4096;
+constexpr int kRowBytes = 512;                   // one cached position of one KV head (256 x bf16)
+constexpr int kVPairPitch = 2 * kRowBytes + 16;  // two V rows, then 16 bytes of padding
+constexpr int kMmaStageBytes = kMmaPos * kRowBytes + (kMmaPos / 2) * kVPairPitch;  // K rows, then V row pairs
+
+// Stage layout. K rows are dense (one copy per stage; the 16-byte loads of Q K^T, two tile rows per
+// quarter warp, are two-way bank conflicts either way). V rows go in pairs, each pair 16 bytes
+// further round the banks than the last, so that the eight row addresses of an ldmatrix fall into
+// four bank groups (two-way conflicts) with eight copies per stage; one row per copy would be
+// conflict-free but costs sixteen copies, which the issuing warp pays one after the other.
+__device__ __forceinline__ unsigned char* v_row(unsigned char* stage, int r) {
+  return stage + kMmaPos * kRowBytes + (r >> 1) * kVPairPitch + (r & 1) * kRowBytes;
+}
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -361,190 +395,359 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int GQ>
-__global__ void __launch_bounds__(kMmaWarps * 32, 1)
+__device__ __host__ __forceinline__ int split_len(int len, int NS) {
+  const int per = 16 * NS;
+  return 16 * max(1, (len + per - 1) / per);
+}
+
+// Where a group stands in its list of (phase, split, stage) items; every warp of the group steps
+// an identical copy, so no communication is needed to agree on the next item.
+struct MmaCursor {
+  int ph, s, st, nst;
+};
+
+// groups per CTA for WPG warps per group: 6 x 1, 4 x 2, 2 x 3, 2 x 4 warps (255 registers each)
+__host__ __device__ constexpr int mma_groups(int wpg) { return wpg == 1 ? 6 : wpg == 2 ? 4 : 2; }
+
+template <int WPG>
+__global__ void __launch_bounds__(mma_groups(WPG) * WPG * 32, 1)
 attn_mma_kernel(const bf16* q, const bf16* kc, const bf16* vc, const int* pos_ptr, float* part_o, float* part_ml,
-                int Hq, int max_len, float scale) {
+                int Hq, int GQ, int max_len, int n, int NS, float scale) {
   constexpr int HD = 256;
+  constexpr int GPC = mma_groups(WPG);         // groups per CTA
+  constexpr int SPG = kMmaRingStages / GPC;    // ring stages per group
   dep_release();
   extern __shared__ __align__(128) unsigned char ring[];
-  __shared__ uint64_t full[kMmaWarps][kMmaStages];
-  // the row is the fastest grid index: the CTAs of the rows of a verify pass that read the same
-  // slice of the cache run at the same time, so the slice comes from HBM once and from L2 after
-  const int t = blockIdx.x, g = blockIdx.y, NS = gridDim.z * kMmaWarps;
+  __shared__ uint64_t full[GPC][SPG], empty[GPC][SPG];
+  const int g = blockIdx.x, stride = gridDim.y * GPC;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int s = blockIdx.z * kMmaWarps + warp;
-  unsigned char* wring = ring + (size_t)warp * kMmaStages * kMmaStageBytes;
-  if (lane == 0) {
-    for (int i = 0; i < kMmaStages; ++i)
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&full[warp][i])), "r"(1));
+  const int grp = warp / WPG, wig = warp % WPG;
+  unsigned char* gring = ring + (size_t)grp * SPG * kMmaStageBytes;
+  if (threadIdx.x == 0) {
+    for (int a = 0; a < GPC; ++a)
+      for (int i = 0; i < SPG; ++i) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&full[a][i])), "r"(1));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&empty[a][i])), "r"(WPG));
+      }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncwarp();
+  __syncthreads();
   dep_wait();
-  const int len = min(max(pos_ptr[0] + t + 1, 0), max_len);
-  const int chunk = (len + NS - 1) / NS;
-  const int start = s * chunk, end = min(len, start + chunk);
-  const int nstage = end > start ? (end - start + kMmaPos - 1) / kMmaPos : 0;
+  const int pos0 = pos_ptr[0];
+  auto row_len = [&](int r) { return min(max(pos0 + r + 1, 0), max_len); };
+  // phases: rows whose split length equals that of row 0, then (rarely) the rest
+  const int c_first = split_len(row_len(0), NS), c_last = split_len(row_len(n - 1), NS);
+  const int nphase = c_first == c_last ? 1 : 2;
+  int lmax0 = 0;  // longest prefix among the rows of phase 0
+  for (int r = 0; r < n; ++r)
+    if (split_len(row_len(r), NS) == c_first) lmax0 = row_len(r);
+  auto phase_c = [&](int ph) { return ph == 0 ? c_first : c_last; };
+  auto phase_lmax = [&](int ph) { return ph == 0 ? lmax0 : row_len(n - 1); };
+  auto stages_of = [&](int ph, int s) {
+    const int C = phase_c(ph);
+    return min(max((phase_lmax(ph) - s * C + kMmaPos - 1) / kMmaPos, 0), C / kMmaPos);
+  };
+  const int s_first = blockIdx.y * GPC + grp;
+  // the producer's cursor: next stage to request
+  MmaCursor pc{0, s_first, 0, 0};
+  auto settle = [&](MmaCursor& c) {  // move to the next existing stage at or after (ph, s, st)
+    while (c.ph < nphase) {
+      if (c.s < NS) {
+        c.nst = stages_of(c.ph, c.s);
+        if (c.st < c.nst) return true;
+        c.s += stride;
+        c.st = 0;
+      } else {
+        ++c.ph;
+        c.s = s_first;
+        c.st = 0;
+      }
+    }
+    return false;
+  };
   const bf16* kb = kc + (size_t)g * max_len * HD;
   const bf16* vb = vc + (size_t)g * max_len * HD;
-
-  // whole warp: lane 0 arms the barrier, then lane r issues the two row copies of position r
-  // (32 copies issued by one lane would serialise into microseconds per stage)
-  auto refill = [&](int st) {
-    const int slot = st % kMmaStages;
-    const int p0 = start + st * kMmaPos, cnt = min(kMmaPos, end - p0);
-    unsigned char* dst = wring + (size_t)slot * kMmaStageBytes;
-    const uint32_t bar = smem_addr(&full[warp][slot]);
-    if (lane == 0)
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)cnt * 1024u) : "memory");
-    __syncwarp();
-    if (lane < cnt) {
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                       smem_addr(dst + lane * kRowPitch)), "l"(kb + (size_t)(p0 + lane) * HD), "r"(512u), "r"(bar) : "memory");
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                       smem_addr(dst + (kMmaPos + lane) * kRowPitch)), "l"(vb + (size_t)(p0 + lane) * HD), "r"(512u),
-                   "r"(bar)
-                   : "memory");
-    }
-  };
-  for (int st = 0; st < min(kMmaStages, nstage); ++st) refill(st);
-
-  // A fragments of Q: row = head g * GQ + gi, thread column tq; chunk 4c + tq of the row (8 dims)
-  // serves k-steps 2c (words 0, 1) and 2c + 1 (words 2, 3). Rows >= GQ are zero.
-  const int gi = lane >> 2, tq = lane & 3;
-  uint32_t qa[8][4];
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (gi < GQ) v = reinterpret_cast<const uint4*>(q + ((size_t)t * Hq + g * GQ + gi) * HD)[4 * c + tq];
-    qa[c][0] = v.x; qa[c][1] = v.y; qa[c][2] = v.z; qa[c][3] = v.w;
-  }
-  float oacc[HD / 8][4];
-#pragma unroll
-  for (int i = 0; i < HD / 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
-  float m = -INFINITY, lsum = 0.f;
+  int issued = 0, done = 0;  // stages requested / consumed by this group so far
   bool ok = true;
+  // Requests the stage under the producer cursor if it is this warp's turn; every warp advances
+  // the cursor. The warp whose turn it is first waits until the slot's previous stage was read by
+  // all warps of the group.
+  auto request_next = [&]() {
+    if (!settle(pc)) return;
+    const int slot = issued % SPG, use = issued / SPG;
+    if (issued % WPG == wig) {
+      if (use > 0 && WPG > 1) {
+        if (!bar_wait(&empty[grp][slot], (use - 1) & 1)) {
+          atomicExch(&g_attn_error, 3);
+          ok = false;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+      if (ok) {
+        const int p0 = pc.s * phase_c(pc.ph) + pc.st * kMmaPos, cnt = min(kMmaPos, max_len - p0);
+        unsigned char* dst = gring + (size_t)slot * kMmaStageBytes;
+        const uint32_t bar = smem_addr(&full[grp][slot]);
+        if (cnt < kMmaPos) {  // end of the cache: V rows nobody copies must still be numbers
+          for (int r = cnt; r < kMmaPos; ++r)
+            reinterpret_cast<uint4*>(v_row(dst, r))[lane] = make_uint4(0u, 0u, 0u, 0u);
+          __syncwarp();
+        }
+        if (lane == 0)
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)cnt * 1024u) : "memory");
+        __syncwarp();
+        // nine copies per stage, one lane each (a bulk copy is a warp-uniform instruction: copies
+        // with per-lane operands are issued one after the other, so fewer and larger is faster):
+        // lane 0 the K rows in one piece, lanes 1..8 two V rows each
+        if (lane == 0) {
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                           smem_addr(dst)), "l"(kb + (size_t)p0 * HD), "r"((uint32_t)cnt * 512u), "r"(bar) : "memory");
+        } else if (lane <= kMmaPos / 2 && 2 * (lane - 1) < cnt) {
+          const int r = 2 * (lane - 1);
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                           smem_addr(v_row(dst, r))), "l"(vb + (size_t)(p0 + r) * HD), "r"((uint32_t)min(2, cnt - r) * 512u),
+                       "r"(bar)
+                       : "memory");
+        }
+      }
+    }
+    ++issued;
+    ++pc.st;
+  };
+  for (int i = 0; i < SPG; ++i) request_next();
 
-  for (int st = 0; st < nstage && ok; ++st) {
-    const int slot = st % kMmaStages;
-    if (!bar_wait(&full[warp][slot], (st / kMmaStages) & 1)) {
-      atomicExch(&g_attn_error, 3);
-      ok = false;
-      break;
-    }
-    unsigned char* kst = wring + (size_t)slot * kMmaStageBytes;
-    unsigned char* vst = kst + kMmaPos * kRowPitch;
-    const int cnt = min(kMmaPos, end - start - st * kMmaPos);
-    if (cnt < kMmaPos) {  // stale rows behind a short last stage must not reach the P V product
-      for (int r = cnt; r < kMmaPos; ++r)
-        reinterpret_cast<uint4*>(vst + r * kRowPitch)[lane] = make_uint4(0u, 0u, 0u, 0u);
-      __syncwarp();
-    }
-    // S = Q K^T for the two 8-position blocks of the stage
-    float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  // A fragments of Q. This thread serves pairs e[0] = 16 wig + gi (tile rows 0..7) and e[1] =
+  // e[0] + 8 (tile rows 8..15), pair e = pass row e / GQ, head e % GQ, in thread column tq:
+  // chunk 4c + tq of the query (8 dims) serves k-steps 2c (words 0, 1) and 2c + 1 (words 2, 3).
+  // Tile rows past the last pair are zero.
+  constexpr int NH = 2;  // halves of a tile: rows 0..7 and 8..15
+  const int gi = lane >> 2, tq = lane & 3;
+  const int npair = n * GQ;
+  bool has[NH], ex[NH];
+  int row[NH], head[NH], len[NH], cl[NH];
+  uint32_t qa[NH][8][4];
+#pragma unroll
+  for (int h = 0; h < NH; ++h) {
+    const int e = 16 * wig + gi + 8 * h;
+    has[h] = e < npair;
+    row[h] = has[h] ? e / GQ : 0;
+    head[h] = g * GQ + (has[h] ? e % GQ : 0);
+    len[h] = has[h] ? row_len(row[h]) : 0;
+    cl[h] = split_len(len[h], NS);
+    ex[h] = len[h] <= kExactLen;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
-#pragma unroll
-      for (int nb = 0; nb < 2; ++nb) {
-        const uint4 kw = *reinterpret_cast<const uint4*>(kst + (nb * 8 + gi) * kRowPitch + (4 * c + tq) * 16);
-        mma_bf16(sacc[nb], qa[c][0], 0u, qa[c][1], 0u, kw.x, kw.y);
-        mma_bf16(sacc[nb], qa[c][2], 0u, qa[c][3], 0u, kw.z, kw.w);
-      }
-    }
-    // online softmax of head row gi over positions 8 nb + 2 tq + {0, 1}
-    float sc[2][2], bm = -INFINITY;
-#pragma unroll
-    for (int nb = 0; nb < 2; ++nb) {
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        sc[nb][j] = (nb * 8 + 2 * tq + j < cnt) ? sacc[nb][j] * scale : -INFINITY;
-        bm = fmaxf(bm, sc[nb][j]);
-      }
-    }
-    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
-    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
-    const float mn = fmaxf(m, bm);
-    const float corr = expf(m - mn);  // first stage: exp(-inf) = 0
-    float pr[2][2];
-    lsum *= corr;
-#pragma unroll
-    for (int nb = 0; nb < 2; ++nb) {
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        pr[nb][j] = expf(sc[nb][j] - mn);
-        lsum += pr[nb][j];
-      }
-    }
-    m = mn;
-    const uint32_t pa0 = pack2(pr[0][0], pr[0][1]), pa2 = pack2(pr[1][0], pr[1][1]);
-#pragma unroll
-    for (int i = 0; i < HD / 8; ++i) { oacc[i][0] *= corr; oacc[i][1] *= corr; }
-    // O += P V: V^T fragments for two 8-dim blocks per ldmatrix.x4.trans
-    const uint32_t vaddr = smem_addr(vst + (((lane >> 3) & 1) * 8 + (lane & 7)) * kRowPitch + (lane >> 4) * 16);
-#pragma unroll
-    for (int i = 0; i < HD / 8; i += 2) {
-      uint32_t b0, b1, b2, b3;
-      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(vaddr + i * 16));
-      mma_bf16(oacc[i], pa0, 0u, pa2, 0u, b0, b1);
-      mma_bf16(oacc[i + 1], pa0, 0u, pa2, 0u, b2, b3);
-    }
-    __syncwarp();
-    if (st + kMmaStages < nstage) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      refill(st + kMmaStages);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (has[h]) v = reinterpret_cast<const uint4*>(q + ((size_t)row[h] * Hq + head[h]) * HD)[4 * c + tq];
+      qa[h][c][0] = v.x; qa[h][c][1] = v.y; qa[h][c][2] = v.z; qa[h][c][3] = v.w;
     }
   }
-  lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
-  lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
-  if (gi < GQ) {
-    const bool none = m == -INFINITY;
-    const size_t slot_o = ((size_t)t * Hq + g * GQ + gi) * NS + s;
-    float2* po = reinterpret_cast<float2*>(part_o + slot_o * HD) + tq;
+  // the remainder product is spent when a pair of this warp has a short prefix (warp-uniform)
+  bool exact_lane = false;
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) po[i * 4] = none ? make_float2(0.f, 0.f) : make_float2(oacc[i][0], oacc[i][1]);
-    if (tq == 0) {
-      part_ml[slot_o * 2] = m;
-      part_ml[slot_o * 2 + 1] = none ? 0.f : lsum;
+  for (int h = 0; h < NH; ++h) exact_lane = exact_lane || (has[h] && ex[h]);
+  const bool exact = __any_sync(0xffffffffu, exact_lane);
+  constexpr int LAST = NH - 1;
+
+  for (int ph = 0; ph < nphase && ok; ++ph) {
+    const int C = phase_c(ph);
+    for (int s = s_first; s < NS && ok; s += stride) {
+      const int nst = stages_of(ph, s);
+      bool act[NH];
+      int lim[NH];  // positions below it are in the pair's prefix
+      float m[NH], l[NH];
+#pragma unroll
+      for (int h = 0; h < NH; ++h) {
+        act[h] = has[h] && cl[h] == C;
+        lim[h] = act[h] ? min(len[h], (s + 1) * C) : 0;
+        m[h] = -INFINITY;
+        l[h] = 0.f;
+      }
+      float oacc[HD / 8][2 * NH];
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 2 * NH; ++j) oacc[i][j] = 0.f;
+      for (int st = 0; st < nst; ++st) {
+        const int slot = done % SPG;
+        if (!bar_wait(&full[grp][slot], (done / SPG) & 1)) {
+          atomicExch(&g_attn_error, 3);
+          ok = false;
+          break;
+        }
+        unsigned char* kst = gring + (size_t)slot * kMmaStageBytes;
+        const int p0 = s * C + st * kMmaPos;
+        // S = Q K^T for the two 8-position blocks of the stage; even and odd k-steps accumulate
+        // apart and are added at the end
+        float sacc[2][2][2 * NH];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+          for (int j = 0; j < 2 * NH; ++j) sacc[nb][0][j] = sacc[nb][1][j] = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 k0 = *reinterpret_cast<const uint4*>(kst + gi * kRowBytes + (4 * c + tq) * 16);
+          const uint4 k1 = *reinterpret_cast<const uint4*>(kst + (8 + gi) * kRowBytes + (4 * c + tq) * 16);
+          mma_bf16(sacc[0][0], qa[0][c][0], qa[LAST][c][0], qa[0][c][1], qa[LAST][c][1], k0.x, k0.y);
+          mma_bf16(sacc[1][0], qa[0][c][0], qa[LAST][c][0], qa[0][c][1], qa[LAST][c][1], k1.x, k1.y);
+          mma_bf16(sacc[0][1], qa[0][c][2], qa[LAST][c][2], qa[0][c][3], qa[LAST][c][3], k0.z, k0.w);
+          mma_bf16(sacc[1][1], qa[0][c][2], qa[LAST][c][2], qa[0][c][3], qa[LAST][c][3], k1.z, k1.w);
+        }
+        // online softmax of a pair over positions p0 + 8 nb + 2 tq + {0, 1}
+        uint32_t pa[2][NH], pl[2][NH];  // P = pa + pl: bf16 head, bf16 remainder; [position block][half]
+        float corr[NH];
+        bool rescale = false;
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+          float sc[2][2], bm = -INFINITY;
+#pragma unroll
+          for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const float sv = sacc[nb][0][2 * h + j] + sacc[nb][1][2 * h + j];
+              sc[nb][j] = (p0 + nb * 8 + 2 * tq + j < lim[h]) ? sv * scale : -INFINITY;
+              bm = fmaxf(bm, sc[nb][j]);
+            }
+          }
+          bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+          bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+          const float mn = fmaxf(m[h], bm);
+          // a stage without a position of this pair leaves its state alone (mn = -inf only then)
+          const bool any = mn != -INFINITY;
+          corr[h] = any ? expf(m[h] - mn) : 1.f;  // first stage: exp(-inf) = 0
+          rescale = rescale || corr[h] != 1.f;
+          float pr[2][2];
+          l[h] *= corr[h];
+#pragma unroll
+          for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              pr[nb][j] = any ? expf(sc[nb][j] - mn) : 0.f;
+              l[h] += pr[nb][j];
+            }
+          }
+          m[h] = mn;
+#pragma unroll
+          for (int nb = 0; nb < 2; ++nb) {
+            const uint32_t hi = pack2(pr[nb][0], pr[nb][1]);
+            pa[nb][h] = hi;
+            pl[nb][h] = (exact && ex[h]) ? pack2(pr[nb][0] - __uint_as_float(hi << 16),
+                                                 pr[nb][1] - __uint_as_float(hi & 0xffff0000u))
+                                         : 0u;
+          }
+        }
+        // rescale only when some pair of the warp saw a new maximum (times 1 changes nothing)
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+          for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 2 * NH; ++j) oacc[i][j] *= corr[j >> 1];
+        }
+        // O += P V: V^T fragments for two 8-dim blocks per ldmatrix.x4.trans
+        const uint32_t vaddr = smem_addr(v_row(kst, ((lane >> 3) & 1) * 8 + (lane & 7)) + (lane >> 4) * 16);
+        if (exact) {
+          // the remainder product of a block follows the head product of the next block, so that
+          // no mma waits for the one issued just before it
+          uint32_t p0r = 0u, p1r = 0u, p2r = 0u, p3r = 0u;
+#pragma unroll
+          for (int i = 0; i < HD / 8; i += 2) {
+            uint32_t b0, b1, b2, b3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(vaddr + i * 16));
+            mma_bf16(oacc[i], pa[0][0], pa[0][LAST], pa[1][0], pa[1][LAST], b0, b1);
+            mma_bf16(oacc[i + 1], pa[0][0], pa[0][LAST], pa[1][0], pa[1][LAST], b2, b3);
+            if (i > 0) {
+              mma_bf16(oacc[i - 2], pl[0][0], pl[0][LAST], pl[1][0], pl[1][LAST], p0r, p1r);
+              mma_bf16(oacc[i - 1], pl[0][0], pl[0][LAST], pl[1][0], pl[1][LAST], p2r, p3r);
+            }
+            p0r = b0; p1r = b1; p2r = b2; p3r = b3;
+          }
+          mma_bf16(oacc[HD / 8 - 2], pl[0][0], pl[0][LAST], pl[1][0], pl[1][LAST], p0r, p1r);
+          mma_bf16(oacc[HD / 8 - 1], pl[0][0], pl[0][LAST], pl[1][0], pl[1][LAST], p2r, p3r);
+        } else {
+#pragma unroll
+          for (int i = 0; i < HD / 8; i += 2) {
+            uint32_t b0, b1, b2, b3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(vaddr + i * 16));
+            mma_bf16(oacc[i], pa[0][0], pa[0][LAST], pa[1][0], pa[1][LAST], b0, b1);
+            mma_bf16(oacc[i + 1], pa[0][0], pa[0][LAST], pa[1][0], pa[1][LAST], b2, b3);
+          }
+        }
+        __syncwarp();
+        if (WPG > 1 && lane == 0)
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(&empty[grp][slot])) : "memory");
+        ++done;
+        if (WPG == 1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        request_next();
+        if (!ok) break;
+      }
+      if (!ok) break;
+      // the split's partials of this thread's pairs (pairs of the other phase are written there;
+      // a split without a position of the pair's prefix is not written: the merge skips it)
+#pragma unroll
+      for (int h = 0; h < NH; ++h) {
+        float lh = l[h];
+        lh += __shfl_xor_sync(0xffffffffu, lh, 1);
+        lh += __shfl_xor_sync(0xffffffffu, lh, 2);
+        if (!act[h] || s * C >= len[h]) continue;
+        const bool none = m[h] == -INFINITY;
+        const size_t slot_o = ((size_t)row[h] * Hq + head[h]) * NS + s;
+        float2* po = reinterpret_cast<float2*>(part_o + slot_o * HD) + tq;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i)
+          po[i * 4] = none ? make_float2(0.f, 0.f) : make_float2(oacc[i][2 * h], oacc[i][2 * h + 1]);
+        if (tq == 0) {
+          part_ml[slot_o * 2] = m[h];
+          part_ml[slot_o * 2 + 1] = none ? 0.f : lh;
+        }
+      }
     }
   }
 }
 
-// Merge of the NS split partials of one (head, row). Phase 1: the (m, l) pairs of all splits go to
+// Merge of the split partials of one (head, row). Phase 1: the (m, l) pairs of the splits go to
 // shared memory in one coalesced sweep, M = max m, weight f_s = exp(m_s - M), L = sum l_s f_s
-// (block reduction in a fixed order). Phase 2: warp w adds O_s f_s over splits w, w + 8, ... in
-// ascending order with independent 16-byte loads in flight (lane = HD / 32 consecutive dims), the 8
-// warps are combined in warp order, then o = bf16(O / L) * bf16(sigmoid(gate)). With hundreds of
-// splits (long caches) a loop whose loads wait for each other would cost as much as the split
-// kernel itself. The order depends on NS only.
-constexpr int kMergeMaxSplits = 1024;
+// (block reduction in a fixed order). Phase 2: warp w adds O_s f_s over splits w, w + 16, ... in
+// ascending order, eight 16-byte loads per lane in flight (lane = HD / 32 consecutive dims), the
+// 16 warps are combined in warp order, then o = bf16(O / L) * bf16(sigmoid(gate)). With hundreds
+// of splits (long caches) a loop whose loads wait for each other costs as much as the split
+// kernel itself: 8 warps with four loads in flight took 13 us for 222 splits. The order depends
+// on the number of splits merged only. With `aligned` (partials of attn_mma_kernel) that number
+// is the count of splits that hold a position of the row's prefix, ceil(len / split length);
+// the others were not written and are not read.
+constexpr int kMergeMaxSplits = 1024, kMergeWarps = 16;
 template <int HD>
-__global__ void __launch_bounds__(kSplitWarps * 32)
+__global__ void __launch_bounds__(kMergeWarps * 32)
 attn_merge_kernel(const float* part_o, const float* part_ml, const bf16* qg, long ldp, bf16* out, long ldo,
-                  int Hq, int NS) {
+                  int Hq, int NS, const int* pos_ptr, int max_len, int aligned) {
   constexpr int E = HD / 32;
   dep_release();
   dep_wait();
   __shared__ float fs[kMergeMaxSplits];
   __shared__ float red[32];
-  __shared__ float so[kSplitWarps][HD];
+  __shared__ float so[kMergeWarps][HD];
   const int h = blockIdx.x, t = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int ns = NS;
+  if (aligned) {
+    const int len = min(max(pos_ptr[0] + t + 1, 0), max_len);
+    const int C = split_len(len, NS);
+    ns = min(NS, (len + C - 1) / C);
+  }
   const size_t base = ((size_t)t * Hq + h) * NS;
   const float2* ml = reinterpret_cast<const float2*>(part_ml) + base;
   // phase 1
   float mymax = -INFINITY;
-  for (int s = threadIdx.x; s < NS; s += blockDim.x) mymax = fmaxf(mymax, ml[s].x);
+  for (int s = threadIdx.x; s < ns; s += blockDim.x) mymax = fmaxf(mymax, ml[s].x);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mymax = fmaxf(mymax, __shfl_xor_sync(0xffffffffu, mymax, o));
   if (lane == 0) red[warp] = mymax;
   __syncthreads();
   float M = red[0];
 #pragma unroll
-  for (int w = 1; w < kSplitWarps; ++w) M = fmaxf(M, red[w]);
+  for (int w = 1; w < kMergeWarps; ++w) M = fmaxf(M, red[w]);
   float lpart = 0.f;
-  for (int s = threadIdx.x; s < NS; s += blockDim.x) {
+  for (int s = threadIdx.x; s < ns; s += blockDim.x) {
     const float2 v = ml[s];
     const float f = v.x == -INFINITY ? 0.f : expf(v.x - M);
     fs[s] = f;
@@ -555,20 +758,33 @@ attn_merge_kernel(const float* part_o, const float* part_ml, const bf16* qg, lon
   float o[E];
 #pragma unroll
   for (int e = 0; e < E; ++e) o[e] = 0.f;
-#pragma unroll 4
-  for (int s = warp; s < NS; s += kSplitWarps) {
-    const float f = fs[s];
-    const float* po = part_o + (base + s) * HD + lane * E;
-    float v[E];
-    if constexpr (E == 8) {
-      const float4 a = reinterpret_cast<const float4*>(po)[0], b = reinterpret_cast<const float4*>(po)[1];
-      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    } else {
+  constexpr int kFlight = 8;
+  for (int s0 = warp; s0 < ns; s0 += kMergeWarps * kFlight) {
+    float v[kFlight][E];
 #pragma unroll
-      for (int e = 0; e < E; ++e) v[e] = po[e];
+    for (int j = 0; j < kFlight; ++j) {
+      const int sj = s0 + j * kMergeWarps;
+      if (sj < ns) {
+        const float* po = part_o + (base + sj) * HD + lane * E;
+        if constexpr (E == 8) {
+          const float4 a = reinterpret_cast<const float4*>(po)[0], b = reinterpret_cast<const float4*>(po)[1];
+          v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
+          v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < E; ++e) v[j][e] = po[e];
+        }
+      }
     }
 #pragma unroll
-    for (int e = 0; e < E; ++e) o[e] = fmaf(v[e], f, o[e]);
+    for (int j = 0; j < kFlight; ++j) {
+      const int sj = s0 + j * kMergeWarps;
+      if (sj < ns) {
+        const float f = fs[sj];
+#pragma unroll
+        for (int e = 0; e < E; ++e) o[e] = fmaf(v[j][e], f, o[e]);
+      }
+    }
   }
 #pragma unroll
   for (int e = 0; e < E; ++e) so[warp][lane * E + e] = o[e];
@@ -576,7 +792,7 @@ attn_merge_kernel(const float* part_o, const float* part_ml, const bf16* qg, lon
   for (int c = threadIdx.x; c < HD; c += blockDim.x) {
     float O = 0.f;
 #pragma unroll
-    for (int w = 0; w < kSplitWarps; ++w) O += so[w][c];
+    for (int w = 0; w < kMergeWarps; ++w) O += so[w][c];
     const float ob = rnd(O / L);
     const float gate = tofloat(qg[(long)t * ldp + (size_t)h * 2 * HD + HD + c]);
     out[(long)t * ldo + (size_t)h * HD + c] = tobf16(ob * rnd(sigmoid_acc(gate)));
@@ -647,38 +863,41 @@ extern "C" int qe_attn_decode(const void* q, const void* kc, const void* vc, con
                       (const bf16*)q, (const bf16*)kc, (const bf16*)vc, pos, part_o, part_ml,     \
                       Hq, Hkv, max_len, scale);                                                   \
     if (e) return e;                                                                              \
-    return (int)launch(attn_merge_kernel<HD>, dim3(Hq, n), dim3(kSplitWarps * 32), 0, s, pdl_on(),              \
+    return (int)launch(attn_merge_kernel<HD>, dim3(Hq, n), dim3(kMergeWarps * 32), 0, s, pdl_on(), \
                        (const float*)part_o, (const float*)part_ml, (const bf16*)qg, ldp,         \
-                       (bf16*)out, ldo, Hq, NS);                                                  \
+                       (bf16*)out, ldo, Hq, NS, pos, max_len, 0);                                 \
   }
-  if (hd == 256 && NS % kMmaWarps == 0 && gq >= 1 && gq <= 8) {
-    const dim3 mgrid(n, Hkv, NS / kMmaWarps);
-    constexpr size_t msmem = (size_t)kMmaWarps * kMmaStages * kMmaStageBytes;
-    int e = QE_ERR_ARG;
-#define QB_MMA(GQ)                                                                                \
+  if (hd == 256 && NS % 6 == 0 && gq >= 1 && gq <= 8) {
+    // one CTA per (KV head, z); z covers the splits of a group stride with about one CTA per SM
+    constexpr size_t msmem = (size_t)kMmaRingStages * kMmaStageBytes;
+    const int wpg = (n * gq + 15) / 16, gpc = mma_groups(wpg);  // one warp per tile of 16 (row, head) pairs
+    const int per_head = std::max(1, (qe_sm_count() + Hkv - 1) / Hkv);
+    const dim3 mgrid(Hkv, std::min((NS + gpc - 1) / gpc, per_head));
+    int e;
+#define QB_MMA(WPG)                                                                               \
   {                                                                                               \
-    static bool attr = false;                                                                     \
-    if (!attr) {                                                                                  \
-      cudaFuncSetAttribute(attn_mma_kernel<GQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem); \
-      attr = true;                                                                                \
+    static bool attr[64] = {};                                                                    \
+    int dv = 0;                                                                                   \
+    if (cudaGetDevice(&dv) != cudaSuccess || dv < 0 || dv >= 64) return QE_ERR_ARG;               \
+    if (!attr[dv]) {                                                                              \
+      cudaFuncSetAttribute(attn_mma_kernel<WPG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem); \
+      attr[dv] = true;                                                                            \
     }                                                                                             \
-    e = (int)launch(attn_mma_kernel<GQ>, mgrid, dim3(kMmaWarps * 32), msmem, s, pdl_on(), (const bf16*)q, \
-                    (const bf16*)kc, (const bf16*)vc, pos, part_o, part_ml, Hq, max_len, scale);   \
+    e = (int)launch(attn_mma_kernel<WPG>, mgrid, dim3(mma_groups(WPG) * WPG * 32), msmem, s, pdl_on(), \
+                    (const bf16*)q, (const bf16*)kc, (const bf16*)vc, pos, part_o, part_ml, Hq, gq, \
+                    max_len, n, NS, scale);                                                       \
   }
-    switch (gq) {
+    switch (wpg) {
       case 1: QB_MMA(1) break;
       case 2: QB_MMA(2) break;
       case 3: QB_MMA(3) break;
-      case 4: QB_MMA(4) break;
-      case 6: QB_MMA(6) break;
-      case 8: QB_MMA(8) break;
-      default: e = -1; break;
+      default: QB_MMA(4) break;
     }
 #undef QB_MMA
-    if (e == 0)
-      return (int)launch(attn_merge_kernel<256>, dim3(Hq, n), dim3(kSplitWarps * 32), 0, s, pdl_on(),
-                         (const float*)part_o, (const float*)part_ml, (const bf16*)qg, ldp, (bf16*)out, ldo, Hq, NS);
-    if (e > 0) return e;
+    if (e) return e;
+    return (int)launch(attn_merge_kernel<256>, dim3(Hq, n), dim3(kMergeWarps * 32), 0, s, pdl_on(),
+                       (const float*)part_o, (const float*)part_ml, (const bf16*)qg, ldp, (bf16*)out, ldo, Hq, NS,
+                       pos, max_len, 1);
   }
   if (hd == 256) QB_DEC(256)
   if (hd == 128) QB_DEC(128)

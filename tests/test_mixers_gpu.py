@@ -210,20 +210,21 @@ def test_attention_vs_oracle_and_row_independence(C, hq, hkv, hd, rd, steps, sta
     assert C.attn_error() == 0
 
 
-def test_attention_at_the_long_context_operating_point(C):
-    """The split kernel as the engine runs it on a 32K-position cache of the 27B shape: 24 query /
-    4 KV heads of dim 256, 5 rows (verify), 222 splits (6 per CTA, one CTA per SM and row), against
-    the oracle's attention over the same cache; rows bit-identical to 1-row passes."""
-    g = torch.Generator().manual_seed(5)
-    hq, hkv, hd, NS, n, start = 24, 4, 256, 222, 5, 32003
+def _decode_against_oracle(C, hq, hkv, NS, n, start, max_len, seed, stale=1.0):
+    """attn_decode on a random cache of head dim 256 against the oracle's attention, plus the
+    1-row passes of every row. Cache rows past the prefixes hold `stale`-scaled random numbers
+    (rejected drafts leave such rows behind). Returns worst error / bound."""
+    g = torch.Generator().manual_seed(seed)
+    hd = 256
     cfg = attn_cfg(hq, hkv, hd, 64)
-    max_len = start + n + 3
     kc = torch.randn(hkv, max_len, hd, generator=g).to(BF)
     vc = torch.randn(hkv, max_len, hd, generator=g).to(BF)
+    kc[:, start + n:] *= stale
+    vc[:, start + n:] *= stale
     q = torch.randn(n, hq, hd, generator=g).to(BF)
     gate = (torch.randn(n, hq, hd, generator=g) * 2).to(BF)
     qg = torch.cat([q, gate], dim=-1).reshape(n, hq * 2 * hd)  # per head [q | gate]
-    refs = [OM.attention_core(q[t], gate[t].reshape(-1), kc, vc, start + t + 1, cfg) for t in range(n)]
+    refs = [OM.attention_core(q[t], gate[t].reshape(-1), kc, vc, min(start + t + 1, max_len), cfg) for t in range(n)]
     kcd, vcd, qd, qgd = kc.to(dev), vc.to(dev), q.reshape(n, hq * hd).to(dev).contiguous(), qg.to(dev)
     pos_t = torch.tensor([start], dtype=torch.int32, device=dev)
     po = torch.empty(8, hq, NS, hd, device=dev)
@@ -237,10 +238,40 @@ def test_attention_at_the_long_context_operating_point(C):
         worst = max(worst, float((diff / (2.0 ** -6 * ref.abs() + 2e-3)).max()))
         o1 = torch.empty(1, hq * hd, dtype=BF, device=dev)
         C.attn_decode(qd[t:t + 1], kcd, vcd, pos_t + t, qgd[t:t + 1], po, pml, o1)
-        assert torch.equal(o1[0], out[t]), "row differs from the 1-row pass"
+        assert torch.equal(o1[0], out[t]), f"row {t} differs from the 1-row pass"
+    # and a second n-row pass gives the same bits (no state left behind in the scratch)
+    out2 = torch.empty_like(out)
+    C.attn_decode(qd, kcd, vcd, pos_t, qgd, po, pml, out2)
+    assert torch.equal(out, out2)
+    assert C.attn_error() == 0
+    return worst
+
+
+def test_attention_at_the_long_context_operating_point(C):
+    """The split kernel as the engine runs it on a 32K-position cache of the 27B shape: 24 query /
+    4 KV heads of dim 256, 5 rows (verify), 222 splits, against the oracle's attention over the
+    same cache; rows bit-identical to 1-row passes."""
+    worst = _decode_against_oracle(C, 24, 4, 222, 5, 32003, 32003 + 5 + 3, seed=5)
     print(f"\n32K positions, 222 splits: worst error / bound = {worst:.3f}")
     assert worst <= 1.0
-    assert C.attn_error() == 0
+
+
+@pytest.mark.parametrize("hq,hkv,NS,n,start,slack", [
+    # the rows of a pass share one K/V stream cut into splits of 16 * ceil(len / (16 NS)) positions;
+    # these passes have rows on both sides of a multiple of 16 NS, where that length changes:
+    (24, 4, 6, 5, 93, 40),      # lengths 94..98 around 96
+    (8, 2, 6, 2, 95, 1),        # the two rows of one tile on different sides (96 | 97)
+    (12, 2, 12, 8, 190, 0),     # 191..198 around 192, the pass ends with the cache
+    (4, 1, 6, 3, 286, 7),       # 287..289 around 288 = 3 * 96
+    (24, 4, 222, 5, 3550, 16),  # the engine's 222 splits around 3552
+    # every row count (1..8 rows = 1..4 warps per stream) well inside one split length
+    (24, 4, 12, 1, 700, 9), (24, 4, 12, 2, 700, 9), (24, 4, 12, 3, 700, 9), (24, 4, 12, 4, 700, 9),
+    (24, 4, 12, 5, 700, 9), (24, 4, 12, 6, 700, 9), (24, 4, 12, 7, 700, 9), (24, 4, 12, 8, 700, 9),
+    # rows that run past the end of the cache see the whole cache
+    (8, 2, 6, 4, 61, -2)])
+def test_attention_rows_share_one_stream(C, hq, hkv, NS, n, start, slack):
+    worst = _decode_against_oracle(C, hq, hkv, NS, n, start, start + n + slack, seed=start + n, stale=50.0)
+    assert worst <= 1.0, worst
 
 
 def test_attention_never_writes_past_the_cache(C):
