@@ -12,7 +12,7 @@ that the reference's own `tests/conftest.py` finds the package next to it:
                           the same-box GPU comparator: `bench.py --impl reference-gpu` runs the
                           reference engine on it.
   baseline/_ref/shim/     the reference's Python package with `_C` and `_w4` replaced by the
-                          three files of baseline/shim/, which re-export qengine_b200. Its copy of
+                          two files of baseline/shim/, which re-export qengine_b200. Its copy of
                           tests/test_gemv_w4.py and tests/test_kernels.py therefore exercises this
                           repository's library, unmodified (tests/test_reference_suites_gpu.py).
 

@@ -576,6 +576,22 @@ def run_ours(a):
                 "ms_per_cycle": d * 1e3 / max(1, st["cycles"]), "identical_to_plain": out == gen}
         del eng_d
         torch.cuda.empty_cache()
+    # ---- the draft layer's fc + in_proj + o_proj pinned in L2 for the draft phase (A/B) ---------
+    if not a.no_mtp and world == 1:
+        eng_p = Engine(cfg, W, max_len=P + n_new + 32, device=dev)
+        eng_p.pin_mtp_l2(True)
+        window_bytes = eng_p.l2_win[1]
+        for label, fa in (("a0", 0), ("a4", 4)):
+            eng_p.generate_spec(prompt, n_new, 4, force_accept=fa, truth=truth)
+            barrier()
+            out, _, d, st = eng_p.generate_spec(prompt, n_new, 4, timing=True, force_accept=fa, truth=truth)
+            mtp[f"l2_window_{label}"] = {
+                "tok_s": (n_new - 1) / d, "ms_per_cycle": d * 1e3 / max(1, st["cycles"]),
+                "identical_to_plain": out == gen, "window_bytes": window_bytes,
+                "without_window_ms_per_cycle": mtp[label]["ms_per_cycle"]}
+        eng_p.pin_mtp_l2(False)
+        del eng_p
+        torch.cuda.empty_cache()
     exchange_us = exchange_timing(eng) if world > 1 else None
     parity = parity_early
 
