@@ -69,7 +69,8 @@ struct GemvArgs {
   int K, G, total;
   int nctas;       // CTAs that own work (<= gridDim.x)
   int nwarps;      // warps of a CTA that own work (small matrices keep min_units per warp)
-  int quantum;     // ranges start at multiples of this many units (4 when G % 4 == 0, else 1)
+  int quantum;     // warp ranges start at multiples of this many units (4 when G % 4 == 0, else 1)
+  int cta_quantum; // CTA ranges start at multiples of this many units: `quantum`, or G (whole tiles)
   int xvec;        // x rows are 16-byte aligned with ldx % 8 == 0
   // fused residual + RMSNorm prologue (h_in != nullptr)
   const bf16* h_in;
@@ -93,12 +94,12 @@ constexpr int kWaitLimit = 1 << 20;
 __device__ __host__ __forceinline__ int cta_begin(int total, int q, int nctas, int c) {
   return q * share_begin(total / q, nctas, c);
 }
-__device__ __forceinline__ void warp_range(int total, int q, int nctas, int nwarps, int cta, int warp, int& u0,
-                                           int& u1) {
+__device__ __forceinline__ void warp_range(int total, int q, int qc, int nctas, int nwarps, int cta, int warp,
+                                           int& u0, int& u1) {
   if (cta >= nctas) { u0 = u1 = total; return; }
-  const int b = share_begin(total / q, nctas, cta), e = share_begin(total / q, nctas, cta + 1);
-  u0 = q * (b + share_begin(e - b, nwarps, min(warp, nwarps)));
-  u1 = q * (b + share_begin(e - b, nwarps, min(warp + 1, nwarps)));
+  const int b = cta_begin(total, qc, nctas, cta), e = cta_begin(total, qc, nctas, cta + 1);
+  u0 = b + q * share_begin((e - b) / q, nwarps, min(warp, nwarps));
+  u1 = b + q * share_begin((e - b) / q, nwarps, min(warp + 1, nwarps));
 }
 
 // x fragment of a lane for the ragged cases (misaligned rows, or the last group when K is not a
@@ -335,7 +336,7 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
     }
   };
   auto range_of = [&](const GemvArgs& a, int& u0, int& u1) {
-    warp_range(a.total, a.quantum, a.nctas, a.nwarps, blockIdx.x, warp, u0, u1);
+    warp_range(a.total, a.quantum, a.cta_quantum, a.nctas, a.nwarps, blockIdx.x, warp, u0, u1);
   };
 
   // weights never depend on the producer of x: the first stages are requested before the
@@ -525,7 +526,7 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
       done = __shfl_sync(0xffffffffu, done, 0);  // also orders lane 0's acquire before the loads below
       if (!done) return;
       float sum[4] = {0.f, 0.f, 0.f, 0.f};
-      const int q = a.quantum;
+      const int q = a.cta_quantum;
       const int c_lo = share_owner(total / q, a.nctas, (T * G) / q);
       const int c_hi = share_owner(total / q, a.nctas, (T * G + G - 1) / q);
 #pragma unroll 1
@@ -657,7 +658,7 @@ const std::vector<ShapeCfg>& env_overrides() {
 struct Resolved {
   qe_w4_plan plan;
   const Geometry* geom;
-  int nctas, nwarps, quantum;
+  int nctas, nwarps, quantum, cta_quantum;
 };
 
 // Shape-only launch policy (never N): as many warps as there are units / min_units, at most one
@@ -685,6 +686,13 @@ Resolved resolve(const qe_w4_params& p, const qe_w4_cfg& c_in) {
   const long per_cta = (units + ctas - 1) / ctas;
   r.nwarps = (int)std::max<long>(1, std::min<long>(r.geom->nw, (per_cta + min_units - 1) / min_units));
   r.quantum = (int)quantum;
+  // CTA ranges of whole tiles where that costs less than the exchange of cut tiles between CTAs
+  // (two global round trips at the end of the launch, about a microsecond): the surplus of the
+  // fullest CTA over the even share, at about 30 ns per unit, must stay well below that. Decided
+  // from the shape alone, like everything else in the plan.
+  const long tiles_max = (tiles + ctas - 1) / ctas;
+  const bool whole_tiles = ctas > 1 && tiles >= ctas && (tiles_max * ctas - tiles) * G <= 26 * ctas;
+  r.cta_quantum = whole_tiles ? (int)G : (int)quantum;
   r.nctas = (int)ctas;
   r.plan.mode = 4;
   r.plan.grid_x = (int)ctas;
@@ -733,6 +741,7 @@ int make_job(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg,
   a.nctas = r.nctas;
   a.nwarps = r.nwarps;
   a.quantum = r.quantum;
+  a.cta_quantum = r.cta_quantum;
   a.xvec = ((p->ldx & 7) == 0 && aligned16(p->x)) ? 1 : 0;
   *smem_extra = 0;
   if (nrm && nrm->h_in) {
