@@ -212,7 +212,8 @@ typedef struct qe_w4_params {
                           with ldx % 8 == 0 take the vector path). Ignored by qe_w4_gemv_ex when a
                           prologue is given. */
   void* out;           /* bf16 output, N rows, stride ldo */
-  float* ws;           /* fp32 partial-sum slots, qe_w4_plan::ws_floats entries, any contents */
+  float* ws;           /* fp32 partial-sum slots, qe_w4_plan::ws_floats entries; zero before the
+                          first call, left zero by every call (like `counters`) */
   int* counters;       /* int32 arrival counters, qe_w4_plan::counters entries, zero between calls */
   int M;               /* logical output rows (QE_EPI_SWIGLU: intermediate size I) */
   int K;               /* logical reduction length, Kp - 128 < K <= Kp */

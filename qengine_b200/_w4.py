@@ -51,7 +51,7 @@ def _workspace(dev: torch.device, ws_floats: int, counters: int) -> _Workspace:
              "W4 workspace would have to grow during graph capture: run the shape once eagerly first")
         if W.ws is not None:
             W.keep.append(W.ws)
-        W.ws = torch.empty(max(ws_floats, _MIN_WS_FLOATS), dtype=torch.float32, device=dev)
+        W.ws = torch.zeros(max(ws_floats, _MIN_WS_FLOATS), dtype=torch.float32, device=dev)
     if W.counters is None or W.counters.numel() < counters:
         _req(not torch.cuda.is_current_stream_capturing(),
              "W4 counters would have to grow during graph capture: run the shape once eagerly first")
@@ -62,11 +62,14 @@ def _workspace(dev: torch.device, ws_floats: int, counters: int) -> _Workspace:
 
 
 def reset_workspaces():
-    """Zero the arrival counters of every device's workspace. Only needed after a launch that
-    reported a ring error (`ring_error() != 0`): such a launch may leave counters non-zero."""
+    """Zero the arrival counters and partial-sum slots of every device's workspace. Only needed
+    after a launch that reported a ring error (`ring_error() != 0`): such a launch may leave them
+    non-zero."""
     for W in _per_device.values():
         if W.counters is not None:
             W.counters.zero_()
+        if W.ws is not None:
+            W.ws.zero_()
 
 
 def _packed(qw, scales):

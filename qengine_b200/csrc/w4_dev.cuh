@@ -133,7 +133,9 @@ __device__ __forceinline__ float silu_fast(float v) { return v / (1.0f + __expf(
 // rows 8..15 the matching up rows (quantize_w4_gate_up, python/qengine/quant.py:114-125), so one
 // lane holds both halves of its outputs: bf16(silu(gate) * up), fp32 math, one rounding
 // (reference epilogue csrc/gemv_w4.cu:188-193).
-__device__ __forceinline__ void tile_out(const OutDesc& d, int tile, const float (&f)[4], int lane) {
+// `mask` bit k set = write f[k] (plain epilogues only; SwiGLU needs all four values of a lane).
+__device__ __forceinline__ void tile_out(const OutDesc& d, int tile, const float (&f)[4], int lane,
+                                         unsigned mask = 0xFu) {
   const int r = lane >> 2, n0 = 2 * (lane & 3);
   if (d.epi == QE_EPI_SWIGLU) {
     const int j = tile * 8 + r;
@@ -148,14 +150,15 @@ __device__ __forceinline__ void tile_out(const OutDesc& d, int tile, const float
   for (int c = 0; c < 2; ++c) {
     const int n = n0 + c;
     if (n >= d.N) continue;
+    const bool w0 = m0 < d.M && (mask >> c & 1u), w1 = m1 < d.M && (mask >> (2 + c) & 1u);
     if (d.out_f32) {
       float* o = static_cast<float*>(d.out) + (long)n * d.ldo;
-      if (m0 < d.M) o[m0] = f[c];
-      if (m1 < d.M) o[m1] = f[2 + c];
+      if (w0) o[m0] = f[c];
+      if (w1) o[m1] = f[2 + c];
     } else {
       bf16* o = static_cast<bf16*>(d.out) + (long)n * d.ldo;
-      if (m0 < d.M) o[m0] = tobf16(f[c]);
-      if (m1 < d.M) o[m1] = tobf16(f[2 + c]);
+      if (w0) o[m0] = tobf16(f[c]);
+      if (w1) o[m1] = tobf16(f[2 + c]);
     }
   }
 }

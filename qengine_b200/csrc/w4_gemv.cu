@@ -71,6 +71,7 @@ struct GemvArgs {
   int nwarps;      // warps of a CTA that own work (small matrices keep min_units per warp)
   int quantum;     // warp ranges start at multiples of this many units (4 when G % 4 == 0, else 1)
   int cta_quantum; // CTA ranges start at multiples of this many units: `quantum`, or G (whole tiles)
+  int two_way;     // every CTA range holds at least one tile's worth of units: a cut tile has two owners
   int xvec;        // x rows are 16-byte aligned with ldx % 8 == 0
   // fused residual + RMSNorm prologue (h_in != nullptr)
   const bf16* h_in;
@@ -513,6 +514,32 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
     const int cta_b = s_rb[0], cta_e = s_rb[NW];
     const int my_cta = blockIdx.x;
     auto publish = [&](int T, const float (&f)[4], int units, int pslot) {
+      if (a.two_way && a.o.epi != QE_EPI_SWIGLU) {
+        // Two owners, one round trip: both swap their partial into the same slot (the lower
+        // CTA's slot 1). Per element, whoever gets the other's value back is second: it adds,
+        // writes the output and empties the slot again. The sum of two numbers does not depend
+        // on who was first. Empty = +0.0, so a partial that is +0.0 travels as -0.0 (same sum).
+        float* sl = a.ws + ((size_t)(pslot ? my_cta : my_cta - 1) * 2 + 1) * 128;
+        unsigned old[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          unsigned bits = __float_as_uint(f[k]);
+          if (bits == 0u) bits = 0x80000000u;
+          old[k] = atomicExch(reinterpret_cast<unsigned*>(sl + k * 32 + lane), bits);
+        }
+        float sum[4];
+        unsigned mask = 0u;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          sum[k] = __uint_as_float(old[k]) + f[k];
+          if (old[k] != 0u) {
+            mask |= 1u << k;
+            __stcg(sl + k * 32 + lane, 0.f);
+          }
+        }
+        if (mask) tile_out(a.o, T, sum, lane, mask);
+        return;
+      }
       // one partial per CTA through global memory; whoever completes the tile adds them all
       float* gm = a.ws + ((size_t)my_cta * 2 + pslot) * 128;
 #pragma unroll
@@ -532,9 +559,12 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
 #pragma unroll 1
       for (int cc = c_lo; cc <= c_hi; ++cc) {
         const int cb = cta_begin(total, q, a.nctas, cc);
-        const float* p = a.ws + ((size_t)cc * 2 + (cb > T * G ? 0 : 1)) * 128;
+        float* p = a.ws + ((size_t)cc * 2 + (cb > T * G ? 0 : 1)) * 128;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) sum[k] += __ldcg(p + k * 32 + lane);
+        for (int k = 0; k < 4; ++k) {
+          sum[k] += __ldcg(p + k * 32 + lane);
+          __stcg(p + k * 32 + lane, 0.f);  // the slots are left empty for the two-owner exchange
+        }
       }
       tile_out(a.o, T, sum, lane);
       if (lane == 0) a.counters[T] = 0;
@@ -658,7 +688,7 @@ const std::vector<ShapeCfg>& env_overrides() {
 struct Resolved {
   qe_w4_plan plan;
   const Geometry* geom;
-  int nctas, nwarps, quantum, cta_quantum;
+  int nctas, nwarps, quantum, cta_quantum, two_way;
 };
 
 // Shape-only launch policy (never N): as many warps as there are units / min_units, at most one
@@ -693,6 +723,8 @@ Resolved resolve(const qe_w4_params& p, const qe_w4_cfg& c_in) {
   const long tiles_max = (tiles + ctas - 1) / ctas;
   const bool whole_tiles = ctas > 1 && tiles >= ctas && (tiles_max * ctas - tiles) * G <= 26 * ctas;
   r.cta_quantum = whole_tiles ? (int)G : (int)quantum;
+  // the smallest CTA range in units; at least a tile long means no tile has three owners
+  r.two_way = ((units / r.cta_quantum) / ctas) * r.cta_quantum >= G ? 1 : 0;
   r.nctas = (int)ctas;
   r.plan.mode = 4;
   r.plan.grid_x = (int)ctas;
@@ -742,6 +774,7 @@ int make_job(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg,
   a.nwarps = r.nwarps;
   a.quantum = r.quantum;
   a.cta_quantum = r.cta_quantum;
+  a.two_way = r.two_way;
   a.xvec = ((p->ldx & 7) == 0 && aligned16(p->x)) ? 1 : 0;
   *smem_extra = 0;
   if (nrm && nrm->h_in) {
