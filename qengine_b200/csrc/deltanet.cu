@@ -89,27 +89,62 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
   float* Sj = a.S + (size_t)j * D * D + c0 + lane;
 
   // ---- independent of this pass's producer: state slice, per-head constants, checkpoints ----
-  // Every load below is issued before anything waits: the state (3 MB per layer, from HBM), all
-  // eight checkpoint slots (whether or not they are pending: that is only known once ctl arrives,
-  // and waiting for it would put a second memory round trip in front of the replay) and ctl.
+  // Every global load of this section is issued into registers before anything is used: a
+  // "shared[i] = global[j]" loop stalls on each store until its load is back, one memory round
+  // trip per iteration (that was 4 us in front of the replay). Loaded here: ctl, the state (3 MB
+  // per layer, from HBM), all eight checkpoint slots (whether or not they are pending: that is
+  // only known once ctl arrives), the per-head constants and the conv taps; the conv history
+  // needs the position and follows as soon as ctl is there.
+  const int ctl_pos = a.ctl[0], ctl_pending = a.ctl[1];
   float s[RP];
 #pragma unroll
   for (int i = 0; i < RP; ++i) s[i] = Sj[(size_t)(warp * RP + i) * D];
-  for (int idx = tid; idx < kMaxRows * D; idx += NT) {
-    const int t = idx / D, i = idx - t * D;
-    k_s[t][i] = a.st_k[((size_t)t * a.Hv + j) * D + i];
+  constexpr int KPT = kMaxRows * D / NT;  // checkpoint k values per thread
+  float kreg[KPT];
+#pragma unroll
+  for (int u = 0; u < KPT; ++u) {
+    const int idx = tid + u * NT, t = idx / D, i = idx - t * D;
+    kreg[u] = a.st_k[((size_t)t * a.Hv + j) * D + i];
   }
-  {
-    const int t = tid >> 5;  // 8 warps = 8 slots, lane = column
-    v_s[t][lane] = a.st_v[((size_t)t * a.Hv + j) * D + c0 + lane];
-    if (lane < 2) gate_s[t][lane] = a.st_g[(t * a.Hv + j) * 2 + lane];
-  }
+  const float vreg = a.st_v[((size_t)warp * a.Hv + j) * D + c0 + lane];  // 8 warps = 8 slots, lane = column
+  const float greg = lane < 2 ? a.st_g[(warp * a.Hv + j) * 2 + lane] : 0.f;
   const float A_log = tofloat(a.A_log[j]), dt_bias = tofloat(a.dt_bias[j]);
   const float nw = tofloat(a.norm_w[c0 + lane]);
+  // conv channels of this thread (q and k: all D channels of the head's q/k head; v: own columns)
+  constexpr int CPT = (2 * D + kCols + NT - 1) / NT;  // 2 for D = 128
+  float cw[CPT][4], hx[CPT][3];
+  int chn[CPT];
+#pragma unroll
+  for (int u = 0; u < CPT; ++u) {
+    const int idx = tid + u * NT;
+    chn[u] = -1;
+    if (idx < 2 * D + kCols) {
+      const int part_id = idx < D ? 0 : idx < 2 * D ? 1 : 2;
+      const int c = part_id == 0 ? idx : part_id == 1 ? idx - D : idx - 2 * D;
+      chn[u] = part_id == 0 ? i_qk * D + c : part_id == 1 ? a.Hk * D + i_qk * D + c : 2 * a.Hk * D + j * D + c0 + c;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) cw[u][w] = tofloat(a.conv_w[chn[u] * 4 + w]);
+    }
+  }
   // ctl and the checkpoints were written by the previous pass, which has completed (the first
   // kernel of a pass is launched in plain stream order): with `early` the whole replay, including
   // the write-back of S, runs before the dependency wait and overlaps the tail of the in_proj GEMV.
-  const int P = a.ctl[0], pend = min(max(a.ctl[1], 0), kMaxRows);
+  const int P = ctl_pos, pend = min(max(ctl_pending, 0), kMaxRows);
+#pragma unroll
+  for (int u = 0; u < CPT; ++u) {
+#pragma unroll
+    for (int b = 0; b < 3; ++b) {
+      const int p = P - 3 + b;
+      hx[u][b] = (chn[u] >= 0 && p >= 0) ? tofloat(a.ring[(size_t)(p & (kRing - 1)) * C + chn[u]]) : 0.f;
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < KPT; ++u) {
+    const int idx = tid + u * NT, t = idx / D, i = idx - t * D;
+    k_s[t][i] = kreg[u];
+  }
+  v_s[warp][lane] = vreg;
+  if (lane < 2) gate_s[warp][lane] = greg;
 
   // S <- decay S + k (beta (v - decay S^T k))^T on this thread's rows of its column; with Q also
   // returns o = S'^T q for the column. Identical arithmetic for replayed and new rows.
@@ -152,32 +187,21 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
 #pragma unroll
     for (int i = 0; i < RP; ++i) Sj[(size_t)(warp * RP + i) * D] = s[i];
   }
-  // conv taps and history of the channels this thread convolves below: constants and state of
-  // earlier passes, fetched before the dependency wait as well
-  constexpr int CPT = (2 * D + kCols + NT - 1) / NT;  // conv channels per thread (2 for D = 128)
-  float cw[CPT][4], hx[CPT][3];
-  int chn[CPT];
-#pragma unroll
-  for (int u = 0; u < CPT; ++u) {
-    const int idx = tid + u * NT;
-    chn[u] = -1;
-    if (idx < 2 * D + kCols) {
-      const int part_id = idx < D ? 0 : idx < 2 * D ? 1 : 2;
-      const int c = part_id == 0 ? idx : part_id == 1 ? idx - D : idx - 2 * D;
-      const int ch = part_id == 0 ? i_qk * D + c : part_id == 1 ? a.Hk * D + i_qk * D + c : 2 * a.Hk * D + j * D + c0 + c;
-      chn[u] = ch;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) cw[u][w] = tofloat(a.conv_w[ch * 4 + w]);
-#pragma unroll
-      for (int b = 0; b < 3; ++b) {
-        const int p = P - 3 + b;
-        hx[u][b] = p >= 0 ? tofloat(a.ring[(size_t)(p & (kRing - 1)) * C + ch]) : 0.f;
-      }
-    }
-  }
   if (a.early) dep_wait();  // from here on: this pass's projections
-  // the gate input of this warp's row is only needed at the very end: fetch it now
+  // the gate input of this warp's row is only needed at the very end: fetch it now; likewise the
+  // decay / beta inputs of row tid, which the same thread would otherwise only request after its
+  // share of the convolution (a second, dependent memory round trip)
   const float z_pre = warp < n ? tofloat(a.z[(long)warp * a.ldp + j * D + c0 + lane]) : 0.f;
+  const float b_pre = tid < n ? tofloat(a.b[(long)tid * a.ldp + j]) : 0.f;
+  const float a_pre = tid < n ? tofloat(a.a[(long)tid * a.ldp + j]) : 0.f;
+  // and every projection value this thread convolves, all rows at once: independent loads in
+  // flight together instead of one round trip per row and channel
+  bf16 xr[CPT][kMaxRows];
+#pragma unroll
+  for (int u = 0; u < CPT; ++u)
+#pragma unroll
+    for (int t = 0; t < kMaxRows; ++t)
+      if (chn[u] >= 0 && t < n) xr[u][t] = a.qkv[(long)t * a.ldp + chn[u]];
   __syncthreads();  // k_s / v_s are about to be overwritten by the new rows
 
   // ---- 2a. causal conv + SiLU of every new row (q, k: all D channels; v: own columns) ----
@@ -191,8 +215,10 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
     float x0 = hx[u][0], x1 = hx[u][1], x2 = hx[u][2];
     // q/k channels are shared by `rep` heads and by the CTAs of a head: one CTA writes them
     const bool owner = part_id == 2 || ((j % rep) == 0 && cs == 0);
-    for (int t = 0; t < n; ++t) {
-      const bf16 xb = a.qkv[(long)t * a.ldp + ch];
+#pragma unroll
+    for (int t = 0; t < kMaxRows; ++t) {
+      if (t >= n) break;
+      const bf16 xb = xr[u][t];
       const float x3 = tofloat(xb);
       float acc = cw[u][0] * x0;
       acc = fmaf(cw[u][1], x1, acc);
@@ -208,8 +234,8 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
   }
   if (tid < n) {
     const int t = tid;
-    const float bt = rnd(sigmoid_acc(tofloat(a.b[(long)t * a.ldp + j])));
-    const float x = tofloat(a.a[(long)t * a.ldp + j]) + dt_bias;
+    const float bt = rnd(sigmoid_acc(b_pre));
+    const float x = a_pre + dt_bias;
     const float sp = x > 20.f ? x : log1pf(expf(x));
     gate_s[t][0] = expf(-expf(A_log) * sp);
     gate_s[t][1] = bt;
