@@ -224,6 +224,12 @@ typedef struct qe_w4_params {
   int out_f32;         /* 0: out is bf16 (the reference's contract). 1 (plain epilogue only): out is
                           fp32, ldo in floats, sums stored unrounded -- the partial sums of a matrix
                           split along K over tensor-parallel ranks. No counterpart in the reference. */
+  int x_f16;           /* 0: x is bf16 (the reference's contract). 1: x holds fp16 rows (same strides in
+                          elements); needs K == Kp, 16-byte aligned rows and ldx % 8 == 0, else
+                          QE_ERR_ARG. The kernel then unpacks the codes to fp16 (one shift per word
+                          instead of three). For values that fp16 holds exactly -- bf16 numbers of
+                          magnitude 2^-17 .. 65504, e.g. rows normalised by qe_w4_norm_rows -- the
+                          result has the bits of the bf16 path. No counterpart in the reference. */
 } qe_w4_params;
 
 /* Launch options with the reference's names (csrc/gemv_w4.h:27-39). 0 / -1 mean "auto by shape".
@@ -258,7 +264,12 @@ typedef struct qe_w4_plan {
  *   NULL, h_in is an embedding table [vocab, K] and row r is table[tok[r]] (zeros when out of
  *   range). Needs K == Kp, 16-byte aligned rows, row strides that are multiples of 8, and
  *   N * (2 K + 16) bytes of shared memory beside the weight rings (QE_ERR_ARG otherwise: run
- *   qe_rmsnorm1p and qe_w4_gemv instead). */
+ *   qe_rmsnorm1p and qe_w4_gemv instead).
+ *   f16 != 0: the normalised rows (rounded to bf16 as always) are kept as fp16 in shared memory and
+ *   the GEMV runs its fp16 flavour (see qe_w4_params::x_f16). A normalised element is at most
+ *   sqrt(K) * |1 + norm_w| in magnitude: the caller checks its norm weights once. xn16_out
+ *   (qe_w4_norm_rows only, optional): fp16 copy of the normalised rows [N, K], stride ldx16, the
+ *   input of a qe_w4_gemv with x_f16 = 1 that then equals the fused launch bit for bit. */
 typedef struct qe_w4_norm {
   const void* h_in;    /* bf16 [N, K] rows (stride ldh), or the embedding table when tok != NULL */
   const int* tok;      /* optional token ids [N] */
@@ -269,6 +280,9 @@ typedef struct qe_w4_norm {
   void* xn_out;        /* optional bf16 [N, K], stride ldxo */
   long ldh, ldd, ldho, ldxo;
   float eps;
+  int f16;             /* fused prologue: fp16 activations, see above */
+  void* xn16_out;      /* qe_w4_norm_rows: optional fp16 [N, K] */
+  long ldx16;
 } qe_w4_norm;
 
 /* Default-initialise a cfg (all auto, pdl on, min_units 4). */

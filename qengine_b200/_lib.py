@@ -18,7 +18,7 @@ class W4Params(C.Structure):
     """struct qe_w4_params"""
     _fields_ = [("qw", P), ("scales", P), ("x", P), ("out", P), ("ws", P), ("counters", P),
                 ("M", c_int), ("K", c_int), ("Mp", c_int), ("Kp", c_int), ("N", c_int),
-                ("ldx", c_long), ("ldo", c_long), ("epilogue", c_int), ("out_f32", c_int)]
+                ("ldx", c_long), ("ldo", c_long), ("epilogue", c_int), ("out_f32", c_int), ("x_f16", c_int)]
 
 
 class W4Cfg(C.Structure):
@@ -31,7 +31,7 @@ class W4Norm(C.Structure):
     """struct qe_w4_norm"""
     _fields_ = [("h_in", P), ("tok", P), ("vocab", c_int), ("delta", P), ("norm_w", P), ("h_out", P),
                 ("xn_out", P), ("ldh", c_long), ("ldd", c_long), ("ldho", c_long), ("ldxo", c_long),
-                ("eps", c_float)]
+                ("eps", c_float), ("f16", c_int), ("xn16_out", P), ("ldx16", c_long)]
 
 
 class W4Plan(C.Structure):

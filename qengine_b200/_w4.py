@@ -130,13 +130,16 @@ def _launch(jobs, cfg, what):
     launches[0] += 1
 
 
-def job(x, qw, scales, out, M, swiglu=False, allow_f32_out=False) -> Job:
-    """Describe out = x @ W~^T (or the SwiGLU of a gate/up pack) without launching it."""
+def job(x, qw, scales, out, M, swiglu=False, allow_f32_out=False, allow_f16_x=False) -> Job:
+    """Describe out = x @ W~^T (or the SwiGLU of a gate/up pack) without launching it.
+    allow_f16_x: x may be fp16 (rows written by `norm_rows(xn16_out=...)`, see qe_w4_params::x_f16);
+    the reference's surface (`gemv`, `gemv_swiglu`) takes bf16 only."""
     for t in (x, qw, scales, out):
         _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
     epilogue = EPI_SWIGLU if swiglu else EPI_NONE
     out_f32 = allow_f32_out and out.dtype == torch.float32 and epilogue == EPI_NONE
-    _req(x.dtype == torch.bfloat16, "x must be bf16 (W4A16 kernel)")
+    x_f16 = allow_f16_x and x.dtype == torch.float16
+    _req(x.dtype == torch.bfloat16 or x_f16, "x must be bf16 (W4A16 kernel)")
     _req(out.dtype == torch.bfloat16 or out_f32, "out must be bf16")
     Mp, Kp = _packed(qw, scales)
     _req(x.dim() == 2 and out.dim() == 2, "x [N,K], out [N,M]")
@@ -151,15 +154,18 @@ def job(x, qw, scales, out, M, swiglu=False, allow_f32_out=False) -> Job:
     else:
         _req(Mp - 16 < M <= Mp, "out width M must match packed rows")
     _req(x.data_ptr() != out.data_ptr(), "in-place not supported")
+    if x_f16:
+        _req(K == Kp and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "fp16 x: K == Kp, aligned rows")
     p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None,
-                 M, K, Mp, Kp, N, x.stride(0), out.stride(0), epilogue, int(out_f32))
+                 M, K, Mp, Kp, N, x.stride(0), out.stride(0), epilogue, int(out_f32), int(x_f16))
     return Job(p, None, x.device, (x, qw, scales, out))
 
 
 def job_fused(h_in, delta, norm_w, eps, qw, scales, out, M, h_out=None, xn_out=None, tok=None,
-              swiglu=False) -> Job:
+              swiglu=False, f16=False) -> Job:
     """Describe out = gemv(RMSNorm1p(h_in + delta) * (1 + norm_w)) without launching it (see
-    `gemv_fused` for the arguments)."""
+    `gemv_fused` for the arguments). f16: keep the normalised rows as fp16 and run the fp16
+    flavour of the GEMV (qe_w4_norm::f16; the caller vouches for sqrt(K) * |1 + norm_w| < 65504)."""
     for t in (h_in, norm_w, qw, scales, out):
         _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
     Mp, Kp = _packed(qw, scales)
@@ -191,8 +197,9 @@ def job_fused(h_in, delta, norm_w, eps, qw, scales, out, M, h_out=None, xn_out=N
         nrm.h_out, nrm.ldho = h_out.data_ptr(), h_out.stride(0)
     if xn_out is not None:
         nrm.xn_out, nrm.ldxo = xn_out.data_ptr(), xn_out.stride(0)
+    nrm.f16 = int(bool(f16))
     p = W4Params(qw.data_ptr(), scales.data_ptr(), None, out.data_ptr(), None, None, M, Kp, Mp, Kp, N,
-                 0, out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, 0)
+                 0, out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, 0, 0)
     return Job(p, nrm, out.device, (h_in, delta, norm_w, qw, scales, out, h_out, xn_out, tok))
 
 
@@ -232,7 +239,7 @@ def gemv_partial(x, qw, scales, out32, M, warps=0, unroll=0, ksplit=0, pdl=True,
 
 
 def gemv_fused(h_in, delta, norm_w, eps, qw, scales, out, M, *, h_out=None, xn_out=None, tok=None,
-               swiglu=False, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
+               swiglu=False, f16=False, warps=0, unroll=0, ksplit=0, pdl=True, variant=0, mode=-1,
                blocks_per_sm=0, min_units=4):
     """Not in the reference: out = gemv(RMSNorm1p(h_in + delta) * (1 + norm_w)) in one launch.
 
@@ -241,15 +248,17 @@ def gemv_fused(h_in, delta, norm_w, eps, qw, scales, out, M, *, h_out=None, xn_o
     embedding table [V, K] and row r is table[tok[r]]. Same arithmetic as `_C.rmsnorm1p` followed
     by `gemv`."""
     _launch([job_fused(h_in, delta, norm_w, eps, qw, scales, out, M, h_out=h_out, xn_out=xn_out, tok=tok,
-                       swiglu=swiglu)],
+                       swiglu=swiglu, f16=f16)],
             _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units), "gemv_w4 fused")
 
 
-def norm_rows(h_in, delta, norm_w, eps, xn_out, h_out=None, tok=None, warps=0, unroll=0, ksplit=0, pdl=True,
-              variant=0, mode=-1, blocks_per_sm=0, min_units=4):
+def norm_rows(h_in, delta, norm_w, eps, xn_out, h_out=None, tok=None, xn16_out=None, warps=0, unroll=0, ksplit=0,
+              pdl=True, variant=0, mode=-1, blocks_per_sm=0, min_units=4):
     """Not in the reference: the prologue of `gemv_fused` as a launch of its own (one block per row),
     bit-identical to it for the same launch options: xn_out = RMSNorm1p(h_in + delta) * (1 + w),
-    h_out = bf16(h_in + delta) (may alias h_in). `norm_rows` + `gemv` == `gemv_fused`."""
+    h_out = bf16(h_in + delta) (may alias h_in). `norm_rows` + `gemv` == `gemv_fused`.
+    xn16_out (fp16 [N, K], optional) receives the same rows as fp16: the input of a GEMV job with
+    fp16 activations, which equals `gemv_fused(f16=True)`."""
     bf = torch.bfloat16
     _req(xn_out.is_cuda and xn_out.dtype == bf and xn_out.dim() == 2 and xn_out.stride(1) == 1, "xn_out bf16 [N, K]")
     N, K = xn_out.shape
@@ -271,6 +280,10 @@ def norm_rows(h_in, delta, norm_w, eps, xn_out, h_out=None, tok=None, warps=0, u
         nrm.delta, nrm.ldd = delta.data_ptr(), delta.stride(0)
     if h_out is not None:
         nrm.h_out, nrm.ldho = h_out.data_ptr(), h_out.stride(0)
+    if xn16_out is not None:
+        _req(xn16_out.is_cuda and xn16_out.dtype == torch.float16 and xn16_out.shape == (N, K) and
+             xn16_out.stride(1) == 1, "xn16_out fp16 [N, K]")
+        nrm.xn16_out, nrm.ldx16 = xn16_out.data_ptr(), xn16_out.stride(0)
     cfg = _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units)
     check(lib.qe_w4_norm_rows(C.byref(nrm), N, K, C.byref(cfg), torch.cuda.current_stream().cuda_stream), "norm_rows")
 
@@ -310,7 +323,7 @@ def gemv_static(x, qw, scales, out, M, swiglu=False, warps=0, unroll=0, ksplit=0
     _req(Kp - 128 < K <= Kp, "shapes disagree")
     _req((Mp // 2 - 8 < M <= Mp // 2) if swiglu else (Mp - 16 < M <= Mp), "out width must match packed rows")
     p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None, M, K, Mp, Kp, N,
-                 x.stride(0), out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, 0)
+                 x.stride(0), out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, 0, 0)
     cfg = W4Cfg(int(warps), int(unroll), int(ksplit), 0, int(variant), int(mode), int(blocks_per_sm), int(min_units))
     code = lib.qe_w4_gemv_static(C.byref(p), C.byref(cfg), torch.cuda.current_stream().cuda_stream)
     _req(code != -28, "gemv_static: this shape needs more scratch than the library's fixed array "

@@ -16,7 +16,7 @@ int pdl_trigger_enabled() { return g_trigger.load(std::memory_order_relaxed); }
 
 }  // namespace qb
 
-extern "C" int qe_abi_version(void) { return 2; }
+extern "C" int qe_abi_version(void) { return 3; }
 
 extern "C" int qe_sm_count(void) {
   static int per_dev[64] = {0};

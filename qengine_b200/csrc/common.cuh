@@ -31,6 +31,13 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 __device__ __forceinline__ uint4 narrow8(const float (&f)[8]) {
   return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
 }
+// eight floats -> eight fp16 (round to nearest), one 16-byte packet
+__device__ __forceinline__ uint4 half8(const float (&f)[8]) {
+  const __half2 a = __floats2half2_rn(f[0], f[1]), b = __floats2half2_rn(f[2], f[3]);
+  const __half2 c = __floats2half2_rn(f[4], f[5]), d = __floats2half2_rn(f[6], f[7]);
+  return make_uint4(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b),
+                    *reinterpret_cast<const uint32_t*>(&c), *reinterpret_cast<const uint32_t*>(&d));
+}
 
 // torch-accurate activations (expf, not the fast intrinsic).
 __device__ __forceinline__ float silu_acc(float v) { return v / (1.0f + expf(-v)); }

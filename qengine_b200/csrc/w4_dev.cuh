@@ -50,6 +50,43 @@ __device__ __forceinline__ void mma_word(float (&c)[4], uint32_t word, uint32_t 
       : "r"(f.a0), "r"(f.a1), "r"(f.a2), "r"(f.a3), "r"(xa), "r"(xb));
 }
 
+// ---- int4 -> fp16 (activations held as fp16) ------------------------------------------------------
+// fp16 has ten mantissa bits: the nibbles at bits 0..3 AND at bits 4..7 of a half-word both sit
+// inside the mantissa of 0x6400 | bits (= 1024 + u, resp. 1024 + 16 u). The first becomes u - 8
+// by subtracting 1032, the second by one fused multiply-add, (1024 + 16 u) / 16 - 72. Only the
+// upper byte needs a shift: one SHF per word instead of three on the half-rate ALU pipe, the
+// busiest unit of the kernel (bf16 has seven mantissa bits, where this does not work).
+__device__ __forceinline__ uint32_t nib2f16_lo(uint32_t w) {
+  uint32_t v;
+  asm("lop3.b32 %0, %1, 0x000F000F, 0x64006400, 0xEA;" : "=r"(v) : "r"(w));
+  asm("sub.rn.f16x2 %0, %0, %1;" : "+r"(v) : "r"(0x64086408u));  // - 1032
+  return v;
+}
+__device__ __forceinline__ uint32_t nib2f16_hi(uint32_t w) {
+  uint32_t v;
+  asm("lop3.b32 %0, %1, 0x00F000F0, 0x64006400, 0xEA;" : "=r"(v) : "r"(w));
+  asm("fma.rn.f16x2 %0, %0, %1, %2;" : "+r"(v) : "r"(0x2C002C00u), "r"(0xD480D480u));  // * 2^-4 - 72
+  return v;
+}
+__device__ __forceinline__ AFrag unpack_word_f16(uint32_t word) {
+  const uint32_t up = word >> 8;
+  return AFrag{nib2f16_lo(word), nib2f16_hi(word), nib2f16_lo(up), nib2f16_hi(up)};
+}
+__device__ __forceinline__ void mma_first_f16(float (&c)[4], uint32_t word, uint32_t xa, uint32_t xb) {
+  const AFrag f = unpack_word_f16(word);
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+      : "r"(f.a0), "r"(f.a1), "r"(f.a2), "r"(f.a3), "r"(xa), "r"(xb), "f"(0.f));
+}
+__device__ __forceinline__ void mma_word_f16(float (&c)[4], uint32_t word, uint32_t xa, uint32_t xb) {
+  const AFrag f = unpack_word_f16(word);
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(f.a0), "r"(f.a1), "r"(f.a2), "r"(f.a3), "r"(xa), "r"(xb));
+}
+
 // Operands of one unit for one lane: 2 x 16 B of codes, 2 scales (rows r, r + 8), 32 x values.
 struct UnitOps {
   uint4 w0, w1;
@@ -71,6 +108,26 @@ __device__ __forceinline__ void unit_fma(float (&acc)[4], const UnitOps& o) {
   mma_word(c, o.w1.y, o.x2.z, o.x2.w);
   mma_word(c, o.w1.z, o.x3.x, o.x3.y);
   mma_word(c, o.w1.w, o.x3.z, o.x3.w);
+  const float lo = __half2float(__ushort_as_half((unsigned short)o.s_lo));
+  const float hi = __half2float(__ushort_as_half((unsigned short)o.s_hi));
+  acc[0] = fmaf(lo, c[0], acc[0]);
+  acc[1] = fmaf(lo, c[1], acc[1]);
+  acc[2] = fmaf(hi, c[2], acc[2]);
+  acc[3] = fmaf(hi, c[3], acc[3]);
+}
+
+// The same with fp16 activations: the products are exact either way (4-bit code times an 8-bit
+// significand), so for activations that fp16 holds exactly the sums have the same bits.
+__device__ __forceinline__ void unit_fma_f16(float (&acc)[4], const UnitOps& o) {
+  float c[4];
+  mma_first_f16(c, o.w0.x, o.x0.x, o.x0.y);
+  mma_word_f16(c, o.w0.y, o.x0.z, o.x0.w);
+  mma_word_f16(c, o.w0.z, o.x1.x, o.x1.y);
+  mma_word_f16(c, o.w0.w, o.x1.z, o.x1.w);
+  mma_word_f16(c, o.w1.x, o.x2.x, o.x2.y);
+  mma_word_f16(c, o.w1.y, o.x2.z, o.x2.w);
+  mma_word_f16(c, o.w1.z, o.x3.x, o.x3.y);
+  mma_word_f16(c, o.w1.w, o.x3.z, o.x3.w);
   const float lo = __half2float(__ushort_as_half((unsigned short)o.s_lo));
   const float hi = __half2float(__ushort_as_half((unsigned short)o.s_hi));
   acc[0] = fmaf(lo, c[0], acc[0]);

@@ -48,6 +48,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <type_traits>
 #include <utility>
 #include <vector>
 
@@ -72,6 +73,10 @@ struct GemvArgs {
   int quantum;     // warp ranges start at multiples of this many units (4 when G % 4 == 0, else 1)
   int cta_quantum; // CTA ranges start at multiples of this many units: `quantum`, or G (whole tiles)
   int two_way;     // every CTA range holds at least one tile's worth of units: a cut tile has two owners
+  int xf16;        // the activations are fp16: `x` points to fp16 rows, or the prologue leaves fp16
+                   // in shared memory (the normalised rows, which fp16 holds exactly, see make_job)
+  __half* xn16_out;  // norm_rows_kernel only: optional fp16 copy of the normalised rows
+  long ldx16;
   int xvec;        // x rows are 16-byte aligned with ldx % 8 == 0
   // fused residual + RMSNorm prologue (h_in != nullptr)
   const bf16* h_in;
@@ -231,9 +236,20 @@ __device__ __forceinline__ void norm_prologue(const GemvArgs& a, unsigned char* 
 #pragma unroll
           for (int e = 0; e < 8; ++e) y[e] = v[e] * inv[i] * (1.0f + g[e]);
           const uint4 q = narrow8(y);
-          xs[p] = q;
-          if (writer && a.xn_out && reinterpret_cast<unsigned char*>(a.xn_out) != x_s)
-            reinterpret_cast<uint4*>(a.xn_out + (long)r * a.ldxo)[p] = q;
+          const bool in_place = reinterpret_cast<unsigned char*>(a.xn_out) == x_s;  // stand-alone kernel
+          if (a.xf16) {  // the bf16-rounded values again, as fp16 (exact for normalised rows)
+            widen8(q, y);
+            const uint4 q16 = half8(y);
+            if (in_place) {
+              xs[p] = q;
+              if (a.xn16_out) reinterpret_cast<uint4*>(a.xn16_out + (long)r * a.ldx16)[p] = q16;
+            } else {
+              xs[p] = q16;
+            }
+          } else {
+            xs[p] = q;
+          }
+          if (writer && a.xn_out && !in_place) reinterpret_cast<uint4*>(a.xn_out + (long)r * a.ldxo)[p] = q;
         }
       }
     }
@@ -402,100 +418,113 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_chain_kernel(const __grid_const
       seg_gb = g;
     };
 
-    // Both loops below walk the ring stage by stage. The fast one serves ranges made of whole
-    // stages that never straddle a tile (every matrix of the model): no per-unit decisions at
-    // all, every operand at an immediate offset from three base pointers.
-    const bool all_fast = xfast && !tail_k && (a.quantum % PERW) == 0;
-    if (all_fast) {
-      const unsigned char* xg = xbase + (size_t)g * 256;
-      // the next stage to request from HBM: whole stages only in this loop, so the copy sizes are
-      // constants and the global addresses advance by constants
-      const unsigned char* gw = reinterpret_cast<const unsigned char*>(a.qw) + (size_t)(u0 + STAGES * PERW) * 1024;
-      const unsigned char* gs = reinterpret_cast<const unsigned char*>(a.scales) + (size_t)(u0 + STAGES * PERW) * 32;
-      int to_request = nstage - STAGES;  // stages not yet requested
-#pragma unroll 1
-      for (int st = 0; st < nstage && ok; ++st) {
-        uint64_t* bar = &full[warp][slot];
-        if (!bar_wait(bar, phase, kWaitLimit)) {
-          ok = false;
-          atomicExch(&g_w4_error, 1);
-          break;
+    // The stream exists twice, once per activation type (a.xf16): two separate loops, each with
+    // its own register allocation, in ONE kernel function -- both unpack flavours inlined side by
+    // side in one loop spill, and two kernel functions that alternate from launch to launch cost
+    // more in instruction fetch than the cheaper unpack saves.
+    auto stream = [&](auto f16_tag) {
+      constexpr bool F16 = decltype(f16_tag)::value;
+      // Both loops below walk the ring stage by stage. The fast one serves ranges made of whole
+      // stages that never straddle a tile (every matrix of the model): no per-unit decisions at
+      // all, every operand at an immediate offset from three base pointers.
+      const bool all_fast = xfast && !tail_k && (a.quantum % PERW) == 0;
+      if (all_fast) {
+        const unsigned char* xg = xbase + (size_t)g * 256;
+        // the next stage to request from HBM: whole stages only in this loop, so the copy sizes are
+        // constants and the global addresses advance by constants
+        const unsigned char* gw = reinterpret_cast<const unsigned char*>(a.qw) + (size_t)(u0 + STAGES * PERW) * 1024;
+        const unsigned char* gs = reinterpret_cast<const unsigned char*>(a.scales) + (size_t)(u0 + STAGES * PERW) * 32;
+        int to_request = nstage - STAGES;  // stages not yet requested
+  #pragma unroll 1
+        for (int st = 0; st < nstage && ok; ++st) {
+          uint64_t* bar = &full[warp][slot];
+          if (!bar_wait(bar, phase, kWaitLimit)) {
+            ok = false;
+            atomicExch(&g_w4_error, 1);
+            break;
+          }
+          unsigned char* stage_w = ring_w + (size_t)slot * kStageW;
+          unsigned char* stage_s = ring_s + (size_t)slot * kStageS;
+          const uint4* wp = reinterpret_cast<const uint4*>(stage_w) + lane;
+          const unsigned short* sp = reinterpret_cast<const unsigned short*>(stage_s) + r;
+          const uint4* xp = reinterpret_cast<const uint4*>(xg);
+          UnitOps ops[PERW];
+  #pragma unroll
+          for (int i = 0; i < PERW; ++i) {
+            ops[i].w0 = wp[i * 64];
+            ops[i].w1 = wp[i * 64 + 32];
+            ops[i].s_lo = sp[i * 16];
+            ops[i].s_hi = sp[i * 16 + 8];
+            ops[i].x0 = xp[i * 16];
+            ops[i].x1 = xp[i * 16 + 1];
+            ops[i].x2 = xp[i * 16 + 8];
+            ops[i].x3 = xp[i * 16 + 9];
+          }
+  #pragma unroll
+          for (int i = 0; i < PERW; ++i) {
+            if constexpr (F16) unit_fma_f16(acc, ops[i]);
+            else unit_fma(acc, ops[i]);
+          }
+          g += PERW;
+          xg += PERW * 256;
+          if (g == G || st == nstage - 1) {
+            close_segment();
+            xg = xbase + (size_t)g * 256;
+          }
+          __syncwarp();  // every lane has read this stage: hand its slot back to the copy engine
+          if (to_request > 0) {
+            if (lane == 0) {
+              async_proxy_fence();
+              bar_expect(bar, kStageW + kStageS);
+              bulk_g2s(stage_w, gw, kStageW, bar);
+              bulk_g2s(stage_s, gs, kStageS, bar);
+            }
+            gw += kStageW;
+            gs += kStageS;
+            --to_request;
+          }
+          if (++slot == STAGES) { slot = 0; phase ^= 1; }
         }
-        unsigned char* stage_w = ring_w + (size_t)slot * kStageW;
-        unsigned char* stage_s = ring_s + (size_t)slot * kStageS;
-        const uint4* wp = reinterpret_cast<const uint4*>(stage_w) + lane;
-        const unsigned short* sp = reinterpret_cast<const unsigned short*>(stage_s) + r;
-        const uint4* xp = reinterpret_cast<const uint4*>(xg);
-        UnitOps ops[PERW];
-#pragma unroll
-        for (int i = 0; i < PERW; ++i) {
-          ops[i].w0 = wp[i * 64];
-          ops[i].w1 = wp[i * 64 + 32];
-          ops[i].s_lo = sp[i * 16];
-          ops[i].s_hi = sp[i * 16 + 8];
-          ops[i].x0 = xp[i * 16];
-          ops[i].x1 = xp[i * 16 + 1];
-          ops[i].x2 = xp[i * 16 + 8];
-          ops[i].x3 = xp[i * 16 + 9];
-        }
-#pragma unroll
-        for (int i = 0; i < PERW; ++i) unit_fma(acc, ops[i]);
-        g += PERW;
-        xg += PERW * 256;
-        if (g == G || st == nstage - 1) {
-          close_segment();
-          xg = xbase + (size_t)g * 256;
-        }
-        __syncwarp();  // every lane has read this stage: hand its slot back to the copy engine
-        if (to_request > 0) {
-          if (lane == 0) {
+      } else {
+  #pragma unroll 1
+        for (int st = 0; st < nstage && ok; ++st) {
+          if (!bar_wait(&full[warp][slot], phase, kWaitLimit)) {
+            ok = false;
+            atomicExch(&g_w4_error, 1);
+            break;
+          }
+          const uint4* wp = reinterpret_cast<const uint4*>(ring_w + (size_t)slot * kStageW) + lane;
+          const unsigned short* sp = reinterpret_cast<const unsigned short*>(ring_s + (size_t)slot * kStageS) + r;
+          const int cnt = min(PERW, n_units - st * PERW);
+  #pragma unroll 1
+          for (int i = 0; i < cnt; ++i) {
+            UnitOps o;
+            o.w0 = wp[i * 64];
+            o.w1 = wp[i * 64 + 32];
+            o.s_lo = sp[i * 16];
+            o.s_hi = sp[i * 16 + 8];
+            if (xfast && !(tail_k && g == G - 1)) {
+              const uint4* xp = reinterpret_cast<const uint4*>(xbase + (size_t)g * 256);
+              o.x0 = xp[0]; o.x1 = xp[1]; o.x2 = xp[8]; o.x3 = xp[9];
+            } else {
+              load_x_slow(o, a.x + (long)xrow * a.ldx, g, t, a.K);
+            }
+            if constexpr (F16) unit_fma_f16(acc, o);
+            else unit_fma(acc, o);
+            ++g;
+            if (g == G || (st == nstage - 1 && i == cnt - 1)) close_segment();
+          }
+          __syncwarp();
+          if (lane == 0 && st + STAGES < nstage) {
             async_proxy_fence();
-            bar_expect(bar, kStageW + kStageS);
-            bulk_g2s(stage_w, gw, kStageW, bar);
-            bulk_g2s(stage_s, gs, kStageS, bar);
+            fill(a, u0, u1, st + STAGES, st + STAGES + 1, slot);
           }
-          gw += kStageW;
-          gs += kStageS;
-          --to_request;
+          if (++slot == STAGES) { slot = 0; phase ^= 1; }
         }
-        if (++slot == STAGES) { slot = 0; phase ^= 1; }
       }
-    } else {
-#pragma unroll 1
-      for (int st = 0; st < nstage && ok; ++st) {
-        if (!bar_wait(&full[warp][slot], phase, kWaitLimit)) {
-          ok = false;
-          atomicExch(&g_w4_error, 1);
-          break;
-        }
-        const uint4* wp = reinterpret_cast<const uint4*>(ring_w + (size_t)slot * kStageW) + lane;
-        const unsigned short* sp = reinterpret_cast<const unsigned short*>(ring_s + (size_t)slot * kStageS) + r;
-        const int cnt = min(PERW, n_units - st * PERW);
-#pragma unroll 1
-        for (int i = 0; i < cnt; ++i) {
-          UnitOps o;
-          o.w0 = wp[i * 64];
-          o.w1 = wp[i * 64 + 32];
-          o.s_lo = sp[i * 16];
-          o.s_hi = sp[i * 16 + 8];
-          if (xfast && !(tail_k && g == G - 1)) {
-            const uint4* xp = reinterpret_cast<const uint4*>(xbase + (size_t)g * 256);
-            o.x0 = xp[0]; o.x1 = xp[1]; o.x2 = xp[8]; o.x3 = xp[9];
-          } else {
-            load_x_slow(o, a.x + (long)xrow * a.ldx, g, t, a.K);
-          }
-          unit_fma(acc, o);
-          ++g;
-          if (g == G || (st == nstage - 1 && i == cnt - 1)) close_segment();
-        }
-        __syncwarp();
-        if (lane == 0 && st + STAGES < nstage) {
-          async_proxy_fence();
-          fill(a, u0, u1, st + STAGES, st + STAGES + 1, slot);
-        }
-        if (++slot == STAGES) { slot = 0; phase ^= 1; }
-      }
-    }
+    };
+    if (a.xf16) stream(std::true_type{});
+    else stream(std::false_type{});
 
     // This warp's ring is empty: ask for the head of its slab of the next matrix now, so that the
     // copies run while the blocks finish this job and meet at the barrier.
@@ -794,8 +823,13 @@ int make_job(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg* cfg,
     a.xn_out = reinterpret_cast<bf16*>(nrm->xn_out);
     a.ldh = nrm->ldh; a.ldd = nrm->ldd; a.ldho = nrm->ldho; a.ldxo = nrm->ldxo;
     a.eps = nrm->eps;
+    a.xf16 = nrm->f16 ? 1 : 0;
   } else if (!p->x) {
     return QE_ERR_ARG;
+  } else if (p->x_f16) {
+    // fp16 activations are served by the vector path only: whole groups, aligned rows
+    if (p->K != p->Kp || !a.xvec) return QE_ERR_ARG;
+    a.xf16 = 1;
   }
   return 0;
 }
@@ -911,6 +945,7 @@ extern "C" int qe_w4_norm_rows(const qe_w4_norm* nrm, int N, int K, const qe_w4_
   if (!nrm || !cfg || N < 1 || N > QE_MAX_ROWS || K < 8 || (K & 7) || !nrm->h_in || !nrm->norm_w || !nrm->xn_out)
     return QE_ERR_ARG;
   if (!aligned16(nrm->h_in) || !aligned16(nrm->norm_w) || !aligned16(nrm->xn_out) || (nrm->ldh & 7) || (nrm->ldxo & 7) ||
+      (nrm->xn16_out && (!aligned16(nrm->xn16_out) || (nrm->ldx16 & 7))) ||
       (nrm->delta && (!aligned16(nrm->delta) || (nrm->ldd & 7))) ||
       (nrm->h_out && (!aligned16(nrm->h_out) || (nrm->ldho & 7))) || (nrm->tok && nrm->vocab < 1))
     return QE_ERR_ARG;
@@ -926,6 +961,11 @@ extern "C" int qe_w4_norm_rows(const qe_w4_norm* nrm, int N, int K, const qe_w4_
   a.xn_out = reinterpret_cast<bf16*>(nrm->xn_out);
   a.ldh = nrm->ldh; a.ldd = nrm->ldd; a.ldho = nrm->ldho; a.ldxo = nrm->ldxo;
   a.eps = nrm->eps;
+  if (nrm->xn16_out) {
+    a.xf16 = 1;
+    a.xn16_out = reinterpret_cast<__half*>(nrm->xn16_out);
+    a.ldx16 = nrm->ldx16;
+  }
   const bool pdl = cfg->pdl && pdl_launch_enabled() && pdl_trigger_enabled();
   const int nw = pick_geometry(*cfg).nw;  // the reduction order follows the CTA size of the GEMV
   cudaStream_t s = (cudaStream_t)stream;

@@ -31,6 +31,7 @@ which makes speculative output token-identical to plain greedy output.
 """
 from __future__ import annotations
 
+import gc
 import os
 from contextlib import contextmanager
 
@@ -106,7 +107,7 @@ class W4Linear:
     # GEMVs that follow one another without another kernel in between and runs them as one chain.
     @staticmethod
     def job(x, p, out):
-        return _w4.job(x, p.qw, p.scales, out, p.M, swiglu=p.gate_up)
+        return _w4.job(x, p.qw, p.scales, out, p.M, swiglu=p.gate_up, allow_f16_x=True)
 
     @staticmethod
     def job_partial(x, p, out32):
@@ -233,6 +234,8 @@ class _Residual:
             xn = keep_normed if keep_normed is not None else self.xn
             e._flush()
             kw = {"pdl": False} if ordered else {}
+            if e.f16:  # the rows also as fp16: input of the GEMV's fp16 flavour, like the fused launch
+                kw["xn16_out"] = e.xn16[:n]
             if self.tok is not None:
                 lin.norm_rows(e.embed, None, w, e.cfg.eps, xn, tok=self.tok, h_out=self.h, **kw)
                 self.tok = None
@@ -240,18 +243,19 @@ class _Residual:
                 lin.norm_rows(self.h, e.mo[:n] if self.owed else None, w, e.cfg.eps, xn,
                               h_out=self.h if self.owed else None, **kw)
             self.owed = False
-            e._gemv(lin.job(xn, p, out))
+            e._gemv(lin.job(e.xn16[:n] if e.f16 else xn, p, out))
             return
         if e.fuse and w4:
             if self.tok is not None:
                 j = lin.job_after_norm(e.embed, None, w, e.cfg.eps, p, out, tok=self.tok, h_out=self.h,
-                                       xn_out=keep_normed)
+                                       xn_out=keep_normed, f16=e.f16)
                 self.tok = None
             elif self.owed:
-                j = lin.job_after_norm(self.h, e.mo[:n], w, e.cfg.eps, p, out, h_out=self.spare, xn_out=keep_normed)
+                j = lin.job_after_norm(self.h, e.mo[:n], w, e.cfg.eps, p, out, h_out=self.spare, xn_out=keep_normed,
+                                       f16=e.f16)
                 self.h, self.spare = self.spare, self.h
             else:
-                j = lin.job_after_norm(self.h, None, w, e.cfg.eps, p, out, xn_out=keep_normed)
+                j = lin.job_after_norm(self.h, None, w, e.cfg.eps, p, out, xn_out=keep_normed, f16=e.f16)
             self.owed = False
             e._gemv(j, ordered=ordered)
             return
@@ -301,6 +305,7 @@ class Engine:
         self.layers = [dict(L) for L in weights["layers"]]
         self.has_mtp = bool(mtp and weights.get("mtp"))
         self.mtp = dict(weights["mtp"]) if self.has_mtp else None
+        self.f16 = self.fuse and os.environ.get("QE_F16", "1") == "1" and self._norms_fit_fp16()
         # caches beyond 8K positions: a multiple of 6 selects the tensor-core split kernel, sized
         # to one CTA per SM and row
         self.ATTN_SPLITS = attn_splits or (16 if max_len <= 8192 else 6 * -(-max(1, int(lib.qe_sm_count())) // cfg.hkv))
@@ -329,6 +334,15 @@ class Engine:
         weights = cache.load_cache(d, cfg, device=device, mtp=kw.get("mtp", True))
         return cls(cfg, weights, linear=linear, device=device, **kw)
 
+    def _norms_fit_fp16(self) -> bool:
+        """GEMVs behind an RMSNorm can take their input as fp16 (cheaper unpack, same bits, see
+        qe_w4_params::x_f16) when every normalised value fits: |x_i| <= sqrt(H) * |1 + w_i|."""
+        ws = [self.final_norm] + [L[k] for L in self.layers for k in ("in_norm", "post_norm")]
+        if self.mtp:
+            ws += [self.mtp[k] for k in ("in_norm", "post_norm", "norm")]
+        top = max(float((1.0 + w.float()).abs().max()) for w in ws)
+        return top * float(self.cfg.hidden) ** 0.5 < 60000.0
+
     # -- construction -------------------------------------------------------------------------
     def _make_draft_head(self, nv: int):
         """The first nv rows of the packed lm_head serve as the draft head (ids 0 .. nv - 1): tiles
@@ -356,6 +370,7 @@ class Engine:
         self.log = buf(self.max_len, dt=I32)
         # activations of a pass; the residual stream has two homes (see _Residual)
         self.h, self.h2, self.xn, self.mo, self.hid = (buf(N, H) for _ in range(5))
+        self.xn16 = buf(N, H, dt=torch.float16)  # normalised rows as fp16 (passes of several rows)
         width = max(c.gdn_proj_rows, c.attn_proj_rows)
         self.proj = buf(N, -(-width // 8) * 8)
         self.mix = buf(N, max(c.value_dim, c.hq * c.head_dim))
@@ -628,9 +643,19 @@ class Engine:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             count0 = launches[0]
-            # a process group's watchdog thread makes CUDA calls of its own during capture
-            with torch.cuda.graph(g, capture_error_mode="global" if self.tp is None else "thread_local"):
-                self._pass(n, mtp_rows, k, force)
+            # Python's cyclic collector must not run inside the capture: an engine that was dropped
+            # earlier (engines hold reference cycles) would have its graphs destroyed there, which
+            # CUDA refuses while a stream is capturing and which invalidates this capture.
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                # a process group's watchdog thread makes CUDA calls of its own during capture
+                with torch.cuda.graph(g, capture_error_mode="global" if self.tp is None else "thread_local"):
+                    self._pass(n, mtp_rows, k, force)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             torch.cuda.synchronize()
         finally:
             _C.set_gdn_early(False)

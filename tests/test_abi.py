@@ -49,5 +49,24 @@ def test_struct_layouts_match_header():
 
 def test_abi_version_and_plan_without_gpu():
     from qengine_b200 import _lib
-    assert _lib.lib.qe_abi_version() == 2
+    assert _lib.lib.qe_abi_version() == 3
     assert _lib.lib.qe_w4_auto_ksplit(5120, 17408, 1, 8) == 1
+
+
+def test_fp16_activation_preconditions_are_checked_at_the_boundary():
+    """qe_w4_gemv with x_f16 = 1 must refuse what its vector path cannot serve (unpadded K,
+    misaligned rows, odd strides) with QE_ERR_ARG (-22) before anything is launched."""
+    import ctypes as C
+    from qengine_b200 import _lib
+    buf = (C.c_char * 4096)()
+    base = (C.addressof(buf) + 255) & ~255
+    cfg = _lib.W4Cfg()
+    _lib.lib.qe_w4_cfg_default(C.byref(cfg))
+
+    def call(K, Kp, x, ldx):
+        p = _lib.W4Params(base, base, x, base, base, base, 16, K, 16, Kp, 1, ldx, 16, 0, 0, 1)
+        return _lib.lib.qe_w4_gemv(C.byref(p), C.byref(cfg), None)
+
+    assert call(200, 256, base, 256) == -22      # K != Kp
+    assert call(256, 256, base + 2, 256) == -22  # row start not 16-byte aligned
+    assert call(256, 256, base, 260) == -22      # stride not a multiple of 8 elements

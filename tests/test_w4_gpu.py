@@ -499,3 +499,55 @@ def test_chain_in_a_cuda_graph(api):
         # the trailing 2-job chain rewrites mo / act / h2 with the same values
         for a, b in zip([bits(t) for t in (h2, h3, act, proj, xn)], want[1:]):
             assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("M,K,gate_up", [(16480, H, False), (I, H, True), (4096, 512, False), (V // 8, H, False)])
+def test_fp16_activation_flavour(api, M, K, gate_up):
+    """GEMVs behind an RMSNorm may take their input as fp16 (qe_w4_params::x_f16, qe_w4_norm::f16):
+    the codes are then unpacked to fp16 with one shift per word. Normalised rows are numbers fp16
+    holds exactly, so the fp16 flavour must give the bits of the bf16 flavour; the fused launch and
+    norm_rows(xn16_out) + a GEMV on the fp16 rows must agree bit for bit for every row count."""
+    w4 = api["w4"]
+    p = api["qgu"](rand_w(M, K, seed=80), rand_w(M, K, seed=81)) if gate_up else api["q"](rand_w(M, K, seed=80))
+    g = torch.Generator(device=DEV).manual_seed(82)
+    h = torch.randn(8, K, generator=g, device=DEV).to(torch.bfloat16)
+    d = (torch.randn(8, K, generator=g, device=DEV) * 0.5).to(torch.bfloat16)
+    nw = (torch.randn(K, generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+    single = None
+    for N in (1, 2, 5, 8):
+        kw = dict(unroll=2) if N == 8 else {}
+        o_bf = torch.empty(N, M, dtype=torch.bfloat16, device=DEV)
+        o_h = torch.empty_like(o_bf)
+        xn_b = torch.empty(N, K, dtype=torch.bfloat16, device=DEV)
+        xn_h = torch.empty_like(xn_b)
+        w4.gemv_fused(h[:N], d[:N], nw, 1e-6, p.qw, p.scales, o_bf, M, xn_out=xn_b, swiglu=gate_up, **kw)
+        w4.gemv_fused(h[:N], d[:N], nw, 1e-6, p.qw, p.scales, o_h, M, xn_out=xn_h, swiglu=gate_up, f16=True, **kw)
+        assert torch.equal(bits(xn_b), bits(xn_h)), "the bf16 copy of the normed rows must not change"
+        # every normalised value here is far above 2^-17 in magnitude or zero: fp16 holds it exactly
+        assert torch.equal(bits(o_bf), bits(o_h)), f"N={N}: fp16 flavour differs from the bf16 flavour"
+        # the stand-alone norm + a GEMV on its fp16 rows
+        xn2 = torch.empty(N, K, dtype=torch.bfloat16, device=DEV)
+        x16 = torch.empty(N, K, dtype=torch.float16, device=DEV)
+        w4.norm_rows(h[:N], d[:N], nw, 1e-6, xn2, xn16_out=x16, **kw)
+        assert torch.equal(bits(xn2), bits(xn_b)) and torch.equal(x16.float(), xn_b.float())
+        o_r = torch.empty_like(o_bf)
+        w4.gemv_chain([w4.job(x16, p.qw, p.scales, o_r, M, swiglu=gate_up, allow_f16_x=True)], **kw)
+        assert torch.equal(bits(o_r), bits(o_h)), f"N={N}: norm_rows + fp16 GEMV differs from the fused launch"
+        if single is None:
+            single = bits(o_h[:1])
+        assert torch.equal(bits(o_h[:1]), single), f"N={N}: row 0 depends on N"
+    assert w4.ring_error() == 0
+
+
+def test_fp16_activations_are_not_part_of_the_reference_surface(api):
+    w4 = api["w4"]
+    p = api["q"](rand_w(32, 256, seed=83))
+    x16 = torch.randn(1, 256, device=DEV).half()
+    out = torch.empty(1, 32, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError):
+        w4.gemv(x16, p.qw, p.scales, out, 32)          # the reference rejects fp16 x; so does this mirror
+    with pytest.raises(RuntimeError):                   # rows that are not 16-byte aligned
+        w4.job(torch.randn(1, 264, device=DEV).half()[:, 4:260], p.qw, p.scales, out, 32, allow_f16_x=True)
+    p2 = api["q"](rand_w(32, 200, seed=84))              # K != Kp
+    with pytest.raises(RuntimeError):
+        w4.job(torch.randn(1, 200, device=DEV).half(), p2.qw, p2.scales, out, 32, allow_f16_x=True)
