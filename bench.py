@@ -319,28 +319,33 @@ def run_reference_gpu(a):
 def w4_sequence_timing(eng, n_rows, reps=10):
     """Every W4 GEMV of one token (all layers in order, then the lm_head) as one CUDA graph on the
     model's own weights: the dominant kernel timed alone, in situ shapes, nothing reused in L2.
-    Returns (ms per token, launches, algorithmic bytes)."""
+    The GEMVs that follow an RMSNorm in the engine (in_proj, gate_up, lm_head) take fp16 rows when
+    the engine runs them that way, the others bf16. Returns (ms per token, launches, bytes)."""
     import torch
+    from qengine_b200 import _w4
     cfg = eng.cfg
     lin = eng.linear
     H = cfg.hidden
     xs = {k: torch.randn(n_rows, k, device=eng.dev).to(torch.bfloat16) for k in
           {H, cfg.value_dim, cfg.hq * cfg.head_dim, cfg.inter}}
+    x16 = xs[H].to(torch.float16)
     outs, plan, nbytes = {}, [], 0
     for L in eng.layers:
         for key in ("in_proj", "out", "gate_up", "down"):
             p = L[key]
             outs.setdefault(p.M, torch.empty(n_rows, p.M, device=eng.dev, dtype=torch.bfloat16))
-            plan.append(p)
+            plan.append((p, key in ("in_proj", "gate_up")))
             nbytes += p.nbytes + n_rows * (p.K + p.M) * 2
     p = eng.lm_head
     outs.setdefault(p.M, torch.empty(n_rows, p.M, device=eng.dev, dtype=torch.bfloat16))
-    plan.append(p)
+    plan.append((p, True))
     nbytes += p.nbytes + n_rows * (p.K + p.M) * 2
+    f16 = bool(getattr(eng, "f16", False))
 
     def body():
-        for p in plan:
-            (lin.gate_up if p.gate_up else lin)(xs[p.K], p, outs[p.M])
+        for p, normed in plan:
+            x = x16 if (f16 and normed) else xs[p.K]
+            _w4.gemv_chain([lin.job(x, p, outs[p.M])], **lin.kw)
 
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
