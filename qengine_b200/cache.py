@@ -201,8 +201,9 @@ def pack_from_grid(Wq: torch.Tensor, rows_per_step: int = 2048):
     Per group the scale is recovered by trial: absmax is |code| * scale for some |code| in 1..8,
     seen through one bf16 rounding (up to four fp16 steps, plus the division), so the fp16 numbers within six steps
     of absmax / 8, absmax / 7, ... absmax / 1 are tried and the one whose grid reproduces the
-    stored bf16 values best is kept (ties: the finest grid). The reference tries / 7 and / 8 with
-    two steps; the wider search also recovers groups whose extreme codes are not in use. The codes
+    stored bf16 values best is kept (ties: the first in the order tried, which starts with the
+    reference's own candidates, / 7 and / 8 with two steps). The wider search also recovers groups
+    whose extreme codes are not in use or whose scale lies more than two steps off. The codes
     and scales found go straight into the packer, so the packed matrix holds exactly the grid
     point chosen (the reference has only a quantiser to pack with and builds an fp32 matrix that
     its quantiser maps onto the same grid point). Returns (W4Packed, {"exact_frac": fraction of
@@ -221,16 +222,20 @@ def pack_from_grid(Wq: torch.Tensor, rows_per_step: int = 2048):
         top = v.abs().amax(-1, keepdim=True)
         best_s = torch.ones_like(top)
         best_err = torch.full_like(top, float("inf"))
-        for full_scale in (8.0, 7.0, 6.0, 5.0, 4.0, 3.0, 2.0, 1.0):
+        # candidates in the reference's order first (absmax / 7 then / 8, two steps either way), so
+        # that a group it reproduces exactly gets the same scale here; then the wider search
+        trials = [(fs, st) for fs in (7.0, 8.0) for st in (-2, -1, 0, 1, 2)]
+        trials += [(fs, st) for fs in (7.0, 8.0) for st in (-6, -5, -4, -3, 3, 4, 5, 6)]
+        trials += [(fs, st) for fs in (6.0, 5.0, 4.0, 3.0, 2.0, 1.0) for st in range(-6, 7)]
+        for full_scale, step in trials:
             est = (top / full_scale).to(torch.float16)
-            for step in range(-6, 7):
-                s = (est.view(torch.int16) + step).view(torch.float16).float()
-                s = torch.where((s > 0) & torch.isfinite(s), s, torch.ones_like(s))
-                q = torch.clamp(torch.round(v / s), -8, 7)
-                err = ((q * s).to(torch.bfloat16).float() - v).abs().sum(-1, keepdim=True)
-                take = err < best_err
-                best_s = torch.where(take, s, best_s)
-                best_err = torch.where(take, err, best_err)
+            s = (est.view(torch.int16) + step).view(torch.float16).float()
+            s = torch.where((s > 0) & torch.isfinite(s), s, torch.ones_like(s))
+            q = torch.clamp(torch.round(v / s), -8, 7)
+            err = ((q * s).to(torch.bfloat16).float() - v).abs().sum(-1, keepdim=True)
+            take = err < best_err
+            best_s = torch.where(take, s, best_s)
+            best_err = torch.where(take, err, best_err)
         empty = top == 0
         best_s = torch.where(empty, torch.zeros_like(best_s), best_s)
         div = torch.where(empty, torch.ones_like(best_s), best_s)

@@ -87,3 +87,20 @@ def test_grid_repack_is_exact_on_grid_matrices():
     assert torch.equal(quant.dequantize_w4(p2).to(torch.bfloat16), Wg) and st2["exact_frac"] == 1.0
     with pytest.raises(ValueError):
         cache.pack_from_grid(torch.zeros(16, 100))
+
+
+def test_grid_repack_against_the_reference():
+    """tests/golden/grid_repack.pt holds the reference's prepare_from_grid on a GPTQ-style grid.
+    Same codes everywhere; the same scales wherever the reference reproduced the stored values
+    (its scale search is narrower and misses a few groups, which this one recovers exactly)."""
+    from pathlib import Path
+    g = torch.load(Path(__file__).resolve().parent / "golden" / "grid_repack.pt")
+    p, st = cache.pack_from_grid(g["grid"])
+    assert torch.equal(p.qw, g["qw"])
+    M, G = g["exact_groups"].shape
+    mine = p.scales.permute(0, 2, 1).reshape(M, G)
+    ref = g["scales"].permute(0, 2, 1).reshape(M, G)
+    ok = g["exact_groups"]
+    assert torch.equal(mine[ok], ref[ok])
+    assert 0.5 < float(ok.float().mean()) < 1.0 and st["exact_frac"] == 1.0
+    assert torch.equal(quant.dequantize_w4(p).to(torch.bfloat16), g["grid"])
