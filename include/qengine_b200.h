@@ -90,7 +90,8 @@ int qe_argmax_merge(const float* vals, const int* idx, int nparts, int rows, int
  *   qe_tp_exchange_norm: part = this rank's fp32 partial rows [rows, H] (stride ldp) of a matrix
  *     split along K. One kernel stores them into every peer's block, collects the peers' rows and
  *     computes x = bf16(x + bf16(sum over ranks, ascending)), out = RMSNorm1p(x) * (1 + w): the
- *     all-reduce and qe_rmsnorm1p in one launch, bit-identical on every rank.
+ *     all-reduce and qe_rmsnorm1p in one launch, bit-identical on every rank. out16 (optional,
+ *     stride ld16): the same rows as fp16, the input of a qe_w4_gemv with x_f16 = 1.
  *   qe_tp_exchange_argmax: (value, index) candidates per row from qe_argmax_v are exchanged and
  *     merged with the argmax ordering rule; out[r] = greedy token over the whole vocabulary.
  * All ranks must issue the same sequence of exchanges with the same row counts. Waits are bounded
@@ -107,8 +108,8 @@ int qe_tp_unmap(void* ptr);
 int qe_tp_comm_create(void* const* blocks, int rank, int world, int H, void** comm);
 int qe_tp_comm_destroy(void* comm);
 int qe_tp_set_timeout_ms(void* comm, long ms);
-int qe_tp_exchange_norm(void* comm, void* x, const float* part, const void* w, void* out, int rows,
-                        long ldx, long ldp, long ldo, float eps, void* stream);
+int qe_tp_exchange_norm(void* comm, void* x, const float* part, const void* w, void* out, void* out16,
+                        int rows, long ldx, long ldp, long ldo, long ld16, float eps, void* stream);
 int qe_tp_exchange_argmax(void* comm, const float* cand_v, const int* cand_i, int rows, int* out,
                           void* stream);
 int qe_tp_error(void* comm, int* info4);

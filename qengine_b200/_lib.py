@@ -61,7 +61,7 @@ SIGNATURES = {
     "qe_tp_comm_create": (c_int, [P, c_int, c_int, c_int, P]),
     "qe_tp_comm_destroy": (c_int, [P]),
     "qe_tp_set_timeout_ms": (c_int, [P, c_long]),
-    "qe_tp_exchange_norm": (c_int, [P, P, P, P, P, c_int, c_long, c_long, c_long, c_float, P]),
+    "qe_tp_exchange_norm": (c_int, [P, P, P, P, P, P, c_int, c_long, c_long, c_long, c_long, c_float, P]),
     "qe_tp_exchange_argmax": (c_int, [P, P, P, c_int, P, P]),
     "qe_tp_error": (c_int, [P, P]),
     "qe_tp_clear_error": (c_int, [P]),

@@ -162,8 +162,8 @@ tp_norm_kernel(bf16* x, const float* part, int nparts, const bf16* w, bf16* out,
 constexpr int kCX = 8;  // CTAs per row = cluster size (portable maximum)
 
 __global__ void __launch_bounds__(1024)
-tp_xnorm_kernel(TpView tv, bf16* x, const float* part, const bf16* w, bf16* out, int H, int PK, long ldx,
-                long ldp, long ldo, float eps) {
+tp_xnorm_kernel(TpView tv, bf16* x, const float* part, const bf16* w, bf16* out, __half* out16, int H, int PK,
+                long ldx, long ldp, long ldo, long ld16, float eps) {
   dep_release();
   dep_wait();
   cg::cluster_group cluster = cg::this_cluster();
@@ -260,7 +260,12 @@ tp_xnorm_kernel(TpView tv, bf16* x, const float* part, const bf16* w, bf16* out,
     widen8(__ldg(reinterpret_cast<const uint4*>(w) + i), g);
 #pragma unroll
     for (int k = 0; k < 8; ++k) y[k] = v[k] * inv * (1.0f + g[k]);
-    reinterpret_cast<uint4*>(out + (long)row * ldo)[i] = narrow8(y);
+    const uint4 q = narrow8(y);
+    reinterpret_cast<uint4*>(out + (long)row * ldo)[i] = q;
+    if (out16) {  // the same bf16-rounded numbers as fp16: input of the GEMV's fp16 flavour
+      widen8(q, y);
+      reinterpret_cast<uint4*>(out16 + (long)row * ld16)[i] = half8(y);
+    }
   }
   // every CTA of the cluster read the sequence number before the cluster barrier above
   if (cs == 0 && tid == 0) *(volatile int*)(hdr + row) = (int)e;
@@ -412,9 +417,9 @@ extern "C" int qe_tp_set_timeout_ms(void* comm, long ms) {
   return 0;
 }
 
-extern "C" int qe_tp_exchange_norm(void* comm, void* x, const float* part, const void* w, void* out, int rows,
-                                   long ldx, long ldp, long ldo, float eps, void* stream) {
-  if (!comm) return QE_ERR_ARG;
+extern "C" int qe_tp_exchange_norm(void* comm, void* x, const float* part, const void* w, void* out, void* out16,
+                                   int rows, long ldx, long ldp, long ldo, long ld16, float eps, void* stream) {
+  if (!comm || (out16 && (!aligned16(out16) || ld16 % 8))) return QE_ERR_ARG;
   const Comm* c = static_cast<Comm*>(comm);
   const int H = c->v.H, npk = H / 8;
   if (rows < 1 || rows > kRows || ldx % 8 || ldo % 8 || ldp % 4 || !aligned16(x) || !aligned16(out) ||
@@ -438,8 +443,8 @@ extern "C" int qe_tp_exchange_norm(void* comm, void* x, const float* part, const
   at[1].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = at;
   lc.numAttrs = pdl_on() ? 2 : 1;
-  return (int)cudaLaunchKernelEx(&lc, tp_xnorm_kernel, c->v, (bf16*)x, part, (const bf16*)w, (bf16*)out, H, PK, ldx,
-                                 ldp, ldo, eps);
+  return (int)cudaLaunchKernelEx(&lc, tp_xnorm_kernel, c->v, (bf16*)x, part, (const bf16*)w, (bf16*)out,
+                                 (__half*)out16, H, PK, ldx, ldp, ldo, ld16, eps);
 }
 
 extern "C" int qe_tp_exchange_argmax(void* comm, const float* cand_v, const int* cand_i, int rows, int* out,

@@ -209,7 +209,9 @@ class _Residual:
         self.h.zero_()
         self.owe(x, p, lin)
 
-    def _norm(self, w, out):
+    def _norm(self, w, out, out16=None):
+        """out = norm(h + owed). Returns True when out16 was filled too (only the exchange kernel of
+        the tensor-parallel path writes the fp16 copy)."""
         e, n = self.e, self.n
         K = e.K  # kernels other than the W4 GEMV: the queue of GEMVs is flushed first
         if not self.owed:
@@ -220,8 +222,11 @@ class _Residual:
             K.rmsnorm1p_parts(self.h, e.parts[n], w, out, e.cfg.eps)
         else:
             e._flush()
-            e.tp.exchange_norm(self.h, e.part32[:n], w, out, e.cfg.eps)
+            e.tp.exchange_norm(self.h, e.part32[:n], w, out, e.cfg.eps, out16=out16)
+            self.owed = False
+            return out16 is not None
         self.owed = False
+        return False
 
     def through(self, w, p, out, lin, keep_normed=None, ordered=False):
         """out = p(norm(h + owed)); keep_normed optionally receives the normed rows. ordered: this
@@ -260,9 +265,9 @@ class _Residual:
             e._gemv(j, ordered=ordered)
             return
         xn = keep_normed if keep_normed is not None else self.xn
-        self._norm(w, xn)
+        as16 = self._norm(w, xn, e.xn16[:n] if (w4 and e.tp_f16) else None)
         if w4:
-            e._gemv(lin.job(xn, p, out))
+            e._gemv(lin.job(e.xn16[:n] if as16 else xn, p, out))
         else:
             e._flush()
             lin(xn, p, out)
@@ -305,7 +310,10 @@ class Engine:
         self.layers = [dict(L) for L in weights["layers"]]
         self.has_mtp = bool(mtp and weights.get("mtp"))
         self.mtp = dict(weights["mtp"]) if self.has_mtp else None
-        self.f16 = self.fuse and os.environ.get("QE_F16", "1") == "1" and self._norms_fit_fp16()
+        fits = os.environ.get("QE_F16", "1") == "1" and self._norms_fit_fp16()
+        self.f16 = self.fuse and fits
+        # tensor parallel over own exchange kernels: the exchange + norm writes the fp16 rows
+        self.tp_f16 = fits and tp is not None and tp.transport == "peer"
         # caches beyond 8K positions: a multiple of 6 selects the tensor-core split kernel, sized
         # to one CTA per SM and row
         self.ATTN_SPLITS = attn_splits or (16 if max_len <= 8192 else 6 * -(-max(1, int(lib.qe_sm_count())) // cfg.hkv))

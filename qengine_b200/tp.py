@@ -221,13 +221,17 @@ class TPGroup:
             return None
         return {"error": e, "late_rank": info[1], "row": info[2], "kind": "argmax" if info[3] else "norm"}
 
-    def exchange_norm(self, x, part, w, out, eps):
-        """x += bf16(sum over ranks of part); out = rmsnorm1p(x) -- one launch."""
+    def exchange_norm(self, x, part, w, out, eps, out16=None):
+        """x += bf16(sum over ranks of part); out = rmsnorm1p(x) -- one launch. out16 (fp16, same
+        shape, optional) receives the normed rows as fp16 as well."""
         from ._lib import check, lib
         assert part.dtype == torch.float32 and part.stride(1) == 1 and x.stride(1) == 1 and out.stride(1) == 1
         assert x.shape == part.shape == out.shape
+        assert out16 is None or (out16.dtype == torch.float16 and out16.shape == out.shape and out16.stride(1) == 1)
         check(lib.qe_tp_exchange_norm(self.comm, x.data_ptr(), part.data_ptr(), w.data_ptr(), out.data_ptr(),
-                                      x.shape[0], x.stride(0), part.stride(0), out.stride(0), float(eps),
+                                      out16.data_ptr() if out16 is not None else None,
+                                      x.shape[0], x.stride(0), part.stride(0), out.stride(0),
+                                      out16.stride(0) if out16 is not None else 0, float(eps),
                                       torch.cuda.current_stream().cuda_stream), "tp exchange_norm")
 
     def exchange_argmax(self, cand_v, cand_i, rows, out):

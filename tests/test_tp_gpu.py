@@ -175,9 +175,12 @@ def test_exchange_norm_against_prefilled_peers(H, world, rank):
                     sl[r, :, 0] = parts[src][r].view(torch.int32)
                     sl[r, :, 1] = seqs[r]
             torch.cuda.synchronize()
+            out16 = torch.empty(n, H, dtype=torch.float16, device="cuda")
             assert lib.qe_tp_exchange_norm(fw.comm, x.data_ptr(), parts[rank].data_ptr(), w.data_ptr(), out.data_ptr(),
-                                           n, x.stride(0), parts[rank].stride(0), out.stride(0), 1e-6, s) == 0
+                                           out16.data_ptr(), n, x.stride(0), parts[rank].stride(0), out.stride(0),
+                                           out16.stride(0), 1e-6, s) == 0
             assert fw.error()[0] == 0
+            assert torch.equal(out16.float(), out.float()), "the fp16 copy of the normed rows"
             xr, ref = _norm_ref(x0, parts, w)
             assert torch.equal(x, xr)
             # the norm over gathered parts (library-collective transport) sums the squares in another
@@ -245,7 +248,7 @@ def test_exchange_wait_runs_out_and_reports_the_late_rank():
         part = torch.ones(1, H, device="cuda")
         w = torch.zeros(H, device="cuda", dtype=BF16)
         out = torch.empty_like(x)
-        args = (fw.comm, x.data_ptr(), part.data_ptr(), w.data_ptr(), out.data_ptr(), 1, H, H, H, 1e-6, s)
+        args = (fw.comm, x.data_ptr(), part.data_ptr(), w.data_ptr(), out.data_ptr(), None, 1, H, H, H, 0, 1e-6, s)
         t0 = time.perf_counter()
         assert lib.qe_tp_exchange_norm(*args) == 0
         err, info = fw.error()
