@@ -104,3 +104,47 @@ def test_grid_repack_against_the_reference():
     assert torch.equal(mine[ok], ref[ok])
     assert 0.5 < float(ok.float().mean()) < 1.0 and st["exact_frac"] == 1.0
     assert torch.equal(quant.dequantize_w4(p).to(torch.bfloat16), g["grid"])
+
+
+def test_files_pickled_with_the_reference_class_load_here(tmp_path):
+    """The other direction of the interchange: layer files whose matrices are instances of the
+    reference's own `qengine.quant.W4Packed` (as its engine writes them, python/qengine/engine.py:
+    224-229) load into this package's class. Needs the unmodified copy of the reference package
+    that baseline/build_ref.py lays out (its quant module has no CUDA dependency)."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    ref_pkg = Path(__file__).resolve().parents[1] / "baseline" / "_ref" / "shim" / "python"
+    if not (ref_pkg / "qengine" / "quant.py").exists():
+        pytest.skip("baseline/_ref is not built")
+    cfg = tiny_config()
+    W = build_model(cfg, seed=9)
+    d = cache.save_cache(tmp_path / "ours", W)
+    # re-save every file from a separate interpreter in which qengine.quant is the reference's module
+    script = f"""
+import sys, torch
+sys.path.insert(0, {str(ref_pkg)!r})
+import importlib.util, types
+pkg = types.ModuleType("qengine"); pkg.__path__ = [{str(ref_pkg / 'qengine')!r}]; sys.modules["qengine"] = pkg
+spec = importlib.util.spec_from_file_location("qengine.quant", {str(ref_pkg / 'qengine' / 'quant.py')!r})
+m = importlib.util.module_from_spec(spec); sys.modules["qengine.quant"] = m; spec.loader.exec_module(m)
+from pathlib import Path
+src, dst = Path({str(d)!r}), Path({str(tmp_path / 'theirs')!r}); dst.mkdir()
+n = 0
+for f in sorted(src.glob("*.pt")):
+    obj = torch.load(f, weights_only=False)
+    def count(o):
+        global n
+        if isinstance(o, m.W4Packed): n += 1
+        elif isinstance(o, dict): [count(v) for v in o.values()]
+    count(obj)
+    torch.save(obj, dst / f.name)
+(dst / "COMPLETE").write_text("w4-rtn-g128-v1\\n")
+print(n)
+"""
+    r = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert int(r.stdout.strip()) == 1 + 4 * cfg.layers + 5   # lm_head, 4 per layer, 5 in the MTP layer
+    back = cache.load_cache(tmp_path / "theirs", cfg)
+    for k in ("embed", "final_norm", "lm_head", "layers", "mtp"):
+        assert _same(W[k], back[k]), k
