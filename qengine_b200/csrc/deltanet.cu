@@ -179,10 +179,6 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
     row_update(k_s[t], nullptr, v_s[t][lane], gate_s[t][0], gate_s[t][1], 0.f, buf, false);
     buf ^= 1;
   }
-  // This CTA is done reading the checkpoints of the previous pass. The CTA with cs == 0 overwrites
-  // st_k / st_g in step 2c while its siblings may still be replaying from them: split cluster
-  // barrier, arrive here, wait just before 2c (the conv and l2norm work in between hides it).
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   if (pend > 0) {
 #pragma unroll
     for (int i = 0; i < RP; ++i) Sj[(size_t)(warp * RP + i) * D] = s[i];
@@ -273,19 +269,6 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
   }
   __syncthreads();
 
-  // ---- 2c. checkpoint every row for the next pass (k, gates: one CTA per head; v: own slice) ----
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // siblings finished their replay
-  for (int t = 0; t < n; ++t) {
-    if (cs == 0) {
-      for (int i = tid; i < D; i += NT) a.st_k[((size_t)t * a.Hv + j) * D + i] = k_s[t][i];
-      if (tid == 0) {
-        a.st_g[(t * a.Hv + j) * 2] = gate_s[t][0];
-        a.st_g[(t * a.Hv + j) * 2 + 1] = gate_s[t][1];
-      }
-    }
-    if (tid < kCols) a.st_v[((size_t)t * a.Hv + j) * D + c0 + tid] = v_s[t][tid];
-  }
-
   // ---- 2d. the recurrence, row by row, on the register copy of S ----
   for (int t = 0; t < n; ++t) {
     const float o = row_update(k_s[t], q_s[t], v_s[t][lane], gate_s[t][0], gate_s[t][1], kq_s[t], buf, true);
@@ -314,6 +297,20 @@ __global__ void __launch_bounds__(kWarps * 32) gdn_cluster_kernel(const GdnArgs 
   }
   // no second barrier: nobody reads remote shared memory after the one above, and every remote
   // store was issued before it
+  // ---- 2f. checkpoint every row for the next pass (k, gates: one CTA per head; v: own slice).
+  // Last, behind the output: nothing in this pass waits for these stores. The CTA with cs == 0
+  // overwrites st_k / st_g, which its siblings read while replaying: the cluster barrier of 2e
+  // lies in between, and every CTA passes it only after its replay ----
+  for (int t = 0; t < n; ++t) {
+    if (cs == 0) {
+      for (int i = tid; i < D; i += NT) a.st_k[((size_t)t * a.Hv + j) * D + i] = k_s[t][i];
+      if (tid == 0) {
+        a.st_g[(t * a.Hv + j) * 2] = gate_s[t][0];
+        a.st_g[(t * a.Hv + j) * 2 + 1] = gate_s[t][1];
+      }
+    }
+    if (tid < kCols) a.st_v[((size_t)t * a.Hv + j) * D + c0 + tid] = v_s[t][tid];
+  }
 }
 
 // Off by default: the early state load assumes that no launch on the same state is still in
