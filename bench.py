@@ -21,6 +21,7 @@ sm_100a by baseline/build_ref.py, on the same synthetic model, and this library 
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import re
@@ -580,6 +581,7 @@ def run_ours(a):
                 "tok_s": (n_new - 1) / d, "tokens_per_cycle": st["tokens_per_cycle"],
                 "ms_per_cycle": d * 1e3 / max(1, st["cycles"]), "identical_to_plain": out == gen}
         del eng_d
+        gc.collect()  # engines hold reference cycles; their graphs and buffers go with the collection
         torch.cuda.empty_cache()
     # ---- the draft layer's fc + in_proj + o_proj pinned in L2 for the draft phase (A/B) ---------
     if not a.no_mtp and world == 1:
@@ -596,6 +598,7 @@ def run_ours(a):
                 "without_window_ms_per_cycle": mtp[label]["ms_per_cycle"]}
         eng_p.pin_mtp_l2(False)
         del eng_p
+        gc.collect()
         torch.cuda.empty_cache()
     exchange_us = exchange_timing(eng) if world > 1 else None
     parity = parity_early
@@ -626,6 +629,7 @@ def run_ours(a):
     longctx = {}
     if a.context > 0:
         del eng
+        gc.collect()
         torch.cuda.empty_cache()
         n_long = min(n_new, 256)
         kw = dict(max_len=a.context + P + n_long + 64, device=dev)
