@@ -267,6 +267,8 @@ def test_attention_at_the_long_context_operating_point(C):
     # every row count (1..8 rows = 1..4 warps per stream) well inside one split length
     (24, 4, 12, 1, 700, 9), (24, 4, 12, 2, 700, 9), (24, 4, 12, 3, 700, 9), (24, 4, 12, 4, 700, 9),
     (24, 4, 12, 5, 700, 9), (24, 4, 12, 6, 700, 9), (24, 4, 12, 7, 700, 9), (24, 4, 12, 8, 700, 9),
+    # eight query heads per KV head: 3..8 rows need three or four tiles (four warps per stream)
+    (16, 2, 12, 8, 700, 9), (16, 2, 12, 7, 96 * 2 - 3, 5), (8, 1, 6, 5, 300, 2), (16, 2, 222, 6, 9000, 11),
     # rows on both sides of 4,096 positions, where the probabilities stop being carried as two bf16
     (24, 4, 12, 5, 4093, 8), (8, 2, 24, 2, 4095, 3),
     # rows that run past the end of the cache see the whole cache
