@@ -536,6 +536,13 @@ def test_fp16_activation_flavour(api, M, K, gate_up):
         if single is None:
             single = bits(o_h[:1])
         assert torch.equal(bits(o_h[:1]), single), f"N={N}: row 0 depends on N"
+    # other block sizes and rings: each must agree with its own bf16 flavour
+    for kw in (dict(warps=8), dict(variant=2), dict(variant=1), dict(unroll=1), dict(min_units=6), dict(pdl=False)):
+        o_bf = torch.empty(3, M, dtype=torch.bfloat16, device=DEV)
+        o_h = torch.empty_like(o_bf)
+        w4.gemv_fused(h[:3], d[:3], nw, 1e-6, p.qw, p.scales, o_bf, M, swiglu=gate_up, **kw)
+        w4.gemv_fused(h[:3], d[:3], nw, 1e-6, p.qw, p.scales, o_h, M, swiglu=gate_up, f16=True, **kw)
+        assert torch.equal(bits(o_bf), bits(o_h)), f"{kw}: fp16 flavour differs from the bf16 flavour"
     assert w4.ring_error() == 0
 
 
