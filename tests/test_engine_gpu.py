@@ -313,3 +313,30 @@ def test_bf16_lm_head_backend(setup):
     assert cos.min() > 0.9999, cos.min()
     plain = eng.generate(prompt, 48)
     assert eng.generate_spec(prompt, 48, 4) == plain
+
+
+def test_norm_weights_too_large_for_fp16_rows_keep_bf16(setup):
+    """GEMVs behind an RMSNorm take fp16 rows only while sqrt(H) * |1 + w| fits fp16 for every
+    norm weight (Engine._norms_fit_fp16); one outsized weight sends the whole engine back to bf16
+    rows, and both engines are self-consistent."""
+    cfg, Wp, base = setup
+    assert base.f16
+    prompt = torch.load(G / "greedy.pt")["prompt"]
+    Wb = dict(Wp)
+    Wb["final_norm"] = Wp["final_norm"].clone()
+    Wb["final_norm"][3] = 5000.0
+    eng = _new_engine(cfg, Wb)
+    assert not eng.f16
+    plain = eng.generate(prompt, 40)
+    assert eng.generate_spec(prompt, 40, 4) == plain
+    # and the bf16-row engine on the unmodified weights decodes what the fp16-row engine decodes
+    import os
+    os.environ["QE_F16"] = "0"
+    try:
+        bf = _new_engine(cfg, Wp)
+    finally:
+        del os.environ["QE_F16"]
+    assert not bf.f16
+    assert bf.generate(prompt, 60) == base.generate(prompt, 60)
+    a, b = bf.sequence_logits(prompt[:16]), base.sequence_logits(prompt[:16])
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16)), "fp16 rows changed logit bits"
