@@ -331,6 +331,18 @@ int qe_w4_gemv_chain(const qe_w4_params* const* p, const qe_w4_norm* const* nrm,
 #define QE_ERR_SCRATCH (-28)
 int qe_w4_gemv_static(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
 
+/* Has no counterpart in the reference, which prefills in passes of at most 8 rows through its GEMV
+ * (python/qengine/engine.py:558-573). The same product as qe_w4_gemv for p->N = 1..QE_MAX_GEMM_ROWS
+ * activation rows with the matrix streamed from HBM once for all of them: a prefill pass of 64
+ * rows reads the weights once instead of eight times. Same wire format, epilogues and out_f32 as
+ * qe_w4_gemv; the arithmetic per 1 KB unit is the GEMV's, the order in which the units of a tile
+ * are added is not, so a row agrees with qe_w4_gemv to fp32 rounding (not bit for bit); results are
+ * bit-identical run to run and row r does not depend on N. Needs K == Kp, Kp / 128 even, bf16 x
+ * with 16-byte aligned rows and ldx % 8 == 0 (QE_ERR_ARG otherwise); p->ws, p->counters and
+ * p->x_f16 (must be 0) are not used. Only cfg->pdl is read. */
+#define QE_MAX_GEMM_ROWS 64
+int qe_w4_gemm(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
+
 /* The weight rings are fed by bulk copies whose completion waits are bounded; this returns the
  * sticky error word those waits set on expiry (0 = none) and qe_w4_clear_error resets it. Both
  * synchronise with the device. No counterpart in the reference. */

@@ -262,8 +262,8 @@ def norm_rows(h_in, delta, norm_w, eps, xn_out, h_out=None, tok=None, xn16_out=N
     bf = torch.bfloat16
     _req(xn_out.is_cuda and xn_out.dtype == bf and xn_out.dim() == 2 and xn_out.stride(1) == 1, "xn_out bf16 [N, K]")
     N, K = xn_out.shape
-    _req(1 <= N <= 8 and K % 8 == 0 and norm_w.dtype == bf and norm_w.numel() == K and norm_w.is_contiguous(),
-         "N in 1..8, K % 8 == 0, norm_w [K]")
+    _req(1 <= N <= MAX_GEMM_ROWS and K % 8 == 0 and norm_w.dtype == bf and norm_w.numel() == K and
+         norm_w.is_contiguous(), "N in 1..64, K % 8 == 0, norm_w [K]")
     _req(h_in.is_cuda and h_in.dtype == bf and h_in.dim() == 2 and h_in.stride(1) == 1 and h_in.size(1) == K, "h_in [*, K]")
     nrm = W4Norm()
     nrm.h_in, nrm.ldh, nrm.norm_w, nrm.eps = h_in.data_ptr(), h_in.stride(0), norm_w.data_ptr(), float(eps)
@@ -286,6 +286,38 @@ def norm_rows(h_in, delta, norm_w, eps, xn_out, h_out=None, tok=None, xn16_out=N
         nrm.xn16_out, nrm.ldx16 = xn16_out.data_ptr(), xn16_out.stride(0)
     cfg = _cfg(warps, unroll, ksplit, pdl, variant, mode, blocks_per_sm, min_units)
     check(lib.qe_w4_norm_rows(C.byref(nrm), N, K, C.byref(cfg), torch.cuda.current_stream().cuda_stream), "norm_rows")
+
+
+MAX_GEMM_ROWS = 64
+
+
+def gemm(x, qw, scales, out, M, swiglu=False, pdl=True, variant=0):
+    """Not in the reference (which prefills in passes of at most 8 rows through `gemv`): the same
+    product for N = 1..64 rows with the matrix read from HBM once for all of them
+    (qe_w4_gemm). out may be bf16 or, without SwiGLU, fp32 (unrounded sums). Needs K == Kp and
+    16-byte aligned rows of x. A row agrees with `gemv` to fp32 rounding, not bit for bit (the
+    groups of a tile are added in another order); results do not depend on N. variant 0: tcgen05
+    with the accumulator in tensor memory; variant 1: the mma.sync kernel (needs Kp / 128 even)."""
+    for t in (x, qw, scales, out):
+        _req(isinstance(t, torch.Tensor) and t.is_cuda, "CUDA tensors")
+    out_f32 = out.dtype == torch.float32 and not swiglu
+    _req(x.dtype == torch.bfloat16 and (out.dtype == torch.bfloat16 or out_f32), "x bf16, out bf16 (or fp32 sums)")
+    Mp, Kp = _packed(qw, scales)
+    _req(x.dim() == 2 and out.dim() == 2 and x.stride(1) == 1 and out.stride(1) == 1, "x [N,K], out [N,M] rows")
+    N, K, M = x.size(0), x.size(1), int(M)
+    _req(1 <= N <= MAX_GEMM_ROWS and out.size(0) == N and out.size(1) == M, "N in 1..64 and out [N, M]")
+    _req(K == Kp, "gemm needs K == Kp")
+    _req(variant in (0, 1) and (variant == 0 or (Kp // 128) % 2 == 0), "variant 1 needs an even number of 128-k groups")
+    _req(x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "gemm needs 16-byte aligned rows of x")
+    _req((Mp // 2 - 8 < M <= Mp // 2) if swiglu else (Mp - 16 < M <= Mp), "out width must match packed rows")
+    _req(x.data_ptr() != out.data_ptr(), "in-place not supported")
+    p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None, M, K, Mp, Kp, N,
+                 x.stride(0), out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, int(out_f32), 0)
+    cfg = W4Cfg(0, 0, 0, int(bool(pdl)), int(variant), -1, 0, 4)
+    code = lib.qe_w4_gemm(C.byref(p), C.byref(cfg), torch.cuda.current_stream().cuda_stream)
+    _req(code != -22, "gemm: argument combination not supported by the kernel")
+    _req(code == 0, f"gemm launch failed: CUDA error {code}")
+    launches[0] += 1
 
 
 def auto_ksplit(Mp, Kp, N, warps=8):

@@ -55,6 +55,9 @@
 #include "w4_dev.cuh"
 
 namespace qb {
+// error word of the GEMM's bounded waits (w4_gemm.cu), reported together with the GEMV's
+int gemm_error_read();
+int gemm_error_clear();
 namespace {
 
 using namespace w4;
@@ -200,7 +203,7 @@ __device__ __forceinline__ void norm_prologue(const GemvArgs& a, unsigned char* 
     for (int i = 0; i < RB; ++i) {
       if (r0 + i < N) {
         const float w = warp_allsum(ss[i]);
-        if (lane == 0) s_red[r0 + i][warp] = w;
+        if (lane == 0) s_red[r0 + i - r_lo][warp] = w;
       }
     }
   }
@@ -214,7 +217,7 @@ __device__ __forceinline__ void norm_prologue(const GemvArgs& a, unsigned char* 
       if (r0 + i < N) {
         float tot = 0.f;
 #pragma unroll
-        for (int w2 = 0; w2 < NW; ++w2) tot += s_red[r0 + i][w2];
+        for (int w2 = 0; w2 < NW; ++w2) tot += s_red[r0 + i - r_lo][w2];
         inv[i] = rsqrtf(tot / (float)a.K + a.eps);
       }
     }
@@ -924,12 +927,16 @@ extern "C" int qe_w4_ring_error(void) {
   int v = 0;
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;
   if (cudaMemcpyFromSymbol(&v, g_w4_error, sizeof(int)) != cudaSuccess) return -1;
-  return v;
+  const int m = gemm_error_read();
+  if (m < 0) return -1;
+  return v | (m ? 16 * m : 0);
 }
 
 extern "C" int qe_w4_clear_error(void) {
   const int z = 0;
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  const int rc = gemm_error_clear();
+  if (rc) return rc;
   return (int)cudaMemcpyToSymbol(g_w4_error, &z, sizeof(int));
 }
 
@@ -942,7 +949,7 @@ extern "C" int qe_w4_gemv_ex(const qe_w4_params* p, const qe_w4_norm* nrm, const
 }
 
 extern "C" int qe_w4_norm_rows(const qe_w4_norm* nrm, int N, int K, const qe_w4_cfg* cfg, void* stream) {
-  if (!nrm || !cfg || N < 1 || N > QE_MAX_ROWS || K < 8 || (K & 7) || !nrm->h_in || !nrm->norm_w || !nrm->xn_out)
+  if (!nrm || !cfg || N < 1 || N > QE_MAX_GEMM_ROWS || K < 8 || (K & 7) || !nrm->h_in || !nrm->norm_w || !nrm->xn_out)
     return QE_ERR_ARG;
   if (!aligned16(nrm->h_in) || !aligned16(nrm->norm_w) || !aligned16(nrm->xn_out) || (nrm->ldh & 7) || (nrm->ldxo & 7) ||
       (nrm->xn16_out && (!aligned16(nrm->xn16_out) || (nrm->ldx16 & 7))) ||

@@ -281,7 +281,7 @@ class Engine:
 
     def __init__(self, cfg: Config, weights: dict, max_len: int = 4096, linear=None, device="cuda",
                  mtp: bool = True, attn_splits: int | None = None, draft_vocab: int | None = None, tp=None,
-                 fuse: bool | None = None, chain: bool | None = None):
+                 fuse: bool | None = None, chain: bool | None = None, wide_prefill: bool = False):
         """weights: dict in the fused layout (qengine_b200.synth.build_model), already on `device`.
         tp: a qengine_b200.tp.TPGroup for tensor parallelism; `cfg` then still describes the whole
         model and `weights` is this rank's shard (qengine_b200.tp.shard_model).
@@ -293,7 +293,11 @@ class Engine:
         chain: launch runs of consecutive W4 GEMVs as one cooperative kernel with grid barriers
         (default off, QE_CHAIN=1 turns it on: measured slower than one launch per GEMV under
         programmatic dependent launch, whose hand-over costs about 1 us against 2.5 us for the
-        barrier)."""
+        barrier).
+        wide_prefill: feed prompts in passes of up to 64 rows through the tensor-memory GEMM
+        (`_w4.gemm`, every matrix read once per pass) instead of 8 rows through the GEMV; see
+        `prefill`. Off by default: the reference prefills 8 rows at a time, and only that way is a
+        chunked prefill bit-identical to feeding the prompt token by token."""
         self.tp, self.vocab_full, self.vocab_base = tp, cfg.vocab, 0
         if tp is not None:
             from .tp import local_config
@@ -328,6 +332,8 @@ class Engine:
         self.force_a = -1       # forced acceptance length of verify passes (< 0: off)
         self.truth = torch.zeros(1, dtype=I32, device=self.dev)
         self.l2_win = None      # (base, bytes) of the persisting window around the draft phase
+        self.wide_prefill = bool(wide_prefill)
+        self.wb = None          # buffers of the wide prefill passes (allocated on first use)
 
     @classmethod
     def from_cache(cls, path, cache_dir, device="cuda", linear=None, **kw):
@@ -682,9 +688,10 @@ class Engine:
     def _split(seq, size):
         return [seq[i:i + size] for i in range(0, len(seq), size)]
 
-    def _prefill_keys(self, P, mtp, k, chunk=NMAX):
-        """Graph keys a prompt of P tokens needs: full chunks, and the last one carrying k."""
-        sizes = [len(c) for c in self._split(range(P), chunk)]
+    def _prefill_keys(self, P, mtp, k, chunk=NMAX, skip=0):
+        """Graph keys a prompt of P tokens needs: full chunks, and the last one carrying k. The
+        first `skip` tokens go through wide passes."""
+        sizes = [len(c) for c in self._split(range(P - skip), chunk)]
         return {(s, mtp, 0, False) for s in sizes[:-1]} | {(sizes[-1], mtp, k, False)}
 
     def _feed(self, tokens, follow):
@@ -711,14 +718,185 @@ class Engine:
         if bad:
             raise RuntimeError("decode aborted: " + "; ".join(bad))
 
+    # -- wide prefill passes ------------------------------------------------------------------------
+    WIDE, WIDE_MIN = 64, 32  # rows per wide pass; shorter prompts are not worth a second set of graphs
+
+    def wide_ok(self) -> bool:
+        """Wide passes exist for a single GPU with every decoder matrix in the W4 wire format."""
+        if self.tp is not None or not isinstance(self.linear, W4Linear):
+            return False
+        blocks = self.layers + ([self.mtp] if self.has_mtp else [])
+        names = ("in_proj", "out", "gate_up", "down")
+        mats = [L[n] for L in blocks for n in names] + ([self.mtp["fc"]] if self.has_mtp else [])
+        return all(isinstance(p, W4Packed) and p.K % 128 == 0 for p in mats) and all(L["gate_up"].gate_up for L in blocks)
+
+    def _wide_split(self, P: int, wide) -> int:
+        """How many leading tokens of a prompt of P go through wide passes: the largest multiple of
+        8 below P (the rest, 1..8 tokens, runs as an ordinary pass, which emits the first token)."""
+        wide = self.wide_prefill if wide is None else wide
+        head = ((P - 1) // NMAX) * NMAX
+        return head if wide and head >= self.WIDE_MIN and self.wide_ok() else 0
+
+    def _make_wide_buffers(self):
+        c, dev, W, H = self.cfg, self.dev, self.WIDE, self.cfg.hidden
+
+        def buf(*shape, dt=BF16):
+            return torch.zeros(*shape, dtype=dt, device=dev)
+
+        class _B:
+            pass
+        B = _B()
+        B.tok = buf(W + 1, dt=I32)
+        B.ctl = buf(W // NMAX, 32, dt=I32)  # control words of the 8-row sub-passes
+        B.off = (torch.arange(W // NMAX, dtype=I32, device=dev) * NMAX).contiguous()
+        B.h, B.xn, B.mo, B.hid = (buf(W, H) for _ in range(4))
+        B.proj = buf(W, -(-max(c.gdn_proj_rows, c.attn_proj_rows) // 8) * 8)
+        B.mix = buf(W, max(c.value_dim, c.hq * c.head_dim))
+        B.act = buf(W, c.inter)
+        B.q = buf(W, c.hq * c.head_dim)
+        if self.has_mtp:
+            B.cat, B.mh = buf(W, 2 * H), buf(W, H)
+        self.wb = B
+
+    def _wide_mixer(self, L, n, kv_only=False):
+        """Token mixing of a wide pass: the mixers take 8 rows, so the rows go through them in
+        sub-passes of 8, each with its own control words (position, and the 8 DeltaNet rows the
+        sub-pass before it staged). kv_only: just write K and V (a draft layer during prefill:
+        nothing else of it is kept)."""
+        c, B = self.cfg, self.wb
+        for j in range(n // NMAX):
+            rows = slice(j * NMAX, (j + 1) * NMAX)
+            ctl = B.ctl[j]
+            if L["type"] == "linear_attention":
+                pr = B.proj[rows, :c.gdn_proj_rows]
+                a0, a1 = c.conv_dim, c.conv_dim + c.value_dim
+                _C.gdn_step_n(pr[:, :a0], pr[:, a0:a1], pr[:, a1:a1 + c.hv], pr[:, a1 + c.hv:], L["ring"],
+                              L["conv_w"], L["A_log"], L["dt_bias"], L["norm_w"], L["S"], L["st_k"], L["st_v"],
+                              L["st_g"], ctl, B.mix[rows, :c.value_dim], c.hk, c.eps, q=self.GDN_Q)
+            else:
+                pr = B.proj[rows, :c.attn_proj_rows]
+                nq = c.hq * 2 * c.head_dim
+                nk = nq + c.hkv * c.head_dim
+                _C.attn_prep(pr[:, :nq], pr[:, nq:nk], pr[:, nk:], L["q_norm"], L["k_norm"], self.inv_freq, ctl,
+                             B.q[rows], L["kc"], L["vc"], c.eps)
+                if not kv_only:
+                    _C.attn_decode(B.q[rows], L["kc"], L["vc"], ctl, pr[:, :nq], self.part_o, self.part_ml,
+                                   B.mix[rows, :c.hq * c.head_dim])
+        width = c.value_dim if L["type"] == "linear_attention" else c.hq * c.head_dim
+        return B.mix[:n, :width]
+
+    def _wide_pass(self, n, mtp):
+        """One prefill pass over n rows (a multiple of 8, at most WIDE) of wb.tok: what n / 8
+        ordinary prefill passes do to the K/V caches, the DeltaNet state and the position, with
+        every matrix streamed once (`_w4.gemm`). No logits: the pass that follows emits them.
+        Follows python/qengine/engine.py:434-477 (layer, main) and :479-496 (draft layer) of the
+        reference with 8-row sub-passes for the mixers."""
+        c, B, lin, eps = self.cfg, self.wb, self.linear, self.cfg.eps
+        nb = n // NMAX
+        self._flush()
+        # control words of the sub-passes: positions 8 apart; every sub-pass but the first finds the
+        # 8 DeltaNet rows of the one before it pending
+        B.ctl[:nb].copy_(self.ctl.expand(nb, -1))
+        B.ctl[:nb, self.POS].add_(B.off[:nb])
+        if nb > 1:
+            B.ctl[1:nb, self.PENDING].fill_(NMAX)
+        h, xn, mo = B.h[:n], B.xn[:n], B.mo[:n]
+
+        def mm(x, p, out):
+            _w4.gemm(x, p.qw, p.scales, out, p.M, swiglu=p.gate_up)
+
+        def block(L, stream, delta, table_tok=None):
+            width = c.gdn_proj_rows if L["type"] == "linear_attention" else c.attn_proj_rows
+            if table_tok is not None:  # rows = embedding rows of the tokens
+                lin.norm_rows(self.embed, None, L["in_norm"], eps, xn, tok=table_tok, h_out=stream)
+            else:
+                lin.norm_rows(stream, delta, L["in_norm"], eps, xn, h_out=stream if delta is not None else None)
+            mm(xn, L["in_proj"], B.proj[:n, :width])
+
+        first = True
+        for L in self.layers:
+            block(L, h, None if first else mo, table_tok=B.tok if first else None)
+            first = False
+            mixed = self._wide_mixer(L, n)
+            mm(mixed, L["out"], mo)
+            lin.norm_rows(h, mo, L["post_norm"], eps, xn, h_out=h)
+            mm(xn, L["gate_up"], B.act[:n])
+            mm(B.act[:n], L["down"], mo)
+        if mtp:
+            # draft layer on the same rows (reference :479-496): input fc([norm(embed(next token)) |
+            # norm(final-normed trunk row)]); during prefill only its K/V rows (or DeltaNet state) stay
+            M, H = self.mtp, c.hidden
+            lin.norm_rows(h, mo, self.final_norm, eps, B.hid[:n], h_out=h)
+            cat = B.cat[:n]
+            lin.norm_rows(self.embed, None, M["pre_e"], eps, cat[:, :H], tok=B.tok[1:])
+            lin.norm_rows(B.hid[:n], None, M["pre_h"], eps, cat[:, H:])
+            mm(cat, M["fc"], B.mh[:n])
+            block(M, B.mh[:n], None)
+            self._wide_mixer(M, n, kv_only=M["type"] != "linear_attention")
+        # commit: the position moves on by n; the last sub-pass left 8 DeltaNet rows pending
+        self.ctl[self.POS].add_(n)
+        self.ctl[self.PENDING].fill_(NMAX)
+
+    def wide_graph(self, n, mtp=False):
+        """The CUDA graph of a wide prefill pass over n rows, captured on first use (like `graph`)."""
+        key = ("wide", n, bool(mtp))
+        if n % NMAX or not NMAX <= n <= self.WIDE or (mtp and not self.has_mtp) or not self.wide_ok():
+            raise ValueError(f"no such pass: {key}")
+        if key in self.graphs:
+            return self.graphs[key]
+        if self.wb is None:
+            self._make_wide_buffers()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._wide_pass(n, mtp)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        count0 = launches[0]
+        gc.collect()  # see graph()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(g, capture_error_mode="global"):
+                self._wide_pass(n, mtp)
+        finally:
+            if gc_was_on:
+                gc.enable()
+        torch.cuda.synchronize()
+        self.graphs[key] = g
+        self.graph_kernels[key] = launches[0] - count0
+        return g
+
+    def _wide_blocks(self, head):
+        return [min(self.WIDE, head - at) for at in range(0, head, self.WIDE)]
+
+    def _need_wide(self, head, mtp):
+        fresh = [n for n in set(self._wide_blocks(head)) if ("wide", n, bool(mtp)) not in self.graphs]
+        for n in fresh:
+            self.wide_graph(n, mtp)
+        if fresh:
+            self.reset()
+
     # -- public loops ---------------------------------------------------------------------------
-    def prefill(self, prompt, mtp=False, k=0, chunk=NMAX):
+    def prefill(self, prompt, mtp=False, k=0, chunk=NMAX, wide=None):
         """Feed the prompt `chunk` rows per pass. The last row's greedy token is the first
         generated token (log[len(prompt)]); with mtp / k the drafts of the first verify pass are
         ready afterwards. Leaves the engine in decode / verify mode. Expects reset() and captured
-        graphs (`generate*` take care of both)."""
-        pieces = self._split(list(prompt), chunk)
+        graphs (`generate*` take care of both).
+        wide (default: the engine's `wide_prefill`): all but the last 1..8 tokens go through passes
+        of up to 64 rows (`_wide_pass`); the state they leave agrees with the 8-row passes to
+        rounding (the GEMM adds a tile's groups in another order than the GEMV), not bit for bit."""
+        prompt = list(prompt)
+        head = self._wide_split(len(prompt), wide)
         self.ctl[self.MODE].fill_(0)
+        at = 0
+        for n in self._wide_blocks(head):
+            row = torch.tensor(prompt[at:at + n + 1], dtype=I32)
+            self.wb.tok[:n + 1].copy_(row)
+            self.wide_graph(n, mtp).replay()
+            at += n
+        pieces = self._split(prompt[head:], chunk)
         for i, piece in enumerate(pieces):
             last = i == len(pieces) - 1
             self._feed(piece, -1 if last else pieces[i + 1][0])
@@ -726,7 +904,7 @@ class Engine:
         self.ctl[self.MODE].fill_(1)
 
     @torch.no_grad()
-    def generate(self, prompt, n_new, timing=False, chunk=NMAX):
+    def generate(self, prompt, n_new, timing=False, chunk=NMAX, wide=None):
         """Plain greedy decoding: prefill, then n_new - 1 single-row passes. Returns the n_new token
         ids; timing=True returns (tokens, prefill seconds, decode seconds)."""
         P = len(prompt)
@@ -734,11 +912,13 @@ class Engine:
         if first + n_new + 1 > self.max_len:
             raise ValueError("sequence does not fit max_len")
         step_key = (1, False, 0, False)
-        self._need(self._prefill_keys(P, False, 0, chunk) | {step_key})
+        head = self._wide_split(P, wide)
+        self._need_wide(head, False)
+        self._need(self._prefill_keys(P, False, 0, chunk, skip=head) | {step_key})
         self.reset()
         t = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         t[0].record()
-        self.prefill(prompt, chunk=chunk)
+        self.prefill(prompt, chunk=chunk, wide=wide)
         t[1].record()
         step = self.graphs[step_key]
         for _ in range(n_new - 1):
@@ -750,7 +930,7 @@ class Engine:
         return (out, t[0].elapsed_time(t[1]) / 1e3, t[1].elapsed_time(t[2]) / 1e3) if timing else out
 
     @torch.no_grad()
-    def generate_spec(self, prompt, n_new, k, timing=False, chunk=NMAX, force_accept=None, truth=None):
+    def generate_spec(self, prompt, n_new, k, timing=False, chunk=NMAX, force_accept=None, truth=None, wide=None):
         """Greedy speculative decoding with k MTP drafts per cycle (verify over k + 1 rows). The
         output equals `generate` token for token. force_accept = a (0..k) together with truth =
         prompt + known greedy continuation overwrites the drafts before every verify so that
@@ -770,11 +950,13 @@ class Engine:
             self.force_a = int(force_accept)
             self.graphs.pop((k + 1, True, k, True), None)  # the graph holds the old truth buffer
         cycle_key = (k + 1, True, k, forced)
-        self._need(self._prefill_keys(P, True, k, chunk) | {cycle_key})
+        head = self._wide_split(P, wide)
+        self._need_wide(head, True)
+        self._need(self._prefill_keys(P, True, k, chunk, skip=head) | {cycle_key})
         self.reset()
         t = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         t[0].record()
-        self.prefill(prompt, mtp=True, k=k, chunk=chunk)
+        self.prefill(prompt, mtp=True, k=k, chunk=chunk, wide=wide)
         self.ctl[self.CYCLES:self.ACCEPTED + 1].zero_()
         self.ctl[16:].zero_()
         t[1].record()

@@ -161,3 +161,13 @@ def gemv(x: torch.Tensor, p: W4Packed, out: torch.Tensor | None = None, **kw) ->
         out = torch.empty(x.shape[0], p.M, dtype=torch.bfloat16, device=x.device)
     (_w4.gemv_swiglu if p.gate_up else _w4.gemv)(x, p.qw, p.scales, out, p.M, **kw)
     return out
+
+
+def gemm(x: torch.Tensor, p: W4Packed, out: torch.Tensor | None = None, **kw) -> torch.Tensor:
+    """The same product for up to 64 rows with the matrix read once (`_w4.gemm`; prefill passes)."""
+    from . import _w4
+
+    if out is None:
+        out = torch.empty(x.shape[0], p.M, dtype=torch.bfloat16, device=x.device)
+    _w4.gemm(x, p.qw, p.scales, out, p.M, swiglu=p.gate_up, **kw)
+    return out

@@ -340,3 +340,50 @@ def test_norm_weights_too_large_for_fp16_rows_keep_bf16(setup):
     assert bf.generate(prompt, 60) == base.generate(prompt, 60)
     a, b = bf.sequence_logits(prompt[:16]), base.sequence_logits(prompt[:16])
     assert torch.equal(a.view(torch.int16), b.view(torch.int16)), "fp16 rows changed logit bits"
+
+
+# ---------------------------------------------------------------------------------------------
+# Prefill in passes of up to 64 rows through the tensor-memory GEMM (Engine.prefill(wide=True); no
+# counterpart in the reference, which prefills 8 rows at a time). The GEMM adds the groups of a tile
+# in another order than the GEMV, so the state agrees with the 8-row passes to rounding only; what
+# must hold exactly is everything downstream of a given prefill: spec == plain, determinism.
+# ---------------------------------------------------------------------------------------------
+def _prefill_and_snapshot(eng, prompt, wide, mtp=False, k=0):
+    head = eng._wide_split(len(prompt), wide)
+    eng._need_wide(head, mtp)
+    eng._need(eng._prefill_keys(len(prompt), mtp, k, skip=head))
+    eng.reset()
+    eng.prefill(prompt, mtp=mtp, k=k, wide=wide)
+    torch.cuda.synchronize()
+    tail = len(prompt) - head if head else (len(prompt) - 1) % 8 + 1
+    blocks = eng.layers + ([eng.mtp] if mtp else [])
+    P = len(prompt)
+    kv = [(L["kc"][:, :P].float().clone(), L["vc"][:, :P].float().clone()) for L in blocks if "kc" in L]
+    return eng.logits[:tail].float().clone(), kv, int(eng.ctl[eng.POS].item()), int(eng.log[P].item()), head
+
+
+@pytest.mark.parametrize("which,P", [("tiny", 33), ("tiny", 100), ("tiny", 137), ("27b", 75)])
+def test_prefill_in_64_row_passes_agrees_with_8_row_passes(setup, wide, which, P):
+    from qengine_b200 import synth
+    cfg, _, eng = setup if which == "tiny" else wide
+    prompt = synth.prompt_ids(P, cfg.vocab, seed=31)
+    lg8, kv8, pos8, tok8, head8 = _prefill_and_snapshot(eng, prompt, False, mtp=True, k=2)
+    lgw, kvw, posw, tokw, headw = _prefill_and_snapshot(eng, prompt, True, mtp=True, k=2)
+    assert head8 == 0 and headw == ((P - 1) // 8) * 8 and posw == pos8 == P
+    cs = min(cosine(lgw[t].cpu(), lg8[t].cpu()) for t in range(lgw.shape[0]))
+    worst = float((lgw - lg8).abs().max())
+    kv_err = max(float((a - b).abs().max() / (b.abs().max() + 1e-6)) for x, y in zip(kvw, kv8) for a, b in zip(x, y))
+    print(f"\n{which} P={P}: last-pass logits cosine {cs:.7f}, max|d| {worst:.4f}, K/V rel err {kv_err:.2e}, "
+          f"first token equal: {tokw == tok8}")
+    assert cs >= 0.9999 and kv_err < 2e-2  # (the logits left in the buffer are the draft layer's)
+
+
+def test_spec_equals_plain_after_a_wide_prefill(setup, wide):
+    from qengine_b200 import synth
+    for (cfg, _, eng), P, n_new in ((setup, 90, 80), (wide, 70, 40)):
+        prompt = synth.prompt_ids(P, cfg.vocab, seed=32)
+        plain = eng.generate(prompt, n_new, wide=True)
+        assert eng.generate(prompt, n_new, wide=True) == plain  # run to run
+        for k in (1, 4):
+            assert eng.generate_spec(prompt, n_new, k, wide=True) == plain, (P, k)
+        assert ("wide", 64, True) in eng.graphs and ("wide", 64, False) in eng.graphs
