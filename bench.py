@@ -600,6 +600,27 @@ def run_ours(a):
         del eng_p
         gc.collect()
         torch.cuda.empty_cache()
+    # ---- prompt processing: 8-row passes through the GEMV vs 64-row passes through the GEMM ------
+    prefill = {}
+    if world == 1 and a.prefill_tokens >= 64:
+        eng_f = Engine(cfg, W, max_len=a.prefill_tokens + 64, device=dev, mtp=False)
+        long_prompt = synth.prompt_ids(a.prefill_tokens, cfg.vocab, seed=4321)
+        firsts = {}
+        for label, wide_pass in (("rows8", False), ("rows64", True)):
+            firsts[label] = eng_f.generate(long_prompt, 2, wide=wide_pass)[0]  # captures the graphs
+            secs = []
+            for _ in range(3):
+                barrier()
+                secs.append(eng_f.generate(long_prompt, 2, timing=True, wide=wide_pass)[1])
+            sec = statistics.median(secs)
+            prefill[label] = {"tok_s": a.prefill_tokens / sec, "ms": sec * 1e3}
+        prefill.update(prompt_tokens=a.prefill_tokens, speedup=prefill["rows64"]["tok_s"] / prefill["rows8"]["tok_s"],
+                       first_token_equal=firsts["rows8"] == firsts["rows64"],
+                       what="host feed + graph replays of a whole prompt; rows64 = passes of 64 rows through "
+                            "qe_w4_gemm (tcgen05), the mixers in sub-passes of 8 rows")
+        del eng_f
+        gc.collect()
+        torch.cuda.empty_cache()
     exchange_us = exchange_timing(eng) if world > 1 else None
     parity = parity_early
 
@@ -707,6 +728,7 @@ def run_ours(a):
             "mtp_k4": mtp,
             "verify_pass": verify,
             "long_context": longctx,
+            "prefill": prefill,
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": (P // 8) * 36 + 8,
                     "d2h_bytes_per_step": n_new * 4},
             "gpu_launches": launches,
@@ -748,6 +770,8 @@ def main():
                     help="pre-filled cache length of the long-context block (0 = skip it)")
     ap.add_argument("--draft-vocab", type=int, default=49152,
                     help="also time the MTP cycle with the draft head pruned to this many ids (0 = skip)")
+    ap.add_argument("--prefill-tokens", type=int, default=1024,
+                    help="prompt length of the prefill comparison (8-row vs 64-row passes; 0 = skip)")
     ap.add_argument("--no-mtp", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-tokens", type=int, default=8, help="whole tokens timed for cpu_baseline (N = 1 only)")

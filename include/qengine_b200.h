@@ -335,12 +335,19 @@ int qe_w4_gemv_static(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream)
  * (python/qengine/engine.py:558-573). The same product as qe_w4_gemv for p->N = 1..QE_MAX_GEMM_ROWS
  * activation rows with the matrix streamed from HBM once for all of them: a prefill pass of 64
  * rows reads the weights once instead of eight times. Same wire format, epilogues and out_f32 as
- * qe_w4_gemv; the arithmetic per 1 KB unit is the GEMV's, the order in which the units of a tile
- * are added is not, so a row agrees with qe_w4_gemv to fp32 rounding (not bit for bit); results are
- * bit-identical run to run and row r does not depend on N. Needs K == Kp, Kp / 128 even, bf16 x
- * with 16-byte aligned rows and ldx % 8 == 0 (QE_ERR_ARG otherwise); p->ws, p->counters and
- * p->x_f16 (must be 0) are not used. Only cfg->pdl is read. */
+ * qe_w4_gemv. Default kernel (cfg->variant != 1): tcgen05.mma with the accumulator in tensor
+ * memory -- per 128-k group the exact integer dot products, scaled in fp32 and added group by
+ * group in ascending order, i.e. the GEMV's arithmetic with another order of additions, so a row
+ * agrees with qe_w4_gemv to fp32 rounding (not bit for bit); results are bit-identical run to run
+ * and row r does not depend on N. cfg->variant == 1: an mma.sync kernel (needs Kp / 128 even).
+ * Needs K == Kp, bf16 x with 16-byte aligned rows and ldx % 8 == 0 (QE_ERR_ARG otherwise);
+ * p->x_f16 must be 0. Matrices of few rows (fewer 128-row super-tiles than half the SMs) are also
+ * split along K; their partial sums meet in p->ws / p->counters, sized by qe_w4_plan_gemm (any
+ * contents in ws; counters zero before the first call, left zero). With either pointer NULL the
+ * split is skipped (same result up to fp32 rounding of the order of additions, fewer SMs busy).
+ * Of cfg only pdl and variant are read. */
 #define QE_MAX_GEMM_ROWS 64
+int qe_w4_plan_gemm(const qe_w4_params* p, const qe_w4_cfg* cfg, qe_w4_plan* plan);
 int qe_w4_gemm(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream);
 
 /* The weight rings are fed by bulk copies whose completion waits are bounded; this returns the

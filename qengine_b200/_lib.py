@@ -96,6 +96,7 @@ SIGNATURES = {
     "qe_w4_clear_error": (c_int, []),
     "qe_w4_gemv_static": (c_int, [C.POINTER(W4Params), C.POINTER(W4Cfg), P]),
     "qe_w4_gemm": (c_int, [C.POINTER(W4Params), C.POINTER(W4Cfg), P]),
+    "qe_w4_plan_gemm": (c_int, [C.POINTER(W4Params), C.POINTER(W4Cfg), C.POINTER(W4Plan)]),
 }
 
 

@@ -289,6 +289,7 @@ def norm_rows(h_in, delta, norm_w, eps, xn_out, h_out=None, tok=None, xn16_out=N
 
 
 MAX_GEMM_ROWS = 64
+_gemm_scratch: dict[int, tuple] = {}
 
 
 def gemm(x, qw, scales, out, M, swiglu=False, pdl=True, variant=0):
@@ -314,6 +315,18 @@ def gemm(x, qw, scales, out, M, swiglu=False, pdl=True, variant=0):
     p = W4Params(qw.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(), None, None, M, K, Mp, Kp, N,
                  x.stride(0), out.stride(0), EPI_SWIGLU if swiglu else EPI_NONE, int(out_f32), 0)
     cfg = W4Cfg(0, 0, 0, int(bool(pdl)), int(variant), -1, 0, 4)
+    plan = W4Plan()
+    check(lib.qe_w4_plan_gemm(C.byref(p), C.byref(cfg), C.byref(plan)), "gemm plan", kernels=0)
+    if plan.ws_floats:  # a matrix of few rows is split along K: scratch of its own (the GEMV's must stay zero)
+        dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
+        W = _gemm_scratch.get(dev)
+        if W is None or W[0].numel() < plan.ws_floats or W[1].numel() < plan.counters:
+            _req(not torch.cuda.is_current_stream_capturing(),
+                 "gemm scratch would have to grow during graph capture: run the shape once eagerly first")
+            W = (torch.empty(max(plan.ws_floats, 1 << 20), dtype=torch.float32, device=x.device),
+                 torch.zeros(max(plan.counters, 1 << 10), dtype=torch.int32, device=x.device), W)  # old ones stay alive
+            _gemm_scratch[dev] = W
+        p.ws, p.counters = W[0].data_ptr(), W[1].data_ptr()
     code = lib.qe_w4_gemm(C.byref(p), C.byref(cfg), torch.cuda.current_stream().cuda_stream)
     _req(code != -22, "gemm: argument combination not supported by the kernel")
     _req(code == 0, f"gemm launch failed: CUDA error {code}")

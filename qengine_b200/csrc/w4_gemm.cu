@@ -27,6 +27,8 @@
 //
 // Every mbarrier wait is bounded; on expiry the warp records the error word, the CTA drains and
 // leaves.
+#include <cuda/atomic>
+
 #include <algorithm>
 
 #include "w4_dev.cuh"
@@ -43,6 +45,9 @@ struct GemmArgs {
   long ldx;
   OutDesc o;  // o.N = all activation rows (1..8 RT)
   int G, tiles, nctas;
+  int kparts;      // tensor-memory kernel: parts of K a super-tile is split into
+  float* ws;       // ... their fp32 sums, [super-tile][part][64][128]
+  int* counters;   // ... and one arrival counter per super-tile, zero between launches
 };
 
 __device__ int g_gemm_error = 0;
@@ -291,19 +296,23 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_gemm_kernel(const __grid_consta
 //     (tcgen05.ld), multiplies by the row's group scale in fp32 and adds to 16 registers:
 //     acc[m, n] += scale[m, g] * D_g[m, n], groups in ascending order -- the arithmetic of the GEMV
 //     (exact products, fp32 sums inside a group, the scale applied once per group).
-// A, B and the accumulators are double-buffered and the halves alternate, so one half unpacks
-// step z + 1 while the other waits for the products of step z; there is no block-wide barrier in
+// A, B and the accumulators have three stages and the halves alternate, so one half unpacks
+// step z + 1 while the products of steps z and z - 1 are under way; there is no block-wide barrier in
 // the loop, the warps meet only through two kinds of mbarrier: "step z may be multiplied" (one
 // arrival per warp: its share of the operands is stored, if it had one, and it has read the
-// products of step z - 2 out of the accumulator) and "products of step z complete"
+// products of step z - 3 out of the accumulator) and "products of step z complete"
 // (tcgen05.commit). After the last group the registers hold the super-tile's [128 x 64] result:
-// rounded and stored (or combined into SwiGLU) from there.
+// rounded and stored (or combined into SwiGLU) from there. A matrix with fewer super-tiles than
+// half the SMs (the 5,120-row out and down projections: 40) is also split along K, up to as many
+// jobs as there are SMs; the parts of a super-tile meet in a caller-provided fp32 workspace.
 // ---------------------------------------------------------------------------------------------
-constexpr int kTcWarps = 16, kTcThreads = (kTcWarps + 1) * 32, kTcStages = 4, kTcCols = 128;
+constexpr int kTcWarps = 16, kTcThreads = (kTcWarps + 1) * 32, kTcStages = 4, kTcDepth = 3, kTcCols = 256;
+constexpr int kTcScales = 8;                   // buffers of group scales (see the loop)
 constexpr uint32_t kTcStageBytes = 1024 + 32;  // one unit of codes + its 16 scales
 constexpr uint32_t kTcRing = kTcStages * kTcStageBytes;
 constexpr uint32_t kTcA = 128 * 256, kTcB = 64 * 256;  // one stage of A / B
-constexpr uint32_t kTcSmem = 2 * kTcA + 2 * kTcB + kTcWarps * kTcRing + 4 * 128 * sizeof(float) + 1024;
+constexpr uint32_t kTcSmem =
+    kTcDepth * (kTcA + kTcB) + kTcWarps * kTcRing + kTcScales * 128 * sizeof(float) + 1024;
 
 // Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
@@ -343,17 +352,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4_gemm_tc_kernel(const __grid_
   dep_release();
   extern __shared__ unsigned char smem_raw[];
   __shared__ uint64_t full_w[kTcWarps][kTcStages];
-  __shared__ uint64_t a_full[2];  // step z may be multiplied: one arrival per unpacking warp
-  __shared__ uint64_t d_full[2];  // its products are in tensor memory (tcgen05.commit)
+  __shared__ uint64_t a_full[kTcDepth];  // step z may be multiplied: one arrival per unpacking warp
+  __shared__ uint64_t d_full[kTcDepth];  // its products are in tensor memory (tcgen05.commit)
   __shared__ uint32_t tmem_slot;
+  __shared__ int s_last;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = lane >> 2, t = lane & 3;
   unsigned char* base = smem_raw + ((1024u - (sa(smem_raw) & 1023u)) & 1023u);  // swizzle atoms: 1 KB aligned
-  float* sc = reinterpret_cast<float*>(base + 2 * kTcA + 2 * kTcB + (size_t)kTcWarps * kTcRing);  // [4][128]
+  unsigned char* Bbase = base + kTcDepth * kTcA;
+  float* sc = reinterpret_cast<float*>(Bbase + kTcDepth * kTcB + (size_t)kTcWarps * kTcRing);  // [kTcScales][128]
 
   if (tid == 0) {
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kTcDepth; ++b) {
       bar_init(&a_full[b], kTcWarps);
       bar_init(&d_full[b], 1);
     }
@@ -363,7 +374,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4_gemm_tc_kernel(const __grid_
   }
   if (lane == 0) bar_fence_init();
   __syncwarp();
-  if (warp == kTcWarps) {  // tensor memory: two accumulators of 64 columns
+  if (warp == kTcWarps) {  // tensor memory: three accumulators of 64 columns
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sa(&tmem_slot)), "r"(kTcCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -373,55 +384,76 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4_gemm_tc_kernel(const __grid_
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
 
-  // ---- this CTA's super-tiles ----
-  const int G = a.G, N = a.o.N;
-  const int ST = (a.tiles + 7) >> 3;
+  // ---- this CTA's jobs: (super-tile, part of K), dealt out round-robin ----
+  const int G = a.G, N = a.o.N, KP = a.kparts;
+  const int J = ((a.tiles + 7) >> 3) * KP;
   const int cta = blockIdx.x, nctas = gridDim.x;
-  const int nj = cta < ST ? (ST - cta + nctas - 1) / nctas : 0;
-  const int Z = nj * G;  // steps
+  const int nj = cta < J ? (J - cta + nctas - 1) / nctas : 0;
+  struct Cur {
+    int j, g, gend, tile0, jidx;
+  };
+  auto cur_set = [&](Cur& c, int j) {
+    c.j = j;
+    if (j < nj) {
+      c.jidx = cta + j * nctas;
+      const int st = c.jidx / KP, part = c.jidx - st * KP;
+      c.g = share_begin(G, KP, part);
+      c.gend = share_begin(G, KP, part + 1);
+      c.tile0 = st * 8;
+    } else {
+      c.jidx = 0; c.g = 0; c.gend = 1 << 30; c.tile0 = 0;
+    }
+  };
+  auto cur_next = [&](Cur& c) {
+    if (++c.g == c.gend) cur_set(c, c.j + 1);
+  };
+  int Z = 0;  // steps
+  {
+    Cur c;
+    for (int j = 0; j < nj; ++j) {
+      cur_set(c, j);
+      Z += c.gend - c.g;
+    }
+  }
 
   if (warp == kTcWarps) {
     // ---- the issuing warp: 8 products per step as soon as the step may be multiplied ----
     // One thread issues: its instruction latency is what a step waits for, so the descriptors are
     // built once and only their start-address field (low word, 16-byte units) moves in the loop.
-    const uint64_t da0 = tc_desc(sa(base)), db0 = tc_desc(sa(base + 2 * kTcA));
+    const uint64_t da0 = tc_desc(sa(base)), db0 = tc_desc(sa(Bbase));
     bool ok = true;
+    int s3 = 0, ph = 0;
 #pragma unroll 1
     for (int z = 0; z < Z && ok; ++z) {
-      const int s = z & 1;
-      if (!warp_wait(&a_full[s], (z >> 1) & 1)) {
+      if (!warp_wait(&a_full[s3], ph)) {
         ok = false;
         atomicExch(&g_gemm_error, 2);
         break;
       }
       tc_fence_after();
       if (lane == 0) {
-        const uint64_t da = da0 + (uint64_t)(s * (kTcA >> 4)), db = db0 + (uint64_t)(s * (kTcB >> 4));
-        const uint32_t d = tmem + s * 64;
+        const uint64_t da = da0 + (uint64_t)(s3 * (kTcA >> 4)), db = db0 + (uint64_t)(s3 * (kTcB >> 4));
+        const uint32_t d = tmem + s3 * 64;
 #pragma unroll
         for (int c2 = 0; c2 < 2; ++c2)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             tc_mma(d, da + (uint64_t)(c2 * (16384 >> 4) + kk * 2), db + (uint64_t)(c2 * (8192 >> 4) + kk * 2),
                    (c2 | kk) ? 1u : 0u);
-        tc_commit(&d_full[s]);
+        tc_commit(&d_full[s3]);
       }
       __syncwarp();
+      if (++s3 == kTcDepth) { s3 = 0; ph ^= 1; }
     }
   } else {
     // ---- the 16 unpacking warps ----
-    unsigned char* ring = base + 2 * kTcA + 2 * kTcB + (size_t)warp * kTcRing;
+    unsigned char* ring = Bbase + kTcDepth * kTcB + (size_t)warp * kTcRing;
     const int par = warp >> 3, ti = warp & 7;  // prepares the steps of this parity; tile of the super-tile
-    // (job, group) of an own step, and the step after the next one
-    auto norm = [&](int& job, int& g) {
-      while (g >= G) { g -= G; ++job; }
-    };
-    // the unit of this warp's tile in (job, g); false beyond the matrix (only the matrix's last
-    // super-tile can lack tiles, and it is the last job of its CTA)
-    auto unit_of = [&](int job, int g, size_t& u) {
-      const int tile = (cta + job * nctas) * 8 + ti;
-      u = (size_t)tile * G + g;
-      return job < nj && tile < a.tiles;
+    // the unit of this warp's tile in a step; false beyond the matrix (only the matrix's last
+    // super-tile can lack tiles, and its jobs are the last ones of their CTAs)
+    auto unit_of = [&](const Cur& c, size_t& u) {
+      u = (size_t)(c.tile0 + ti) * G + c.g;
+      return c.j < nj && c.tile0 + ti < a.tiles;
     };
     auto fill_w = [&](size_t u, int at) {  // lane 0
       unsigned char* dst = ring + (size_t)at * kTcStageBytes;
@@ -429,14 +461,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4_gemm_tc_kernel(const __grid_
       bulk_g2s(dst, reinterpret_cast<const unsigned char*>(a.qw) + u * 1024, 1024, &full_w[warp][at]);
       bulk_g2s(dst + 1024, a.scales + u * 16, 32, &full_w[warp][at]);
     };
-    int rj = 0, rg = par;  // next own step to request from HBM
-    norm(rj, rg);
+    Cur cz, cr;  // the current step; the next own step to request from HBM
+    cur_set(cz, 0);
+    cur_set(cr, 0);
+    if (par) cur_next(cr);
     for (int q = 0; q < kTcStages; ++q) {
       size_t u;
-      if (!unit_of(rj, rg, u)) break;
+      if (!unit_of(cr, u)) break;
       if (lane == 0) fill_w(u, q);
-      rg += 2;
-      norm(rj, rg);
+      cur_next(cr);
+      cur_next(cr);
     }
     dep_wait();
 
@@ -452,9 +486,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4_gemm_tc_kernel(const __grid_
       for (int i = 0; i < 4; ++i)
         xr[i] = n0 + 16 * i < N ? xsrc[(long)i * xstep + g * 16] : make_uint4(0u, 0u, 0u, 0u);
     };
-    int cj = 0, cg = par;  // next own step to prepare
-    norm(cj, cg);
-    if (cj < nj) load_x(cg);
+    {
+      Cur c = cz;
+      if (par) cur_next(c);
+      if (c.j < nj) load_x(c.g);
+    }
 
     const int m = 32 * (warp & 3) + lane;  // this thread's row of the super-tile (a tensor-memory lane)
     const int col0 = 16 * (warp >> 2);     // its 16 activation rows
@@ -466,38 +502,60 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4_gemm_tc_kernel(const __grid_
     bool ok = true;
     // acc += scale[m, group of step z] * D(z)
     auto drain = [&](int z) {
-      if (ok && !warp_wait(&d_full[z & 1], (z >> 1) & 1)) {
+      const int s3 = z % kTcDepth, ph = (z / kTcDepth) & 1;
+      if (ok && !warp_wait(&d_full[s3], ph)) {
         ok = false;
         atomicExch(&g_gemm_error, 4);
       }
       if (!ok) return;
       tc_fence_after();
       float v[16];
-      tc_ld16(t_lane + (z & 1) * 64, v);
-      const float sm = sc[(z & 3) * 128 + m];
+      tc_ld16(t_lane + s3 * 64, v);
+      const float sm = sc[(z & (kTcScales - 1)) * 128 + m];
 #pragma unroll
       for (int k = 0; k < 16; ++k) acc[k] = fmaf(sm, v[k], acc[k]);
     };
+    auto store_out = [&](int tile0) {  // the finished sums of a super-tile, from registers
+      const int tile = tile0 + (m >> 4), rr = m & 15;
+      if (a.o.epi == QE_EPI_SWIGLU) {
+        bf16* o = static_cast<bf16*>(a.o.out);
+        const int jrow = tile * 8 + rr;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          const float up = __shfl_down_sync(0xffffffffu, acc[k], 8);
+          const int n = col0 + k;
+          if (ok && rr < 8 && jrow < a.o.M && n < N) o[(long)n * a.o.ldo + jrow] = tobf16(silu_fast(acc[k]) * up);
+        }
+      } else {
+        const int mrow = tile * 16 + rr;
+        if (ok && mrow < a.o.M) {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const int n = col0 + k;
+            if (n >= N) continue;
+            if (a.o.out_f32) static_cast<float*>(a.o.out)[(long)n * a.o.ldo + mrow] = acc[k];
+            else static_cast<bf16*>(a.o.out)[(long)n * a.o.ldo + mrow] = tobf16(acc[k]);
+          }
+        }
+      }
+    };
 
-    // A warp that is about to write stage s for step z has read the products of step z - 2, so
-    // they are complete and stage s is free; its arrival for step z tells the issuing warp the
-    // same about the accumulator. The scales have four buffers: a writer of step z + 4 has seen
-    // the products of step z + 2, which were only issued after everybody had drained step z.
-    int slot = 0, phase = 0, g = 0, job = 0;
+    // Three stages of A, B and accumulator; a warp reads the products of step z two steps later.
+    // Before it arrives for step z (and before it writes stage z % 3) it has read the products of
+    // step z - 3, so they are complete, the stage is free, and the issuing warp may overwrite that
+    // accumulator once all 16 have arrived. A writer of the scales of step z + L has seen the
+    // products of step z + L - 3, issued after everybody arrived for that step; a reader still
+    // busy with step z has arrived for z + 2 at most, so L <= 5: eight buffers of scales.
+    int slot = 0, phase = 0, since = 0, s3 = 0;
 #pragma unroll 1
     for (int z = 0; z < Z; ++z) {
-      const int s = z & 1;
-      if (s == par) {
-        unsigned char* As = base + (size_t)s * kTcA;
-        unsigned char* Bs = base + 2 * kTcA + (size_t)s * kTcB;
+      if ((z & 1) == par) {
+        unsigned char* As = base + (size_t)s3 * kTcA;
+        unsigned char* Bs = Bbase + (size_t)s3 * kTcB;
 #pragma unroll
         for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(Bs + boff + 2048 * i) = xr[i];
         size_t u;
-        const bool has = unit_of(cj, cg, u);
-        cg += 2;
-        norm(cj, cg);
-        if (cj < nj) load_x(cg);  // the activations of the next own step: two steps to land
-        if (has) {
+        if (unit_of(cz, u)) {
           if (ok && !warp_wait(&full_w[warp][slot], phase)) {
             ok = false;
             atomicExch(&g_gemm_error, 1);
@@ -506,7 +564,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4_gemm_tc_kernel(const __grid_
             const unsigned char* st = ring + (size_t)slot * kTcStageBytes;
             const uint4 w0 = reinterpret_cast<const uint4*>(st)[lane], w1 = reinterpret_cast<const uint4*>(st)[32 + lane];
             if (lane < 16)
-              sc[(z & 3) * 128 + 16 * ti + lane] = __half2float(reinterpret_cast<const __half*>(st + 1024)[lane]);
+              sc[(z & (kTcScales - 1)) * 128 + 16 * ti + lane] = __half2float(reinterpret_cast<const __half*>(st + 1024)[lane]);
             unsigned char* rowp = As + (16 * ti + r) * 128;  // row r of the tile; row r + 8 is 1 KB on
             const uint32_t c0 = (uint32_t)((2 * t) ^ r) << 4, c1 = (uint32_t)((2 * t + 1) ^ r) << 4;
 #pragma unroll
@@ -522,13 +580,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4_gemm_tc_kernel(const __grid_
           }
           __syncwarp();  // every lane has read this stage: hand its slot back to the copy engine
           size_t un;
-          if (unit_of(rj, rg, un)) {
-            if (lane == 0 && ok) {
-              async_proxy_fence();
-              fill_w(un, slot);
-            }
-            rg += 2;
-            norm(rj, rg);
+          if (unit_of(cr, un)) {
+            if (lane == 0 && ok) fill_w(un, slot);
+            cur_next(cr);
+            cur_next(cr);
           }
           if (++slot == kTcStages) { slot = 0; phase ^= 1; }
         }
@@ -536,39 +591,61 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4_gemm_tc_kernel(const __grid_
       }
       tc_fence_before();  // this thread's tensor-memory loads are ordered before the arrival
       __syncwarp();
-      if (lane == 0) bar_arrive(&a_full[s]);
-      if (g > 0) drain(z - 1);  // overlaps the products of this step
-      if (++g == G) {
-        // last group of a super-tile: its result is complete after one more drain
-        g = 0;
+      if (lane == 0) bar_arrive(&a_full[s3]);
+      if (++s3 == kTcDepth) s3 = 0;
+      if ((z & 1) == par) {
+        // The activations of the next own step: requested after the proxy fence above (which
+        // would wait for them), two steps ahead of their use.
+        Cur c = cz;
+        cur_next(c);
+        cur_next(c);
+        if (c.j < nj) load_x(c.g);
+      }
+      if (since >= 2) drain(z - 2);
+      if (cz.g + 1 == cz.gend) {
+        // last group of the job: two or three more drains complete its sums
+        if (since >= 1) drain(z - 1);
         drain(z);
-        const int st_idx = cta + job * nctas;
-        ++job;
-        const int tile = st_idx * 8 + (m >> 4), rr = m & 15;
-        if (a.o.epi == QE_EPI_SWIGLU) {
-          bf16* o = static_cast<bf16*>(a.o.out);
-          const int jrow = tile * 8 + rr;
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const float up = __shfl_down_sync(0xffffffffu, acc[k], 8);
-            const int n = col0 + k;
-            if (ok && rr < 8 && jrow < a.o.M && n < N) o[(long)n * a.o.ldo + jrow] = tobf16(silu_fast(acc[k]) * up);
-          }
+        since = 0;
+        if (KP == 1) {
+          store_out(cz.tile0);
         } else {
-          const int mrow = tile * 16 + rr;
-          if (ok && mrow < a.o.M) {
+          // A super-tile split along K: every part leaves its fp32 sums in the workspace; the
+          // CTA that delivers the last part adds them in ascending order of the parts (so the
+          // result does not depend on who was last) and stores the tile.
+          float* wsj = a.ws + (size_t)cz.jidx * (64 * 128);
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              const int n = col0 + k;
-              if (n >= N) continue;
-              if (a.o.out_f32) static_cast<float*>(a.o.out)[(long)n * a.o.ldo + mrow] = acc[k];
-              else static_cast<bf16*>(a.o.out)[(long)n * a.o.ldo + mrow] = tobf16(acc[k]);
+          for (int k = 0; k < 16; ++k) __stcg(wsj + (col0 + k) * 128 + m, acc[k]);
+          __threadfence();
+          asm volatile("bar.sync 1, %0;" ::"n"(kTcWarps * 32) : "memory");
+          const int st = cz.tile0 >> 3;
+          if (tid == 0) {
+            cuda::atomic_ref<int, cuda::thread_scope_device> arrivals(a.counters[st]);
+            const int last = arrivals.fetch_add(1, cuda::memory_order_acq_rel) == KP - 1;
+            if (last) a.counters[st] = 0;
+            s_last = last;
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(kTcWarps * 32) : "memory");
+          const int last = s_last;
+          asm volatile("bar.sync 1, %0;" ::"n"(kTcWarps * 32) : "memory");  // s_last may be rewritten
+          if (last) {
+            __threadfence();
+#pragma unroll
+            for (int k = 0; k < 16; ++k) acc[k] = 0.f;
+            for (int p2 = 0; p2 < KP; ++p2) {
+              const float* wp = a.ws + (size_t)(st * KP + p2) * (64 * 128);
+#pragma unroll
+              for (int k = 0; k < 16; ++k) acc[k] += __ldcg(wp + (col0 + k) * 128 + m);
             }
+            store_out(cz.tile0);
           }
         }
 #pragma unroll
         for (int k = 0; k < 16; ++k) acc[k] = 0.f;
+      } else {
+        ++since;
       }
+      cur_next(cz);
     }
     if (!ok) {  // give the copies that are still in flight a bounded chance to land
       __syncwarp();
@@ -601,6 +678,15 @@ const GemmGeom kGemmGeoms[] = {gemm_geom<16, 4, 4, 2>(), gemm_geom<16, 8, 2, 4>(
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Parts of K a super-tile is split into (tensor-memory kernel): 1 unless the matrix has fewer
+// super-tiles than half the SMs; then as many as keep the job count within the SMs, at least 8
+// groups each. Shape (and device) only, never the row count.
+int gemm_kparts(int tiles, int G, int epilogue) {
+  const int ST = (tiles + 7) / 8, sms = qe_sm_count();
+  if (epilogue != QE_EPI_NONE || ST * 2 > sms) return 1;
+  return std::max(1, std::min({sms / ST, G / 8, 16}));
+}
+
 // The opt-in limit of dynamic shared memory is a per-device, per-function setting: raised once.
 cudaError_t allow_smem(const GemmGeom& g, int which) {
   static bool done[2][64] = {};
@@ -630,6 +716,19 @@ int gemm_error_clear() {
 }  // namespace qb
 
 using namespace qb;
+
+extern "C" int qe_w4_plan_gemm(const qe_w4_params* p, const qe_w4_cfg* cfg, qe_w4_plan* plan) {
+  if (!p || !cfg || !plan || p->Mp <= 0 || p->Kp <= 0 || p->Mp % 16 || p->Kp % 128) return QE_ERR_ARG;
+  const int tiles = p->Mp / 16, ST = (tiles + 7) / 8;
+  const int kp = cfg->variant == 1 ? 1 : gemm_kparts(tiles, p->Kp / 128, p->epilogue);
+  plan->mode = cfg->variant == 1 ? 1 : 0;
+  plan->grid_x = std::min(qe_sm_count(), cfg->variant == 1 ? tiles : ST * kp);
+  plan->grid_y = 1;
+  plan->threads = cfg->variant == 1 ? 512 : kTcThreads;
+  plan->ws_floats = kp > 1 ? (long)ST * kp * 64 * 128 : 0;
+  plan->counters = kp > 1 ? ST : 0;
+  return 0;
+}
 
 extern "C" int qe_w4_gemm(const qe_w4_params* p, const qe_w4_cfg* cfg, void* stream) {
   if (!p || !cfg) return QE_ERR_ARG;
@@ -665,7 +764,11 @@ extern "C" int qe_w4_gemm(const qe_w4_params* p, const qe_w4_cfg* cfg, void* str
     a.o.out_f32 = (p->out_f32 && p->epilogue == QE_EPI_NONE) ? 1 : 0;
     a.G = G;
     a.tiles = p->Mp / 16;
-    a.nctas = std::min(qe_sm_count(), (a.tiles + 7) / 8);
+    a.kparts = gemm_kparts(a.tiles, G, p->epilogue);
+    if (a.kparts > 1 && (!p->ws || !p->counters)) a.kparts = 1;  // no scratch: whole K per job
+    a.ws = p->ws;
+    a.counters = p->counters;
+    a.nctas = std::min(qe_sm_count(), ((a.tiles + 7) / 8) * a.kparts);
     const bool pdl = cfg->pdl && pdl_launch_enabled() && pdl_trigger_enabled();
     return (int)launch(w4_gemm_tc_kernel, dim3(a.nctas), dim3(kTcThreads), kTcSmem, (cudaStream_t)stream, pdl, a);
   }
