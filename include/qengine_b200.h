@@ -219,7 +219,7 @@ typedef struct qe_w4_params {
   int M;               /* logical output rows (QE_EPI_SWIGLU: intermediate size I) */
   int K;               /* logical reduction length, Kp - 128 < K <= Kp */
   int Mp, Kp;          /* padded sizes (multiples of 16 / 128) */
-  int N;               /* activation rows, 1..8 */
+  int N;               /* activation rows, 1..8 (qe_w4_gemm: 1..QE_MAX_GEMM_ROWS) */
   long ldx, ldo;
   int epilogue;        /* QE_EPI_* */
   int out_f32;         /* 0: out is bf16 (the reference's contract). 1 (plain epilogue only): out is
@@ -301,6 +301,7 @@ int qe_w4_gemv_ex(const qe_w4_params* p, const qe_w4_norm* nrm, const qe_w4_cfg*
  * the arithmetic (thread map, reduction order) the GEMV selected by `cfg` uses in its prologue:
  * running this and then qe_w4_gemv on xn_out gives the bits of qe_w4_gemv_ex. For passes of
  * several rows, where N blocks in parallel beat every GEMV block repeating the work for all rows.
+ * N = 1..QE_MAX_GEMM_ROWS (the rows of a qe_w4_gemm pass).
  * h_out may alias h_in here; xn_out is required. K % 8 == 0. Semantics of launch_rmsnorm1p
  * (csrc/ops.h:8-9). */
 int qe_w4_norm_rows(const qe_w4_norm* nrm, int N, int K, const qe_w4_cfg* cfg, void* stream);

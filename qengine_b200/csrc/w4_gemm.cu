@@ -5,28 +5,35 @@
 //   out[n, m] = bf16( sum_g fp32(scale[m, g]) * sum_{k in group g} (code[m, k] - 8) * x[n, k] )
 //
 // No counterpart in the reference, which prefills in passes of at most 8 rows through its GEMV
-// (python/qengine/engine.py:558-573). Same packed wire format (w4_dev.cuh), same arithmetic per
-// 1 KB unit as the GEMV (exact products on mma.sync.m16n8k16, fp32 accumulation, the group scale
-// applied once per unit); the order in which the units of a tile are added differs from the
+// (python/qengine/engine.py:558-573). Same packed wire format (w4_dev.cuh) and the GEMV's
+// arithmetic per group (exact products of 4-bit integers and bf16 activations, fp32 sums, the
+// group scale applied once); the order in which the groups of a tile are added differs from the
 // GEMV's, so a row agrees with the GEMV to fp32 rounding, not bit for bit.
 //
-// Design. With R rows every unit (16 weight rows x 128 k, 1 KB) needs R x 256 B of activations:
-// at 64 rows 16 KB per KB of weights, far more than L2 can deliver to 148 SMs at the rate the
-// weights arrive. The activations therefore live in shared memory, one slab of GS groups (GS x 128
-// k) of all rows at a time, double-buffered and filled by bulk copies; all warps of a CTA walk K
-// slab by slab together. Work is dealt out in whole tiles (16 output rows): a CTA owns a
-// contiguous range of tiles, a warp owns one tile per round -- or, when the CTA has fewer tiles
-// than warps, 1/2 or 1/4 of the groups of every slab of one tile -- and keeps that tile's
+// Two kernels behind qe_w4_gemm:
+//   * w4_gemm_tc_kernel (the default): tcgen05.mma, operands in shared memory, accumulator in
+//     tensor memory; described in front of it, further down.
+//   * w4_gemm_kernel (cfg->variant == 1): mma.sync.m16n8k16 on register fragments, described
+//     next. With 8 row tiles it issues eight times the mma.sync instructions of the GEMV per
+//     unit and saturates near 130 TFLOP/s, the rate of the legacy tensor path on this part: 64
+//     rows cost about as much as the eight GEMV passes they replace. It is kept as the measured
+//     baseline of the tensor-memory kernel and as a second implementation the tests compare.
+//
+// w4_gemm_kernel. With R rows every unit (16 weight rows x 128 k, 1 KB) needs R x 256 B of
+// activations: at 64 rows 16 KB per KB of weights, far more than L2 can deliver to 148 SMs at
+// the rate the weights arrive. The activations therefore live in shared memory, one slab of GS
+// groups (GS x 128 k) of all rows at a time, double-buffered and filled by bulk copies; all warps
+// of a CTA walk K slab by slab together. Work is dealt out in whole tiles (16 output rows): a CTA
+// owns a contiguous range of tiles, a warp owns one tile per round -- or, when the CTA has fewer
+// tiles than warps, 1/2 or 1/4 of the groups of every slab of one tile -- and keeps that tile's
 // R x 16 sums in registers across all slabs. Each warp has a private ring of weight stages (its
 // units of one slab, contiguous in memory) fed by bulk copies, as in the GEMV. Warps that share
 // a tile add their sums through shared memory in ascending warp order after the last slab: no
-// atomics, results are bit-identical run to run and independent of the number of rows.
-// What bounds it: the B fragments of mma.sync come from shared memory, R x 256 B per unit and
-// warp, so at 64 rows the kernel runs at about half the rate of the weight stream (the shared
-// memory pipe, 128 B per clock and SM), at 32 rows near it.
+// atomics, results are bit-identical run to run.
 //
-// Every mbarrier wait is bounded; on expiry the warp records the error word, the CTA drains and
-// leaves.
+// Every mbarrier wait of both kernels is bounded; on expiry the warp records the error word
+// (reported by qe_w4_ring_error), stops working, keeps arriving where others wait for it, and the
+// CTA frees its tensor memory and leaves.
 #include <cuda/atomic>
 
 #include <algorithm>

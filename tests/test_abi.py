@@ -70,3 +70,40 @@ def test_fp16_activation_preconditions_are_checked_at_the_boundary():
     assert call(200, 256, base, 256) == -22      # K != Kp
     assert call(256, 256, base + 2, 256) == -22  # row start not 16-byte aligned
     assert call(256, 256, base, 260) == -22      # stride not a multiple of 8 elements
+
+
+def test_gemm_plan_and_argument_checks_without_gpu():
+    """qe_w4_plan_gemm is shape arithmetic (148 SMs assumed without a device): matrices with fewer
+    128-row super-tiles than half the SMs are split along K and need scratch, the others do not.
+    qe_w4_gemm refuses what its kernels cannot serve with QE_ERR_ARG (-22) before any launch."""
+    import ctypes as C
+    from qengine_b200 import _lib
+    cfg = _lib.W4Cfg()
+    _lib.lib.qe_w4_cfg_default(C.byref(cfg))
+
+    def plan(M, K, epilogue=0, variant=0):
+        p = _lib.W4Params(None, None, None, None, None, None, M, K, -(-M // 16) * 16, K, 64, K, M, epilogue, 0, 0)
+        c = _lib.W4Cfg(0, 0, 0, 1, variant, -1, 0, 4)
+        out = _lib.W4Plan()
+        assert _lib.lib.qe_w4_plan_gemm(C.byref(p), C.byref(c), C.byref(out)) == 0
+        return out
+
+    down = plan(5120, 17408)          # 40 super-tiles -> 3 parts of K
+    assert (down.grid_x, down.ws_floats, down.counters, down.threads) == (120, 40 * 3 * 64 * 128, 40, 17 * 32)
+    big = plan(2 * 17408, 5120, epilogue=1)  # gate/up: 272 super-tiles, never split
+    assert (big.grid_x, big.ws_floats, big.counters) == (148, 0, 0)
+    assert plan(16480, 5120).ws_floats == 0 and plan(16480, 5120).grid_x == 129
+    assert plan(5120, 17408, variant=1).ws_floats == 0  # the mma.sync kernel never splits
+
+    buf = (C.c_char * 4096)()
+    base = (C.addressof(buf) + 255) & ~255
+
+    def call(N, K, Kp, x, ldx, x_f16=0):
+        p = _lib.W4Params(base, base, x, base, None, None, 16, K, 16, Kp, N, ldx, 16, 0, 0, x_f16)
+        return _lib.lib.qe_w4_gemm(C.byref(p), C.byref(cfg), None)
+
+    assert call(65, 256, 256, base, 256) == -22      # more than 64 rows
+    assert call(8, 200, 256, base, 256) == -22       # K != Kp
+    assert call(8, 256, 256, base + 2, 256) == -22   # rows not 16-byte aligned
+    assert call(8, 256, 256, base, 260) == -22       # stride not a multiple of 8 elements
+    assert call(8, 256, 256, base, 256, x_f16=1) == -22
