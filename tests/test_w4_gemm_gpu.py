@@ -99,10 +99,12 @@ def test_gate_up_swiglu(api, variant):
 
 @pytest.mark.parametrize("M,K", [(16, 256), (1, 256), (100, 512), (2368 * 16, 256), (2368 * 16 + 40, 256),
                                  (5000 * 16, 256), (148 * 16, 768), (149 * 16, 1024), (777, 1280),
-                                 (148 * 128, 256), (148 * 128 + 16, 256), (300 * 128 - 40, 512)])
+                                 (148 * 128, 256), (148 * 128 + 16, 256), (300 * 128 - 40, 512),
+                                 (1000, 2048), (200, 3072), (5000, 1024)])
 def test_tile_counts_and_rounds(api, M, K, variant):
     """One tile, fewer tiles than SMs, exactly 16 per SM, more than 16 per SM (several rounds of the
-    mma.sync kernel); one super-tile of 128 rows per SM, one more, a ragged last super-tile."""
+    mma.sync kernel); one super-tile of 128 rows per SM, one more, a ragged last super-tile; few
+    super-tiles, so that K is split into 2, 3 and 3 parts, the last super-tile ragged."""
     p = api["q"](rand_w(M, K, seed=21))
     Wd = api["deq"](p)
     x = rand_x(64, K, seed=22)
