@@ -387,3 +387,18 @@ def test_spec_equals_plain_after_a_wide_prefill(setup, wide):
         for k in (1, 4):
             assert eng.generate_spec(prompt, n_new, k, wide=True) == plain, (P, k)
         assert ("wide", 64, True) in eng.graphs and ("wide", 64, False) in eng.graphs
+
+
+def test_wide_prefill_as_the_engines_default(setup):
+    """Engine(wide_prefill=True) feeds every long enough prompt in 64-row passes without being asked
+    per call; short prompts and wide=False still take the 8-row passes."""
+    from qengine_b200 import synth
+    from qengine_b200.engine import Engine
+    cfg, Wp, eng = setup
+    auto = Engine(cfg, synth.model_to(Wp, "cuda"), max_len=256, wide_prefill=True)
+    prompt = synth.prompt_ids(80, cfg.vocab, seed=33)
+    assert auto._wide_split(80, None) == 72 and auto._wide_split(80, False) == 0 and auto._wide_split(20, None) == 0
+    assert auto._wide_blocks(72) == [64, 8] and eng._wide_split(80, None) == 0
+    assert auto.generate(prompt, 24) == eng.generate(prompt, 24, wide=True)
+    assert ("wide", 64, False) in auto.graphs and ("wide", 8, False) in auto.graphs
+    assert auto.generate(prompt, 24, wide=False) == eng.generate(prompt, 24)
