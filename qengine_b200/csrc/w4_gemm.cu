@@ -297,15 +297,15 @@ __global__ void __launch_bounds__(NW * 32, 1) w4_gemm_kernel(const __grid_consta
 //     and copy the step's activations [64 rows x 128 k] from global memory (L2) into the same
 //     layout as the B operand, one own step ahead through registers;
 //   * a seventeenth warp waits for the 16 arrivals of a step and issues its 8 tcgen05.mma (M 128,
-//     N 64, K 16), which leave the group's exact integer dot products D_g[m, n] in one of two
+//     N 64, K 16), which leave the group's exact integer dot products D_g[m, n] in one of three
 //     64-column accumulators in tensor memory;
-//   * every one of the 16 warps, every step, reads its 16 columns of D_{g-1} for its row
+//   * every one of the 16 warps, every step, reads its 16 columns of D_{g-2} for its row
 //     (tcgen05.ld), multiplies by the row's group scale in fp32 and adds to 16 registers:
 //     acc[m, n] += scale[m, g] * D_g[m, n], groups in ascending order -- the arithmetic of the GEMV
 //     (exact products, fp32 sums inside a group, the scale applied once per group).
 // A, B and the accumulators have three stages and the halves alternate, so one half unpacks
-// step z + 1 while the products of steps z and z - 1 are under way; there is no block-wide barrier in
-// the loop, the warps meet only through two kinds of mbarrier: "step z may be multiplied" (one
+// step z + 1 while the products of steps z and z - 1 are under way; there is no block-wide barrier
+// in the loop, the warps meet only through two kinds of mbarrier: "step z may be multiplied" (one
 // arrival per warp: its share of the operands is stored, if it had one, and it has read the
 // products of step z - 3 out of the accumulator) and "products of step z complete"
 // (tcgen05.commit). After the last group the registers hold the super-tile's [128 x 64] result:
